@@ -1,0 +1,208 @@
+"""B200 (sm_100a) routed-expert MoE FFN operator: Python face of the C-ABI library.
+
+The product is `libb200moe.so` (CUDA C++, declared in include/b200moe.h). This module
+only binds it with ctypes and mirrors the reference engine's MoE operator surface
+(GpuModel::moe / moe_b / moe_q4w_run / router_topk_b, src/gpu/parts/40_model.inc of the
+reference) for Python callers and tests. There is no CPU or PyTorch fallback: if the
+library is missing or fails, calls raise.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200moe.so")
+
+GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
+GGML_Q5_1, GGML_Q4_K = 7, 12
+
+STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
+          5: "device timeout", 6: "NCCL error", 7: "out of memory"}
+
+# Every symbol include/b200moe.h declares: name -> (restype, argtypes)
+_P, _I, _SZ = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+
+
+class Config(ctypes.Structure):
+    """Field-for-field mirror of b200moe_config."""
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "experts", "topk", "d_model", "d_mid", "n_layers", "max_tokens", "has_shared", "device",
+        "gemm_impl", "decode_max_tokens", "ep_rank", "ep_size")] + [("reserved", ctypes.c_int32 * 4)]
+
+
+SYMBOLS = {
+    "b200moe_create": (_I, [ctypes.POINTER(Config), ctypes.POINTER(_P)]),
+    "b200moe_destroy": (_I, [_P]),
+    "b200moe_status_string": (ctypes.c_char_p, [_I]),
+    "b200moe_last_error": (ctypes.c_char_p, [_P]),
+    "b200moe_load_q4cp": (_I, [_P, _I, _P, _SZ, _P, _SZ]),
+    "b200moe_load_gguf": (_I, [_P, _I, _P, _P, _P, _I, _I]),
+    "b200moe_load_shared_q4cp": (_I, [_P, _I, _P, _P, _P, _P]),
+    "b200moe_forward": (_I, [_P, _I, _P, _I, _P, _P, _P]),
+    "b200moe_forward_routed": (_I, [_P, _I, _P, _I, _P, _P, _I, _P, _P]),
+    "b200moe_forward_host": (_I, [_P, _I, _P, _I, _P, _P, _P]),
+    "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
+    "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
+    "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
+    "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
+    "b200moe_synchronize": (_I, [_P, _P]),
+    "b200moe_launch_count": (ctypes.c_int64, [_P]),
+    "b200moe_version": (ctypes.c_char_p, []),
+}
+
+_lib = None
+
+
+class B200MoeError(RuntimeError):
+    def __init__(self, status, detail=""):
+        self.status = status
+        super().__init__("b200moe status %d (%s) %s" % (status, STATUS.get(status, "?"), detail))
+
+
+def lib():
+    """Load libb200moe.so and declare its entry points. Raises if it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "%s not found: build it with `python -m gfx1151_engine_b200.build` "
+                "(there is no fallback implementation)" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def _ptr(obj):
+    """Address of a torch tensor / numpy array / int; None -> NULL."""
+    if obj is None:
+        return None
+    if isinstance(obj, int):
+        return obj
+    if hasattr(obj, "data_ptr"):
+        return obj.data_ptr()
+    if hasattr(obj, "ctypes"):
+        return obj.ctypes.data
+    raise TypeError("cannot take the address of %r" % type(obj))
+
+
+def _stream(stream):
+    if stream is None:
+        return None
+    return getattr(stream, "cuda_stream", stream)
+
+
+class MoeOperator:
+    """One handle = the MoE layers of one GPU, with shared workspaces.
+
+    Method names follow the reference's host functions for this path; arguments are
+    device tensors (torch) or raw device addresses.
+    """
+
+    def __init__(self, experts, topk, d_model, d_mid, max_tokens, n_layers=1, has_shared=False,
+                 device=0, gemm_impl=GEMM_AUTO, decode_max_tokens=0, ep_rank=0, ep_size=1):
+        self.cfg = Config(experts, topk, d_model, d_mid, n_layers, max_tokens, int(has_shared), device,
+                          gemm_impl, decode_max_tokens, ep_rank, ep_size)
+        self._h = _P()
+        st = lib().b200moe_create(ctypes.byref(self.cfg), ctypes.byref(self._h))
+        if st != 0:
+            self._h = _P()
+            raise B200MoeError(st, "b200moe_create")
+
+    # -- plumbing ---------------------------------------------------------------------
+    def _check(self, st):
+        if st != 0:
+            raise B200MoeError(st, (lib().b200moe_last_error(self._h) or b"").decode())
+
+    def close(self):
+        if self._h:
+            lib().b200moe_destroy(self._h)
+            self._h = _P()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def launches(self):
+        return lib().b200moe_launch_count(self._h)
+
+    # -- weights (wview / gguf_experts_open of the reference) ------------------------------
+    def load_q4cp(self, layer, gate_up, down):
+        self._check(lib().b200moe_load_q4cp(self._h, layer, _ptr(gate_up), _nbytes(gate_up),
+                                            _ptr(down), _nbytes(down)))
+
+    def load_gguf(self, layer, gate, up, down, type_gu=GGML_Q4_K, type_dn=GGML_Q5_1):
+        self._check(lib().b200moe_load_gguf(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),
+                                            type_gu, type_dn))
+
+    def load_shared_q4cp(self, layer, gate, up, down, gate_w_bf16):
+        self._check(lib().b200moe_load_shared_q4cp(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),
+                                                   _ptr(gate_w_bf16)))
+
+    # -- forward (moe / moe_b of the reference) ---------------------------------------------
+    def moe_b(self, layer, x, logits, out, T=None, stream=None):
+        """out[T][d] (bf16) = MoE(x[T][d] bf16, router logits[T][E] f32); asynchronous."""
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_forward(self._h, layer, _ptr(x), T, _ptr(logits), _ptr(out),
+                                          _stream(stream)))
+
+    moe = moe_b  # the single-token entry point of the reference is the same call with T = 1
+
+    def moe_q4w_run(self, layer, x, topids, topw, out, stride=16, T=None, stream=None):
+        """The seam below the router: caller-supplied top-k ids / weights."""
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_forward_routed(self._h, layer, _ptr(x), T, _ptr(topids), _ptr(topw),
+                                                 stride, _ptr(out), _stream(stream)))
+
+    def moe_b_host(self, layer, x_host, logits_host, out_host, T, stream=None):
+        """Host buffers in, host buffer out; returns when the result is in out_host."""
+        self._check(lib().b200moe_forward_host(self._h, layer, _ptr(x_host), T, _ptr(logits_host),
+                                               _ptr(out_host), _stream(stream)))
+
+    def router_topk_b(self, logits, topids, topw, stride=16, T=None, stream=None):
+        T = logits.shape[0] if T is None else T
+        self._check(lib().b200moe_router_topk(self._h, _ptr(logits), T, _ptr(topids), _ptr(topw),
+                                              stride, _stream(stream)))
+
+    def route(self, topids, topw, T, stride=16, stream=None):
+        self._check(lib().b200moe_route(self._h, _ptr(topids), _ptr(topw), stride, T, _stream(stream)))
+
+    def synchronize(self, stream=None):
+        """Wait for the stream and raise if a device-side wait gave up."""
+        self._check(lib().b200moe_synchronize(self._h, _stream(stream)))
+
+    # -- inspection ---------------------------------------------------------------------------
+    def get_routing(self, T):
+        """(topids[T,16], topw[T,16], tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k]) as numpy."""
+        import numpy as np
+        k, E = self.cfg.topk, self.cfg.experts
+        ids = np.zeros((T, 16), np.int32)
+        w = np.zeros((T, 16), np.float32)
+        tok = np.zeros(T * k, np.int32)
+        pw = np.zeros(T * k, np.float32)
+        eoff = np.zeros(E + 1, np.int32)
+        pid = np.zeros(T * k, np.int32)
+        self._check(lib().b200moe_debug_get_routing(self._h, T, _ptr(ids), _ptr(w), _ptr(tok), _ptr(pw),
+                                                    _ptr(eoff), _ptr(pid)))
+        return ids, w, tok, pw, eoff, pid
+
+    def dequant_rows(self, layer, which, expert, row0, nrows, out, stream=None):
+        self._check(lib().b200moe_dequant_rows(self._h, layer, which, expert, row0, nrows, _ptr(out),
+                                               _stream(stream)))
+
+
+def _nbytes(obj):
+    if hasattr(obj, "nbytes"):
+        return int(obj.nbytes)
+    if hasattr(obj, "numel"):
+        return int(obj.numel() * obj.element_size())
+    raise TypeError("cannot size %r" % type(obj))
+
+
+def version():
+    return lib().b200moe_version().decode()

@@ -1,0 +1,599 @@
+// api.cu -- the C ABI declared in include/b200moe.h: handle, workspaces, weight loading
+// (one-time repack into HBM) and the forward sequences. Host-side mirror of the
+// reference's GpuModel::moe / moe_b / moe_q4w_run / moe_gguf dispatch
+// (src/gpu/parts/40_model.inc:1664-1861, 4018-4157): same thresholds (T <= 16 takes the
+// GEMV path), same order of stages, status codes instead of exit().
+#include "../../include/b200moe.h"
+#include "kernels.h"
+#include "tc.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+using namespace b200moe;
+
+namespace {
+
+struct LayerWeights {
+  Image gu, dn, sh_gu, sh_dn;
+  uint16_t* sh_gate_w = nullptr;
+  bool loaded = false, shared_loaded = false;
+};
+
+}  // namespace
+
+struct b200moe_ctx {
+  b200moe_config cfg{};
+  int decode_max = 16;
+  int tile_cap = kTcTileN;
+  std::vector<LayerWeights> layers;
+  std::vector<void*> allocs;  // everything cudaMalloc'ed for workspaces
+  RouteBuffers rb{};
+  void* hid = nullptr;      // [rows][mid] fp32 (GEMV path) or fp16 (tensor-core path)
+  void* pairs = nullptr;    // [rows][d]   fp32 or fp16
+  __half* x_sorted = nullptr;
+  void *x_stage = nullptr, *out_stage = nullptr;
+  float* logits_stage = nullptr;
+  int32_t* status_dev = nullptr;
+  int32_t* status_host = nullptr;  // pinned
+  TcPlan* tc = nullptr;
+  int64_t launches = 0;
+  int max_rows = 0, max_tiles = 0, max_tiles_sh = 0;
+  std::string err;
+};
+
+namespace {
+
+int fail(b200moe_handle h, int code, const std::string& msg) {
+  if (h) h->err = msg;
+  return code;
+}
+
+#define CU_TRY(h, expr)                                                                  \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return fail(h, B200MOE_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+  } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(b200moe_handle h, T** p, size_t count) {
+  void* q = nullptr;
+  cudaError_t e = cudaMalloc(&q, count * sizeof(T) + 256);
+  if (e == cudaSuccess) {
+    h->allocs.push_back(q);
+    *p = (T*)q;
+  }
+  return e;
+}
+
+size_t q4cp_bytes(size_t rows, size_t cols) {
+  return 64 + rows * cols / 2 + rows * (((cols / 32 * 2) + 15) & ~(size_t)15);
+}
+
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Device-visible copy of a source blob: the pointer itself when it already is device
+// memory, else a temporary upload (freed by the caller through `tmp`).
+cudaError_t stage(const void* src, size_t bytes, const uint8_t** dev, std::vector<void*>& tmp) {
+  if (is_device_ptr(src)) {
+    *dev = (const uint8_t*)src;
+    return cudaSuccess;
+  }
+  void* q = nullptr;
+  cudaError_t e = cudaMalloc(&q, bytes + 16);
+  if (e != cudaSuccess) return e;
+  tmp.push_back(q);
+  e = cudaMemcpy(q, src, bytes, cudaMemcpyHostToDevice);
+  *dev = (const uint8_t*)q;
+  return e;
+}
+
+void free_all(std::vector<void*>& v) {
+  for (void* p : v) cudaFree(p);
+  v.clear();
+}
+
+cudaError_t alloc_image(Image& img, int fmt, int n_experts, int rows, int K, int paired) {
+  img.fmt = fmt;
+  img.n_experts = n_experts;
+  img.paired = paired;
+  img.n_mtiles = paired ? rows / 64 : rows / 128;  // paired: rows = mid (gate rows)
+  img.n_kblocks = K / kTileK;
+  cudaError_t e = cudaMalloc((void**)&img.data, img.expert_stride() * n_experts + 256);
+  if (e != cudaSuccess) return e;
+  return cudaMalloc((void**)&img.book, 32 * sizeof(float));
+}
+
+void free_image(Image& img) {
+  if (img.data) cudaFree(img.data);
+  if (img.book) cudaFree(img.book);
+  img = Image{};
+}
+
+SrcTensor q4cp_src(const uint8_t* blob, long long rows_total, long long cols,
+                   long long rows_per_expert, long long row_off) {
+  SrcTensor s;
+  s.codes = blob + 64;
+  s.scales = blob + 64 + rows_total * cols / 2;
+  s.rows_per_expert = rows_per_expert;
+  s.row_off = row_off;
+  s.scale_stride = ((cols / 32 * 2) + 15) & ~15ll;
+  return s;
+}
+
+int check_layer(b200moe_handle h, int layer) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  if (layer < 0 || layer >= (int)h->layers.size())
+    return fail(h, B200MOE_ERR_BAD_ARG, "layer index out of range");
+  return B200MOE_OK;
+}
+
+int local_experts(const b200moe_config& c) { return c.experts / c.ep_size; }
+int first_expert(const b200moe_config& c) { return c.ep_rank * (c.experts / c.ep_size); }
+
+}  // namespace
+
+extern "C" {
+
+const char* b200moe_version(void) { return "b200moe 0.1 sm_100a"; }
+
+const char* b200moe_status_string(int s) {
+  switch (s) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_ERR_BAD_ARG: return "bad argument";
+    case B200MOE_ERR_UNSUPPORTED: return "unsupported shape or format";
+    case B200MOE_ERR_CUDA: return "CUDA error";
+    case B200MOE_ERR_NOT_LOADED: return "layer weights not loaded";
+    case B200MOE_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case B200MOE_ERR_NCCL: return "NCCL error";
+    case B200MOE_ERR_ALLOC: return "out of memory";
+    default: return "unknown status";
+  }
+}
+
+const char* b200moe_last_error(b200moe_handle h) { return h ? h->err.c_str() : "null handle"; }
+
+int64_t b200moe_launch_count(b200moe_handle h) { return h ? h->launches : 0; }
+
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
+  if (!cfg || !out) return B200MOE_ERR_BAD_ARG;
+  *out = nullptr;
+  b200moe_config c = *cfg;
+  if (c.ep_size <= 0) c.ep_size = 1;
+  if (c.n_layers <= 0) c.n_layers = 1;
+  if (c.experts < 1 || c.topk < 1 || c.d_model < 1 || c.d_mid < 1 || c.max_tokens < 1 ||
+      c.ep_rank < 0 || c.ep_rank >= c.ep_size)
+    return B200MOE_ERR_BAD_ARG;
+  if (c.experts > kMaxExperts || c.topk > kMaxTopK || c.topk > c.experts ||
+      c.d_model % 128 != 0 || c.d_mid % 64 != 0 || c.experts % c.ep_size != 0)
+    return B200MOE_ERR_UNSUPPORTED;
+  if (cudaSetDevice(c.device) != cudaSuccess) {
+    cudaGetLastError();
+    return B200MOE_ERR_CUDA;
+  }
+  b200moe_handle h = new (std::nothrow) b200moe_ctx();
+  if (!h) return B200MOE_ERR_ALLOC;
+  h->cfg = c;
+  h->decode_max = c.decode_max_tokens > 0 ? c.decode_max_tokens : 16;
+  h->layers.resize(c.n_layers);
+  const int Tm = c.max_tokens, k = c.topk, E = c.experts, d = c.d_model, mid = c.d_mid;
+  const size_t pairs = (size_t)Tm * k;
+  const size_t rows = pairs + (c.has_shared ? Tm : 0);
+  h->max_rows = (int)rows;
+  h->max_tiles = (int)(pairs / h->tile_cap) + E + 1;
+  h->max_tiles_sh = Tm / h->tile_cap + 1;
+  const size_t dec_rows = (size_t)std::min(Tm, h->decode_max) * (k + (c.has_shared ? 1 : 0));
+  const bool simt_all = c.gemm_impl == B200MOE_GEMM_SIMT;
+  const size_t hid_bytes = std::max(rows * mid * (simt_all ? 4 : 2), dec_rows * mid * 4);
+  const size_t pair_bytes = std::max(rows * d * (simt_all ? 4 : 2), dec_rows * d * 4);
+  cudaError_t e = cudaSuccess;
+  auto A = [&](auto** p, size_t n) {
+    if (e == cudaSuccess) e = dev_alloc(h, p, n);
+  };
+  A(&h->rb.topids, (size_t)Tm * kIdStride);
+  A(&h->rb.topw, (size_t)Tm * kIdStride);
+  A(&h->rb.tokidx, rows);
+  A(&h->rb.pw, rows);
+  A(&h->rb.eoff, (size_t)E + 1);
+  A(&h->rb.pairids, pairs);
+  A(&h->rb.blockcnt, ((pairs + 511) / 512) * E);
+  A(&h->rb.runs, (size_t)kMaxExperts + 1);
+  A(&h->rb.n_runs, 2);
+  A(&h->rb.tiles, (size_t)h->max_tiles);
+  A(&h->rb.tiles_sh, (size_t)h->max_tiles_sh);
+  A(&h->rb.n_tiles, 2);
+  A(&h->rb.sgate, (size_t)Tm);
+  A((uint8_t**)&h->hid, hid_bytes);
+  A((uint8_t**)&h->pairs, pair_bytes);
+  if (!simt_all) A(&h->x_sorted, rows * d);
+  A((uint8_t**)&h->x_stage, (size_t)Tm * d * 2);
+  A((uint8_t**)&h->out_stage, (size_t)Tm * d * 2);
+  A(&h->logits_stage, (size_t)Tm * E);
+  A(&h->status_dev, 4);
+  if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 16);
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&h->status_host, 16);
+  if (e == cudaSuccess && !simt_all)
+    e = tc_create(&h->tc, h->x_sorted, (__half*)h->hid, (long long)rows, d, mid);
+  if (e != cudaSuccess) {
+    std::string msg = std::string("b200moe_create: ") + cudaGetErrorString(e);
+    cudaGetLastError();
+    b200moe_destroy(h);
+    fprintf(stderr, "%s\n", msg.c_str());
+    return e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA;
+  }
+  *out = h;
+  return B200MOE_OK;
+}
+
+int b200moe_destroy(b200moe_handle h) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  cudaSetDevice(h->cfg.device);
+  cudaDeviceSynchronize();
+  for (auto& L : h->layers) {
+    free_image(L.gu);
+    free_image(L.dn);
+    free_image(L.sh_gu);
+    free_image(L.sh_dn);
+    if (L.sh_gate_w) cudaFree(L.sh_gate_w);
+  }
+  free_all(h->allocs);
+  if (h->status_host) cudaFreeHost(h->status_host);
+  if (h->tc) tc_destroy(h->tc);
+  cudaGetLastError();
+  delete h;
+  return B200MOE_OK;
+}
+
+int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size_t gate_up_bytes,
+                      const void* down_src, size_t down_bytes) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!gate_up_src || !down_src) return fail(h, B200MOE_ERR_BAD_ARG, "null weight pointer");
+  const b200moe_config& c = h->cfg;
+  const size_t E = c.experts, d = c.d_model, mid = c.d_mid;
+  if (gate_up_bytes != q4cp_bytes(E * 2 * mid, d) || down_bytes != q4cp_bytes(E * d, mid))
+    return fail(h, B200MOE_ERR_BAD_ARG, "q4cp blob size does not match [E*2*mid,d] / [E*d,mid]");
+  if (((uintptr_t)gate_up_src | (uintptr_t)down_src) & 15)
+    return fail(h, B200MOE_ERR_BAD_ARG, "q4cp blobs must be 16-byte aligned");
+  CU_TRY(h, cudaSetDevice(c.device));
+  LayerWeights& L = h->layers[layer];
+  free_image(L.gu);
+  free_image(L.dn);
+  L.loaded = false;
+  std::vector<void*> tmp;
+  const uint8_t *gu = nullptr, *dn = nullptr;
+  const int nl = local_experts(c), e0 = first_expert(c);
+  cudaError_t e = stage(gate_up_src, gate_up_bytes, &gu, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.gu, kQ4CP, nl, (int)mid, (int)d, 1);
+  if (e == cudaSuccess) {
+    SrcTensor g = q4cp_src(gu, E * 2 * mid, d, 2 * mid, 0), u = q4cp_src(gu, E * 2 * mid, d, 2 * mid, mid);
+    e = launch_repack(L.gu, g, u, (int)d, e0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, gu, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book + 16, gu, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e == cudaSuccess) e = stage(down_src, down_bytes, &dn, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.dn, kQ4CP, nl, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) {
+    SrcTensor a = q4cp_src(dn, E * d, mid, d, 0);
+    e = launch_repack(L.dn, a, a, (int)mid, e0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, dn, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book + 16, dn, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(h, e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA,
+                std::string("load_q4cp: ") + cudaGetErrorString(e));
+  }
+  L.loaded = true;
+  return B200MOE_OK;
+}
+
+int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
+                      const void* down_src, int type_gu, int type_dn) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!gate_src || !up_src || !down_src) return fail(h, B200MOE_ERR_BAD_ARG, "null weight pointer");
+  if (type_gu != B200MOE_GGML_Q4_K || type_dn != B200MOE_GGML_Q5_1)
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "GGUF experts: gate/up must be Q4_K and down Q5_1");
+  const b200moe_config& c = h->cfg;
+  const size_t E = c.experts, d = c.d_model, mid = c.d_mid;
+  if (d % 256 != 0) return fail(h, B200MOE_ERR_UNSUPPORTED, "Q4_K needs d_model % 256 == 0");
+  CU_TRY(h, cudaSetDevice(c.device));
+  LayerWeights& L = h->layers[layer];
+  free_image(L.gu);
+  free_image(L.dn);
+  L.loaded = false;
+  const size_t gu_bytes = E * mid * (d / 256 * 144), dn_bytes = E * d * (mid / 32 * 24);
+  std::vector<void*> tmp;
+  const uint8_t *g = nullptr, *u = nullptr, *dn = nullptr;
+  const int nl = local_experts(c), e0 = first_expert(c);
+  cudaError_t e = stage(gate_src, gu_bytes, &g, tmp);
+  if (e == cudaSuccess) e = stage(up_src, gu_bytes, &u, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.gu, kQ4K, nl, (int)mid, (int)d, 1);
+  if (e == cudaSuccess) {
+    SrcTensor sg, su;
+    sg.codes = g;
+    sg.rows_per_expert = mid;
+    su.codes = u;
+    su.rows_per_expert = mid;
+    e = launch_repack(L.gu, sg, su, (int)d, e0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e == cudaSuccess) e = stage(down_src, dn_bytes, &dn, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.dn, kQ51, nl, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) {
+    SrcTensor a;
+    a.codes = dn;
+    a.rows_per_expert = d;
+    e = launch_repack(L.dn, a, a, (int)mid, e0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(h, e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA,
+                std::string("load_gguf: ") + cudaGetErrorString(e));
+  }
+  L.loaded = true;
+  return B200MOE_OK;
+}
+
+int b200moe_load_shared_q4cp(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
+                             const void* down_src, const void* gate_w_bf16_src) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!h->cfg.has_shared) return fail(h, B200MOE_ERR_BAD_ARG, "handle was created without a shared expert");
+  if (!gate_src || !up_src || !down_src || !gate_w_bf16_src)
+    return fail(h, B200MOE_ERR_BAD_ARG, "null weight pointer");
+  if (((uintptr_t)gate_src | (uintptr_t)up_src | (uintptr_t)down_src) & 15)
+    return fail(h, B200MOE_ERR_BAD_ARG, "q4cp blobs must be 16-byte aligned");
+  const b200moe_config& c = h->cfg;
+  const size_t d = c.d_model, mid = c.d_mid;
+  CU_TRY(h, cudaSetDevice(c.device));
+  LayerWeights& L = h->layers[layer];
+  free_image(L.sh_gu);
+  free_image(L.sh_dn);
+  if (L.sh_gate_w) cudaFree(L.sh_gate_w), L.sh_gate_w = nullptr;
+  L.shared_loaded = false;
+  std::vector<void*> tmp;
+  const uint8_t *g = nullptr, *u = nullptr, *dn = nullptr;
+  cudaError_t e = stage(gate_src, q4cp_bytes(mid, d), &g, tmp);
+  if (e == cudaSuccess) e = stage(up_src, q4cp_bytes(mid, d), &u, tmp);
+  if (e == cudaSuccess) e = stage(down_src, q4cp_bytes(d, mid), &dn, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.sh_gu, kQ4CP, 1, (int)mid, (int)d, 1);
+  if (e == cudaSuccess) e = alloc_image(L.sh_dn, kQ4CP, 1, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) {
+    e = launch_repack(L.sh_gu, q4cp_src(g, mid, d, mid, 0), q4cp_src(u, mid, d, mid, 0), (int)d, 0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) {
+    SrcTensor a = q4cp_src(dn, d, mid, d, 0);
+    e = launch_repack(L.sh_dn, a, a, (int)mid, 0, 0);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(L.sh_gu.book, g, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(L.sh_gu.book + 16, u, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(L.sh_dn.book, dn, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(L.sh_dn.book + 16, dn, 64, cudaMemcpyDeviceToDevice);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&L.sh_gate_w, d * 2);
+  if (e == cudaSuccess) e = cudaMemcpy(L.sh_gate_w, gate_w_bf16_src, d * 2, cudaMemcpyDefault);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(h, e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA,
+                std::string("load_shared_q4cp: ") + cudaGetErrorString(e));
+  }
+  L.shared_loaded = true;
+  return B200MOE_OK;
+}
+
+int b200moe_router_topk(b200moe_handle h, const float* logits_dev, int T, int32_t* topids_dev,
+                        float* topw_dev, int stride, void* stream) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  if (!logits_dev || !topids_dev || !topw_dev || T < 0 || stride < h->cfg.topk)
+    return fail(h, B200MOE_ERR_BAD_ARG, "router_topk: bad argument");
+  if (T == 0) return B200MOE_OK;
+  CU_TRY(h, launch_router_topk(logits_dev, T, h->cfg.experts, h->cfg.topk, topids_dev, topw_dev,
+                               stride, (cudaStream_t)stream));
+  h->launches++;
+  return B200MOE_OK;
+}
+
+int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw_dev, int stride,
+                  int T, void* stream) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  if (!topids_dev || !topw_dev || T < 0 || T > h->cfg.max_tokens || stride < h->cfg.topk)
+    return fail(h, B200MOE_ERR_BAD_ARG, "route: bad argument");
+  if (T == 0) return B200MOE_OK;
+  int n = 0;
+  CU_TRY(h, launch_route(h->rb, topids_dev, topw_dev, stride, T, h->cfg.topk, h->cfg.experts,
+                         h->tile_cap, (cudaStream_t)stream, &n));
+  h->launches += n;
+  return B200MOE_OK;
+}
+
+static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const int32_t* ids,
+                        const float* w, int stride, void* out, cudaStream_t st) {
+  const b200moe_config& c = h->cfg;
+  LayerWeights& L = h->layers[layer];
+  const int k = c.topk, E = c.experts, d = c.d_model, mid = c.d_mid;
+  const bool shared = c.has_shared != 0;
+  if (!L.loaded || (shared && !L.shared_loaded))
+    return fail(h, B200MOE_ERR_NOT_LOADED, "forward: layer weights not loaded");
+  int n = 0;
+  CU_TRY(h, launch_route(h->rb, ids, w, stride, T, k, E, h->tile_cap, st, &n));
+  if (shared) {
+    CU_TRY(h, launch_shared_gate(x, L.sh_gate_w, T, d, k, h->rb, st));
+    n++;
+  }
+  const int pairs = T * k;
+  const bool simt = c.gemm_impl == B200MOE_GEMM_SIMT ||
+                    (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max);
+  if (!simt && (L.gu.fmt != kQ4CP || L.dn.fmt != kQ4CP))
+    return fail(h, B200MOE_ERR_UNSUPPORTED,
+                "tensor-core path implements q4cp experts only; create the handle with "
+                "B200MOE_GEMM_SIMT for GGUF experts at T > decode_max_tokens");
+  if (simt && c.gemm_impl != B200MOE_GEMM_SIMT && T > h->decode_max)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
+  if (simt) {
+    const int max_runs = std::min(E, pairs);
+    CU_TRY(h, launch_up_simt(L.gu, x, d, mid, h->rb.tokidx, h->rb.runs, h->rb.n_runs, max_runs,
+                             (float*)h->hid, st));
+    CU_TRY(h, launch_down_simt(L.dn, (const float*)h->hid, d, mid, h->rb.runs, h->rb.n_runs,
+                               max_runs, (float*)h->pairs, st));
+    n += 2;
+    if (shared) {
+      CU_TRY(h, launch_up_simt(L.sh_gu, x, d, mid, h->rb.tokidx, h->rb.runs + kMaxExperts,
+                               h->rb.n_runs + 1, 1, (float*)h->hid, st));
+      CU_TRY(h, launch_down_simt(L.sh_dn, (const float*)h->hid, d, mid, h->rb.runs + kMaxExperts,
+                                 h->rb.n_runs + 1, 1, (float*)h->pairs, st));
+      n += 2;
+    }
+    CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
+                                 shared ? pairs : -1, out, st));
+    n++;
+  } else {
+    if (!h->tc) return fail(h, B200MOE_ERR_UNSUPPORTED, "tensor-core path not available on this handle");
+    const int rows = pairs + (shared ? T : 0);
+    CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, rows, d, h->x_sorted, st));
+    n++;
+    CU_TRY(h, launch_up_tc(h->tc, L.gu, h->rb.tiles, h->rb.n_tiles, h->max_tiles, (__half*)h->hid,
+                           h->status_dev, st));
+    CU_TRY(h, launch_down_tc(h->tc, L.dn, h->rb.tiles, h->rb.n_tiles, h->max_tiles,
+                             (__half*)h->pairs, h->status_dev, st));
+    n += 2;
+    if (shared) {
+      CU_TRY(h, launch_up_tc(h->tc, L.sh_gu, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh,
+                             (__half*)h->hid, h->status_dev, st));
+      CU_TRY(h, launch_down_tc(h->tc, L.sh_dn, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh,
+                               (__half*)h->pairs, h->status_dev, st));
+      n += 2;
+    }
+    CU_TRY(h, launch_combine_f16((const __half*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
+                                 shared ? pairs : -1, out, st));
+    n++;
+  }
+  h->launches += n;
+  return B200MOE_OK;
+}
+
+int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
+                    const float* logits_dev, void* out_bf16_dev, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_dev || !logits_dev || !out_bf16_dev || T < 0 || T > h->cfg.max_tokens)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward: bad argument (null pointer or T out of range)");
+  if (T == 0) return B200MOE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_TRY(h, launch_router_topk(logits_dev, T, h->cfg.experts, h->cfg.topk, h->rb.topids, h->rb.topw,
+                               kIdStride, st));
+  h->launches++;
+  return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st);
+}
+
+int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
+                           const int32_t* topids_dev, const float* topw_dev, int stride,
+                           void* out_bf16_dev, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_dev || !topids_dev || !topw_dev || !out_bf16_dev || T < 0 ||
+      T > h->cfg.max_tokens || stride < h->cfg.topk)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward_routed: bad argument");
+  if (T == 0) return B200MOE_OK;
+  return forward_impl(h, layer, x_bf16_dev, T, topids_dev, topw_dev, stride, out_bf16_dev,
+                      (cudaStream_t)stream);
+}
+
+int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, int T,
+                         const float* logits_host, void* out_bf16_host, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_host || !logits_host || !out_bf16_host || T < 0 || T > h->cfg.max_tokens)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward_host: bad argument");
+  if (T == 0) return B200MOE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t xb = (size_t)T * h->cfg.d_model * 2;
+  CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_bf16_host, xb, cudaMemcpyHostToDevice, st));
+  CU_TRY(h, cudaMemcpyAsync(h->logits_stage, logits_host, (size_t)T * h->cfg.experts * 4,
+                            cudaMemcpyHostToDevice, st));
+  if (int s = b200moe_forward(h, layer, h->x_stage, T, h->logits_stage, h->out_stage, stream)) return s;
+  CU_TRY(h, cudaMemcpyAsync(out_bf16_host, h->out_stage, xb, cudaMemcpyDeviceToHost, st));
+  CU_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost, st));
+  CU_TRY(h, cudaStreamSynchronize(st));
+  if (h->status_host[0] != 0) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "device-side wait timed out (code %d, detail %d)", h->status_host[0],
+             h->status_host[1]);
+    return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
+  }
+  return B200MOE_OK;
+}
+
+int b200moe_debug_get_routing(b200moe_handle h, int T, int32_t* topids_host, float* topw_host,
+                              int32_t* tokidx_host, float* pw_host, int32_t* eoff_host,
+                              int32_t* pairids_host) {
+  if (!h || T < 0 || T > h->cfg.max_tokens) return B200MOE_ERR_BAD_ARG;
+  CU_TRY(h, cudaDeviceSynchronize());
+  const size_t pairs = (size_t)T * h->cfg.topk;
+  if (topids_host) CU_TRY(h, cudaMemcpy(topids_host, h->rb.topids, (size_t)T * kIdStride * 4, cudaMemcpyDeviceToHost));
+  if (topw_host) CU_TRY(h, cudaMemcpy(topw_host, h->rb.topw, (size_t)T * kIdStride * 4, cudaMemcpyDeviceToHost));
+  if (tokidx_host) CU_TRY(h, cudaMemcpy(tokidx_host, h->rb.tokidx, pairs * 4, cudaMemcpyDeviceToHost));
+  if (pw_host) CU_TRY(h, cudaMemcpy(pw_host, h->rb.pw, pairs * 4, cudaMemcpyDeviceToHost));
+  if (eoff_host) CU_TRY(h, cudaMemcpy(eoff_host, h->rb.eoff, ((size_t)h->cfg.experts + 1) * 4, cudaMemcpyDeviceToHost));
+  if (pairids_host) CU_TRY(h, cudaMemcpy(pairids_host, h->rb.pairids, pairs * 4, cudaMemcpyDeviceToHost));
+  CU_TRY(h, cudaMemcpy(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost));
+  if (h->status_host[0] != 0) return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, "device-side wait timed out");
+  return B200MOE_OK;
+}
+
+int b200moe_synchronize(b200moe_handle h, void* stream) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost, st));
+  CU_TRY(h, cudaStreamSynchronize(st));
+  if (h->status_host[0] != 0) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "device-side wait timed out (code %d, wait site %d)", h->status_host[0],
+             h->status_host[1]);
+    CU_TRY(h, cudaMemsetAsync(h->status_dev, 0, 16, st));
+    CU_TRY(h, cudaStreamSynchronize(st));
+    return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
+  }
+  return B200MOE_OK;
+}
+
+int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int row0, int nrows,
+                         float* out_dev, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  LayerWeights& L = h->layers[layer];
+  if (which < 0 || which > 3 || !out_dev || nrows < 0 || row0 < 0)
+    return fail(h, B200MOE_ERR_BAD_ARG, "dequant_rows: bad argument");
+  const bool sh = which >= 2;
+  if (sh ? !L.shared_loaded : !L.loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "dequant_rows: not loaded");
+  const Image& img = which == 0 ? L.gu : which == 1 ? L.dn : which == 2 ? L.sh_gu : L.sh_dn;
+  const int e_local = sh ? expert : expert - first_expert(h->cfg);
+  const int rows_per = img.paired ? 2 * h->cfg.d_mid : h->cfg.d_model;
+  if (e_local < 0 || e_local >= img.n_experts || row0 + nrows > rows_per)
+    return fail(h, B200MOE_ERR_BAD_ARG, "dequant_rows: expert or rows out of range");
+  if (nrows == 0) return B200MOE_OK;
+  CU_TRY(h, launch_dequant_rows(img, e_local, row0, nrows, h->cfg.d_mid, out_dev, (cudaStream_t)stream));
+  h->launches++;
+  return B200MOE_OK;
+}
+
+}  // extern "C"

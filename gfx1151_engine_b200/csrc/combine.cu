@@ -1,0 +1,120 @@
+// combine.cu -- the memory-bound ends of the path: the expert-sorted activation gather
+// in front of the grouped GEMM and the weighted top-k combine behind it.
+//
+// Combine replaces k_moe_reduce_pw / k_moe_reduce_pw_sg
+// (src/gpu/parts/24_kernels_moe_lt.inc:81-124 of the reference):
+//   out[t][c] = sum_{s<k} pw[row_s] * pairs[row_s][c]   (+ gate[t] * pairs[shared row][c])
+// with row_s = pairids[t*k + s], i.e. a fixed order (ascending expert id), fp32
+// accumulation, every output element written exactly once -- deterministic, no atomics.
+#include "kernels.h"
+
+namespace b200moe {
+
+namespace {
+
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __half* p, float* v) {
+  uint4 u = *(const uint4*)p;
+  const __half2* h = (const __half2*)&u;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// One block per token; each thread owns 8 consecutive columns per step.
+template <typename TP>
+__global__ void __launch_bounds__(256)
+k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
+          const int32_t* __restrict__ pairids, int k, int d, int shared_row0,
+          __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  __shared__ int s_row[kMaxTopK + 1];
+  __shared__ float s_w[kMaxTopK + 1];
+  int n = k;
+  if (threadIdx.x < k) {
+    int row = pairids[(size_t)t * k + threadIdx.x];
+    s_row[threadIdx.x] = row;
+    s_w[threadIdx.x] = pw[row];
+  }
+  if (shared_row0 >= 0) {
+    if (threadIdx.x == 0) {
+      s_row[k] = shared_row0 + t;
+      s_w[k] = pw[shared_row0 + t];
+    }
+    n = k + 1;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < n; s++) {
+      float v[8];
+      load8(pairs + (size_t)s_row[s] * d + c, v);
+      const float w = s_w[s];
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[i] = fmaf(w, v[i], acc[i]);
+    }
+    uint4 o;
+    __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+    for (int i = 0; i < 4; i++) ob[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *(uint4*)(out + (size_t)t * d + c) = o;
+  }
+}
+
+// x_sorted[row][:] = fp16(x[tokidx[row]][:]); bf16 -> fp16 is exact for 2^-14 <= |v| < 65520,
+// larger magnitudes saturate to the largest finite half.
+__global__ void __launch_bounds__(256)
+k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx, int rows, int d,
+             __half* __restrict__ xs) {
+  const int per_row = d / 8;
+  const long long total = (long long)rows * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / per_row), c = (int)(i % per_row) * 8;
+    const uint4 u = *(const uint4*)(x + (size_t)tokidx[row] * d + c);
+    const uint16_t* b = (const uint16_t*)&u;
+    uint4 o;
+    __half2* oh = (__half2*)&o;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float f0 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j]), -65504.f), 65504.f);
+      float f1 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j + 1]), -65504.f), 65504.f);
+      oh[j] = __floats2half2_rn(f0, f1);
+    }
+    *(uint4*)(xs + (size_t)row * d + c) = o;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
+  k_combine<float><<<T, 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
+  k_combine<__half><<<T, 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0,
+                                       (__nv_bfloat16*)out_bf16);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
+                              __half* x_sorted, cudaStream_t st) {
+  long long total = (long long)rows * (d / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  k_gather_f16<<<blocks, 256, 0, st>>>((const uint16_t*)x_bf16, tokidx, rows, d, x_sorted);
+  return cudaGetLastError();
+}
+
+}  // namespace b200moe

@@ -1,0 +1,64 @@
+// kernels.h -- internal launch interface between the C-ABI layer (api.cu) and the kernel
+// translation units. Every launcher enqueues on `st` and returns the CUDA launch status;
+// none synchronises or allocates.
+#pragma once
+#include "common.cuh"
+
+namespace b200moe {
+
+// Source of one half (tile rows 0..63 or 64..127) of a repacked image, in the layout of
+// the reference's files.
+struct SrcTensor {
+  const uint8_t* codes = nullptr;   // q4cp: code bytes; GGUF: raw blocks
+  const uint8_t* scales = nullptr;  // q4cp only
+  long long rows_per_expert = 0;
+  long long row_off = 0;            // first row of this half inside an expert
+  long long scale_stride = 0;       // q4cp: bytes per scale record
+};
+
+// ---- repack.cu ----
+cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
+                          int first_expert, cudaStream_t st);
+cudaError_t launch_dequant_rows(const Image& img, int expert, int row0, int nrows, int mid_rows,
+                                float* out, cudaStream_t st);
+
+// ---- route.cu ----
+struct RouteBuffers {
+  int32_t* topids;   // [T][16]
+  float* topw;       // [T][16]
+  int32_t* tokidx;   // [rows]  rows = T*k (+T with a shared expert)
+  float* pw;         // [rows]
+  int32_t* eoff;     // [E+1]
+  int32_t* pairids;  // [T*k]
+  int32_t* blockcnt; // [nblocks][E] scratch
+  Run* runs;         // [E+1] active experts in ascending id (+ the shared expert last)
+  int32_t* n_runs;   // [2]: routed runs, 1 (the shared run sits at runs[kMaxExperts])
+  Tile* tiles;       // grouped GEMM work list, large tiles first
+  Tile* tiles_sh;    // work list of the shared expert (all T tokens)
+  int32_t* n_tiles;  // [2]: routed, shared
+  float* sgate;      // [T] sigmoid gate of the shared expert
+};
+cudaError_t launch_router_topk(const float* logits, int T, int E, int k, int32_t* ids, float* w,
+                               int stride, cudaStream_t st);
+cudaError_t launch_route(const RouteBuffers& rb, const int32_t* ids, const float* w, int stride,
+                         int T, int k, int E, int tile_cap, cudaStream_t st, int* launches);
+cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, int T, int d,
+                               int k, const RouteBuffers& rb, cudaStream_t st);
+
+// ---- expert_simt.cu ----
+cudaError_t launch_up_simt(const Image& img, const void* x_bf16, int d, int mid,
+                           const int32_t* tokidx, const Run* runs, const int32_t* n_runs,
+                           int max_runs, float* hid_f32, cudaStream_t st);
+cudaError_t launch_down_simt(const Image& img, const float* hid_f32, int d, int mid, const Run* runs,
+                             const int32_t* n_runs, int max_runs, float* pairs_f32,
+                             cudaStream_t st);
+
+// ---- combine.cu ----
+cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);
+cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);
+cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
+                              __half* x_sorted, cudaStream_t st);
+
+}  // namespace b200moe

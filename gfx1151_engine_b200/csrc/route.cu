@@ -1,0 +1,277 @@
+// route.cu -- router top-k and the expert bucketing of (token, slot) pairs.
+//
+// Semantics follow the reference:
+//   * probabilities as its CPU path forms them (src/ref.cpp:574-582): exp in double of
+//     (logit - max), rounded to float, summed in double in index order, divided in
+//     double, rounded to float; selection of the k largest, descending, ties to the lowest
+//     expert id (the rule of its GPU router, src/gpu/parts/20_kernels_gemv.inc:1488-1494);
+//     weights p / sum(selected p) with the sum taken in rank order (src/ref.cpp:587-588, 606).
+//   * bucketing = stable sort of pair index p = t*k + s by expert
+//     (src/gpu/parts/10_ple_io.inc:844-853; CPU twin src/gpu/parts/40_model.inc:4171-4183),
+//     eoff filled for empty experts too, pairids[t*k + rank] with rank = number of the
+//     token's experts with a smaller id (src/gpu/parts/10_ple_io.inc:802-806).
+// Everything here is integer/bookkeeping work and deterministic: no atomics on global
+// memory, no dependence on block scheduling order.
+#include "kernels.h"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int kRouterWarps = 8;
+constexpr int kChunk = 512;  // pairs handled by one single-warp block of the bucketing kernels
+
+__device__ __forceinline__ double shfl_double(double v, int src) {
+  int lo = __double2loint(v), hi = __double2hiint(v);
+  lo = __shfl_sync(0xffffffffu, lo, src);
+  hi = __shfl_sync(0xffffffffu, hi, src);
+  return __hiloint2double(hi, lo);
+}
+
+// One warp per token, E <= 512: lane holds experts lane, lane+32, ...
+__global__ void __launch_bounds__(kRouterWarps * 32)
+k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __restrict__ ids,
+              float* __restrict__ w, int stride) {
+  __shared__ float s_p[kRouterWarps][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouterWarps + warp;
+  if (t >= T) return;
+  const float* lg = logits + (size_t)t * E;
+  float v[16];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    int e = j * 32 + lane;
+    v[j] = e < E ? lg[e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const double dmx = (double)mx;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    int e = j * 32 + lane;
+    float p = e < E ? (float)exp((double)v[j] - dmx) : 0.f;
+    if (e < E) s_p[warp][e] = p;
+    v[j] = p;
+  }
+  __syncwarp();
+  double se = 0;
+  if (lane == 0)
+    for (int i = 0; i < E; i++) se += (double)s_p[warp][i];  // index order, as the reference sums
+  se = shfl_double(se, 0);
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    int e = j * 32 + lane;
+    v[j] = e < E ? (float)((double)v[j] / se) : -1.f;
+  }
+  int my_id = 0;
+  float my_p = 0.f;
+  double kept = 0;
+  for (int r = 0; r < k; r++) {
+    float bv = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+      if (v[j] > bv) {
+        bv = v[j];
+        bi = j * 32 + lane;
+      }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+      if (j == (bi >> 5) && lane == (bi & 31)) v[j] = -1.f;
+    if (lane == r) {
+      my_id = bi;
+      my_p = bv;
+    }
+    kept += (double)bv;
+  }
+  for (int i = lane; i < stride; i += 32) {
+    // lanes >= k hold zeros; stride > 32 is padded with zeros as well
+    bool valid = i < k && i < 32;
+    ids[(size_t)t * stride + i] = valid ? my_id : 0;
+    w[(size_t)t * stride + i] = valid ? (float)((double)my_p / kept) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+k_route_count(const int32_t* __restrict__ ids, int stride, int pairs, int k, int E,
+              int32_t* __restrict__ blockcnt) {
+  __shared__ int hist[kMaxExperts];
+  const int lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) hist[e] = 0;
+  __syncwarp();
+  const int base = blockIdx.x * kChunk;
+  for (int it = 0; it < kChunk / 32; it++) {
+    int p = base + it * 32 + lane;
+    if (p < pairs) atomicAdd(&hist[ids[(size_t)(p / k) * stride + p % k]], 1);
+  }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) blockcnt[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+// One block of 512 threads: per-expert exclusive prefix over the chunk counts, expert
+// offsets, the list of non-empty experts and the grouped-GEMM tile list (full tiles first,
+// then the ragged ones in descending size so that a static round-robin stays balanced).
+__global__ void __launch_bounds__(kMaxExperts)
+k_route_scan(int32_t* __restrict__ blockcnt, int nblk, int E, int pairs, int T, int tile_cap,
+             int32_t* __restrict__ eoff, Run* __restrict__ runs, int32_t* __restrict__ n_runs,
+             Tile* __restrict__ tiles, Tile* __restrict__ tiles_sh, int32_t* __restrict__ n_tiles) {
+  __shared__ int s_a[kMaxExperts], s_b[kMaxExperts], s_c[kMaxExperts];
+  const int e = threadIdx.x;
+  int cnt = 0;
+  if (e < E) {
+    for (int b = 0; b < nblk; b++) {
+      int c = blockcnt[(size_t)b * E + e];
+      blockcnt[(size_t)b * E + e] = cnt;
+      cnt += c;
+    }
+  }
+  // three inclusive scans side by side: counts, non-empty flags, full tiles
+  const int nfull = cnt / tile_cap, part = cnt % tile_cap;
+  s_a[e] = cnt;
+  s_b[e] = cnt > 0;
+  s_c[e] = nfull;
+  __syncthreads();
+  for (int o = 1; o < kMaxExperts; o <<= 1) {
+    int a = e >= o ? s_a[e - o] : 0, b = e >= o ? s_b[e - o] : 0, c = e >= o ? s_c[e - o] : 0;
+    __syncthreads();
+    s_a[e] += a;
+    s_b[e] += b;
+    s_c[e] += c;
+    __syncthreads();
+  }
+  const int first = s_a[e] - cnt;
+  const int total_full = s_c[kMaxExperts - 1];
+  if (e < E) eoff[e] = first;
+  if (e == 0) {
+    eoff[E] = pairs;
+    n_runs[0] = s_b[kMaxExperts - 1];
+    n_runs[1] = 1;  // the shared expert's run, kept at runs[kMaxExperts]
+    runs[kMaxExperts] = Run{0, pairs, T};
+  }
+  if (cnt > 0) runs[s_b[e] - 1] = Run{e, first, cnt};
+  const int full0 = s_c[e] - nfull;
+  for (int j = 0; j < nfull; j++) tiles[full0 + j] = Tile{e, first + j * tile_cap, tile_cap};
+  __syncthreads();
+  // rank of the ragged tile among all ragged tiles: larger first, ties to the lower id
+  s_a[e] = part;
+  __syncthreads();
+  int rank = 0, nparts = 0;
+  for (int o = 0; o < kMaxExperts; o++) {
+    int p = s_a[o];
+    nparts += p > 0;
+    rank += (p > part) || (p == part && o < e);
+  }
+  if (part > 0) tiles[total_full + rank] = Tile{e, first + nfull * tile_cap, part};
+  // tiles of the shared expert: all T tokens in token order, rows behind the routed ones
+  const int nsh = (T + tile_cap - 1) / tile_cap;
+  for (int j = e; j < nsh; j += kMaxExperts)
+    tiles_sh[j] = Tile{0, pairs + j * tile_cap, min(tile_cap, T - j * tile_cap)};
+  if (e == 0) {
+    n_tiles[0] = total_full + nparts;
+    n_tiles[1] = nsh;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+k_route_place(const int32_t* __restrict__ ids, const float* __restrict__ w, int stride, int pairs,
+              int k, int E, const int32_t* __restrict__ blockcnt, const int32_t* __restrict__ eoff,
+              int32_t* __restrict__ tokidx, float* __restrict__ pw, int32_t* __restrict__ pairids) {
+  __shared__ int cursor[kMaxExperts];
+  const int lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) cursor[e] = eoff[e] + blockcnt[(size_t)blockIdx.x * E + e];
+  __syncwarp();
+  const int base = blockIdx.x * kChunk;
+  for (int it = 0; it < kChunk / 32; it++) {
+    const int p = base + it * 32 + lane;
+    const bool live = p < pairs;
+    const unsigned act = __ballot_sync(0xffffffffu, live);
+    if (live) {
+      const int t = p / k, s = p % k;
+      const int e = ids[(size_t)t * stride + s];
+      const unsigned same = __match_any_sync(act, e);
+      const int leader = __ffs(same) - 1;
+      int start = 0;
+      if (lane == leader) {
+        start = cursor[e];
+        cursor[e] = start + __popc(same);
+      }
+      start = __shfl_sync(same, start, leader);
+      const int row = start + __popc(same & ((1u << lane) - 1u));
+      tokidx[row] = t;
+      pw[row] = w[(size_t)t * stride + s];
+      int rank = 0;
+      for (int q = 0; q < k; q++) rank += ids[(size_t)t * stride + q] < e;
+      pairids[(size_t)t * k + rank] = row;
+    }
+    __syncwarp();
+  }
+}
+
+// Scalar sigmoid gate of the shared expert (src/ref.cpp:623-626, 635): one warp per token.
+// Also appends the shared expert's rows (token order) behind the routed rows.
+__global__ void __launch_bounds__(256)
+k_shared_gate(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gw, int T, int d, int k,
+              int32_t* __restrict__ tokidx, float* __restrict__ pw, float* __restrict__ sgate) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= T) return;
+  double a = 0;
+  for (int c = lane; c < d; c += 32)
+    a += (double)bf16_bits_to_f32(gw[c]) * (double)bf16_bits_to_f32(x[(size_t)t * d + c]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    int lo = __shfl_xor_sync(0xffffffffu, __double2loint(a), o);
+    int hi = __shfl_xor_sync(0xffffffffu, __double2hiint(a), o);
+    a += __hiloint2double(hi, lo);
+  }
+  if (lane == 0) {
+    float g = sigmoid_f32((float)a);
+    sgate[t] = g;
+    tokidx[(size_t)T * k + t] = t;
+    pw[(size_t)T * k + t] = g;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_router_topk(const float* logits, int T, int E, int k, int32_t* ids, float* w,
+                               int stride, cudaStream_t st) {
+  k_router_topk<<<(T + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, 0, st>>>(
+      logits, T, E, k, ids, w, stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_route(const RouteBuffers& rb, const int32_t* ids, const float* w, int stride,
+                         int T, int k, int E, int tile_cap, cudaStream_t st, int* launches) {
+  const int pairs = T * k;
+  const int nblk = (pairs + kChunk - 1) / kChunk;
+  k_route_count<<<nblk, 32, 0, st>>>(ids, stride, pairs, k, E, rb.blockcnt);
+  k_route_scan<<<1, kMaxExperts, 0, st>>>(rb.blockcnt, nblk, E, pairs, T, tile_cap, rb.eoff, rb.runs,
+                                           rb.n_runs, rb.tiles, rb.tiles_sh, rb.n_tiles);
+  k_route_place<<<nblk, 32, 0, st>>>(ids, w, stride, pairs, k, E, rb.blockcnt, rb.eoff, rb.tokidx,
+                                     rb.pw, rb.pairids);
+  if (launches) *launches += 3;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, int T, int d, int k,
+                               const RouteBuffers& rb, cudaStream_t st) {
+  k_shared_gate<<<(T + 7) / 8, 256, 0, st>>>((const uint16_t*)x_bf16, gate_w_bf16, T, d, k,
+                                             rb.tokidx, rb.pw, rb.sgate);
+  return cudaGetLastError();
+}
+
+int route_chunk() { return kChunk; }
+
+}  // namespace b200moe

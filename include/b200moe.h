@@ -1,0 +1,158 @@
+/* b200moe.h -- C ABI of the B200 (sm_100a) routed-expert MoE FFN operator.
+ *
+ * This library stands behind the MoE call sites of gfx1151-engine's layer loop. The
+ * engine has no plugin interface: its operator surface is a set of GpuModel member
+ * functions in one translation unit. Each entry point below names the reference
+ * function (path within the reference project, file:line) whose job it takes over.
+ *
+ * Conventions
+ *   - Every function returns an int status (B200MOE_OK == 0). Nothing aborts, throws
+ *     across the boundary or falls back to the CPU; an unsupported request is an error.
+ *   - Pointers named *_dev are device pointers on the handle's GPU; *_host are host
+ *     pointers; `src` pointers of the loaders may be either.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ *   - A handle belongs to one GPU and one host thread at a time.
+ *   - Hidden states are bf16 row-major [T][d_model]; router logits fp32 [T][experts];
+ *     top-k id / weight rows carry `stride` entries of which the first topk are valid
+ *     (the engine uses stride 16, src/gpu/parts/40_model.inc:4116-4136).
+ */
+#ifndef B200MOE_H
+#define B200MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200moe_ctx* b200moe_handle;
+
+enum {
+  B200MOE_OK = 0,
+  B200MOE_ERR_BAD_ARG = 1,      /* null pointer, negative size, T > max_tokens ... */
+  B200MOE_ERR_UNSUPPORTED = 2,  /* shape / format outside what the kernels implement */
+  B200MOE_ERR_CUDA = 3,         /* a CUDA runtime or driver call failed */
+  B200MOE_ERR_NOT_LOADED = 4,   /* forward before the layer's weights were loaded */
+  B200MOE_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up */
+  B200MOE_ERR_NCCL = 6,
+  B200MOE_ERR_ALLOC = 7
+};
+
+/* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
+enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12 };
+
+/* Which expert GEMM implementation forward uses for T > decode_max_tokens. */
+enum {
+  B200MOE_GEMM_AUTO = 0,   /* tcgen05 grouped GEMM */
+  B200MOE_GEMM_SIMT = 1,   /* fp32 CUDA-core kernels (the decode path, at any T); for A/B checks */
+  B200MOE_GEMM_TC = 2      /* tcgen05 grouped GEMM even for T <= decode_max_tokens */
+};
+
+typedef struct {
+  int32_t experts;        /* routed experts E (<= 512, as in k_router_topk, src/gpu/parts/20_kernels_gemv.inc:1443) */
+  int32_t topk;           /* experts per token k (<= 16) */
+  int32_t d_model;        /* multiple of 128 */
+  int32_t d_mid;          /* expert intermediate size, multiple of 64 */
+  int32_t n_layers;       /* layers sharing this handle's workspaces */
+  int32_t max_tokens;     /* largest T of any forward call (the engine's maxbatch_cap, src/gpu/parts/40_model.inc:611-655) */
+  int32_t has_shared;     /* 1: an always-on shared expert with a sigmoid scalar gate exists */
+  int32_t device;         /* CUDA device ordinal */
+  int32_t gemm_impl;      /* B200MOE_GEMM_* */
+  int32_t decode_max_tokens; /* T up to which the GEMV path runs; 0 = default 16 (moe_naive_max, src/gpu/parts/40_model.inc:1963-1966) */
+  int32_t ep_rank;        /* expert-parallel rank and size; size 1 = single GPU */
+  int32_t ep_size;
+  int32_t reserved[4];
+} b200moe_config;
+
+/* Replaces: GpuModel construction of the MoE workspaces (src/gpu/parts/40_model.inc:611-655)
+ * and GpuMoeRouting::init (src/gpu/parts/10_ple_io.inc:833-843). Allocates every buffer a
+ * later forward needs; forward itself never allocates. */
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out);
+int b200moe_destroy(b200moe_handle h);
+
+/* Human-readable text for a status code / the last failure recorded on the handle
+ * (replaces the message printed by CK(), src/gpu/parts/00_platform.inc:59-67). */
+const char* b200moe_status_string(int status);
+const char* b200moe_last_error(b200moe_handle h);
+
+/* Replaces: wview() over the hgn q4cp expert tensors (src/gpu/parts/30_host_util.inc:875-899;
+ * blob layout src/hgn.h:5-9, 219-238): gate_up is the fused [E*2*mid, d] tensor, down is
+ * [E*d, mid]; each blob = [16 x f32 codebook][codes][per-row fp16 scale records].
+ * One-time repack into library-owned HBM tiles; the source may be freed on return.
+ * With expert parallelism every rank passes the full tensors and keeps its own experts. */
+int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size_t gate_up_bytes,
+                      const void* down_src, size_t down_bytes);
+
+/* Replaces: gguf_experts_open / GgExperts (src/gpu/parts/30_host_util.inc:348-452): raw GGUF
+ * blocks of blk.L.ffn_{gate,up,down}_exps.weight, expert e's rows at e*rows*row_bytes
+ * (src/gguf.h:3-11). type_gu must be Q4_K and type_dn Q5_1. */
+int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
+                      const void* down_src, int type_gu, int type_dn);
+
+/* Replaces: the shared-expert weight views used by moe_b_shared(_ey)
+ * (src/gpu/parts/40_model.inc:4689-4711) and ref.cpp:623-636: three q4cp tensors
+ * [mid,d], [mid,d], [d,mid] and the bf16 [d] weight of the scalar sigmoid gate. */
+int b200moe_load_shared_q4cp(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
+                             const void* down_src, const void* gate_w_bf16_src);
+
+/* Replaces: GpuModel::moe_b from the router top-k on (src/gpu/parts/40_model.inc:4018-4157) and
+ * GpuModel::moe (:1806-1861); oracle Model::moe, src/ref.cpp:574-637. Asynchronous on
+ * `stream`; no allocation, no host synchronisation. out is fully overwritten. */
+int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
+                    const float* logits_dev, void* out_bf16_dev, void* stream);
+
+/* Replaces: the seam below the router, moe_q4w_run (src/gpu/parts/40_model.inc:1736-1804) and
+ * moe_gguf (:1664-1714): the caller supplies top-k ids and weights (descending probability). */
+int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
+                           const int32_t* topids_dev, const float* topw_dev, int stride,
+                           void* out_bf16_dev, void* stream);
+
+/* The same call for callers whose buffers live in host memory (pinned or pageable):
+ * copies x and logits to the GPU, runs b200moe_forward, copies out back and waits.
+ * This is the end-to-end path the benchmark times against the CPU reference. */
+int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, int T,
+                         const float* logits_host, void* out_bf16_host, void* stream);
+
+/* Replaces: router_topk_b / k_router_topk_w32 (src/gpu/parts/40_model.inc:4011-4017,
+ * src/gpu/parts/20_kernels_gemv.inc:1495-1562); arithmetic of src/ref.cpp:574-588.
+ * Order: descending probability, ties to the lowest expert id. */
+int b200moe_router_topk(b200moe_handle h, const float* logits_dev, int T, int32_t* topids_dev,
+                        float* topw_dev, int stride, void* stream);
+
+/* Replaces: GpuMoeRouting::run + k_moe_tiles (src/gpu/parts/10_ple_io.inc:784-861). Builds, in
+ * the handle's workspace, the stable (expert, pair) permutation, expert offsets, reduce
+ * order and tile list for the given selection. */
+int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw_dev, int stride,
+                  int T, void* stream);
+
+/* Reads back what the last forward / route call left in the workspace (host buffers; any may
+ * be NULL): tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k] as defined by
+ * src/gpu/parts/10_ple_io.inc:790-811, and topids/topw rows of 16. Synchronises the device. */
+int b200moe_debug_get_routing(b200moe_handle h, int T, int32_t* topids_host, float* topw_host,
+                              int32_t* tokidx_host, float* pw_host, int32_t* eoff_host,
+                              int32_t* pairids_host);
+
+/* Dequantises rows of a loaded tensor from the repacked image into fp32 (device buffer
+ * [nrows][cols]); bit-identical to q4cp_row (src/hgn.h:249-261) / gguf::dequant_row
+ * (src/gguf.h:339-443). which: 0 gate_up (rows 0..2*mid-1 of an expert: gate then up),
+ * 1 down (rows 0..d-1), 2 shared gate_up, 3 shared down. */
+int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int row0, int nrows,
+                         float* out_dev, void* stream);
+
+/* Waits for `stream` and reports B200MOE_ERR_DEVICE_TIMEOUT if a kernel of an earlier
+ * forward gave up a bounded wait (replaces the implicit check of CK() after
+ * hipStreamSynchronize in the reference's layer loop). Clears the recorded condition. */
+int b200moe_synchronize(b200moe_handle h, void* stream);
+
+/* Number of kernels this library launched since the handle was created (the benchmark
+ * reports the difference across its timed region). */
+int64_t b200moe_launch_count(b200moe_handle h);
+
+/* Library build information: "b200moe <version> sm_100a". */
+const char* b200moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H */

@@ -1,0 +1,301 @@
+"""GPU: parity of the CUDA path (through the C ABI) with the CPU oracle and the golden
+vectors of the reference. Integer results are compared bit for bit; the layer output
+within max-abs 2e-2 and mean-rel 1e-3 after rounding both sides to bf16."""
+import dataclasses
+import os
+
+import numpy as np
+import pytest
+
+import gfx1151_engine_b200 as pkg
+import oracle
+from gfx1151_engine_b200 import synth
+from helpers import (assert_output_close, bf16_out_to_f32, bf16_tensor, crc, dev_bytes, output_errors)
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def make_op(torch, spec, max_tokens, impl=pkg.GEMM_AUTO, layer=None, **kw):
+    op = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, max_tokens, has_shared=spec.shared,
+                         gemm_impl=impl, **kw)
+    if layer is not None:
+        if spec.fmt == "q4cp":
+            op.load_q4cp(0, dev_bytes(torch, layer["gate_up"]), dev_bytes(torch, layer["down"]))
+        else:
+            op.load_gguf(0, dev_bytes(torch, layer["gate"]), dev_bytes(torch, layer["up"]),
+                         dev_bytes(torch, layer["down"]))
+        if spec.shared:
+            op.load_shared_q4cp(0, dev_bytes(torch, layer["sh_gate"]), dev_bytes(torch, layer["sh_up"]),
+                                dev_bytes(torch, layer["sh_down"]), dev_bytes(torch, layer["sh_gate_w"]))
+    return op
+
+
+def run_layer(torch, op, spec, xb, logits):
+    T = xb.shape[0]
+    x = bf16_tensor(torch, xb, (T, spec.d))
+    lg = torch.from_numpy(np.ascontiguousarray(logits, np.float32)).cuda()
+    out = torch.full((T, spec.d), float("nan"), dtype=torch.bfloat16, device="cuda")  # NaN-prefilled
+    op.moe_b(0, x, lg, out)
+    op.synchronize()
+    return bf16_out_to_f32(torch, out)
+
+
+# ---------------------------------------------------------------- dequantisation --------
+@pytest.mark.parametrize("book", ["linear", "random"])
+def test_dequant_q4cp_bit_exact(cuda, book):
+    torch = cuda
+    spec = synth.LayerSpec(experts=3, topk=2, d=256, mid=128, shared=True, book=book)
+    layer = synth.make_layer(spec, seed=31)
+    op = make_op(torch, spec, 4, layer=layer)
+    for e in range(spec.experts):
+        out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 0, e, 0, 2 * spec.mid, out)
+        want = oracle.q4cp_rows(layer["gate_up"], spec.experts * 2 * spec.mid, spec.d, e * 2 * spec.mid, 2 * spec.mid)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+        out = torch.empty((spec.d, spec.mid), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 1, e, 0, spec.d, out)
+        want = oracle.q4cp_rows(layer["down"], spec.experts * spec.d, spec.mid, e * spec.d, spec.d)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+    # shared expert: gate rows then up rows, separate code books
+    out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+    op.dequant_rows(0, 2, 0, 0, 2 * spec.mid, out)
+    want = np.concatenate([oracle.q4cp_rows(layer["sh_gate"], spec.mid, spec.d, 0, spec.mid),
+                           oracle.q4cp_rows(layer["sh_up"], spec.mid, spec.d, 0, spec.mid)])
+    assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+    # a ragged row range
+    out = torch.empty((5, spec.mid), dtype=torch.float32, device="cuda")
+    op.dequant_rows(0, 3, 0, 7, 5, out)
+    assert np.array_equal(bits(out.cpu().numpy()), bits(oracle.q4cp_rows(layer["sh_down"], spec.d, spec.mid, 7, 5)))
+
+
+def test_dequant_gguf_bit_exact(cuda):
+    torch = cuda
+    spec = synth.LayerSpec(experts=2, topk=1, d=512, mid=128, fmt="gguf")
+    layer = synth.make_layer(spec, seed=32)
+    op = make_op(torch, spec, 4, impl=pkg.GEMM_SIMT, layer=layer)
+    for e in range(spec.experts):
+        out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 0, e, 0, 2 * spec.mid, out)
+        rb = spec.d // 256 * 144
+        g = oracle.gguf_rows(12, layer["gate"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        u = oracle.gguf_rows(12, layer["up"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(np.concatenate([g, u])))
+        out = torch.empty((spec.d, spec.mid), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 1, e, 0, spec.d, out)
+        rb = spec.mid // 32 * 24
+        dn = oracle.gguf_rows(7, layer["down"][e * spec.d * rb:(e + 1) * spec.d * rb], spec.mid, spec.d)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(dn))
+
+
+# ---------------------------------------------------------------- routing ----------------
+@pytest.mark.parametrize("T,E,k,zipf", [(1, 512, 10, False), (5, 512, 10, False), (777, 512, 10, True),
+                                        (16, 64, 8, False), (300, 8, 2, True), (4096, 512, 10, True),
+                                        (33, 100, 16, False)])
+def test_router_and_permutation_bit_exact(cuda, T, E, k, zipf):
+    torch = cuda
+    logits = synth.make_logits(synth.rng_for(40 + T, 1), T, E, zipf=zipf)
+    ids_o, w_o, probs = oracle.router_topk(logits, k, want_probs=True)
+    assert oracle.count_topk_ties(probs, k) == 0, "seeded input has a probability tie; pick another seed"
+    op = pkg.MoeOperator(E, k, 128, 64, T)
+    lg = torch.from_numpy(logits).cuda()
+    ids = torch.full((T, 16), -1, dtype=torch.int32, device="cuda")
+    w = torch.full((T, 16), -1.0, dtype=torch.float32, device="cuda")
+    op.router_topk_b(lg, ids, w)
+    op.route(ids, w, T)
+    _, _, tok, pw, eoff, pid = op.get_routing(T)
+    ids, w = ids.cpu().numpy(), w.cpu().numpy()
+    assert np.array_equal(ids[:, :k], ids_o[:, :k])                      # top-k ids: bit-exact
+    assert (ids[:, k:] == 0).all() and (w[:, k:] == 0).all()             # padding lanes cleared
+    assert np.abs(w[:, :k] - w_o[:, :k]).max() <= 1e-6                   # weights: 1e-6 (fp64 sum order)
+    tok_o, pw_o, eoff_o, pid_o = oracle.route(ids, w, k, E)
+    assert np.array_equal(tok, tok_o) and np.array_equal(eoff, eoff_o) and np.array_equal(pid, pid_o)
+    assert np.array_equal(bits(pw), bits(pw_o))
+
+
+def test_router_ties_go_to_lowest_index(cuda):
+    torch = cuda
+    E, k = 64, 4
+    logits = np.zeros((2, E), np.float32)       # all equal: expect experts 0..k-1
+    logits[1, [7, 3, 50]] = 1.0                 # three equal leaders, then index 0
+    op = pkg.MoeOperator(E, k, 128, 64, 2)
+    ids = torch.zeros((2, 16), dtype=torch.int32, device="cuda")
+    w = torch.zeros((2, 16), dtype=torch.float32, device="cuda")
+    op.router_topk_b(torch.from_numpy(logits).cuda(), ids, w)
+    ids = ids.cpu().numpy()
+    assert ids[0, :k].tolist() == [0, 1, 2, 3] and ids[1, :k].tolist() == [3, 7, 50, 0]
+
+
+# ---------------------------------------------------------------- whole layer -----------
+def ref_logits(layer, x):
+    """float(sum in double) of bf16 router weight times x, as the reference's matvec forms them."""
+    rw = synth.bf16_bits_to_f32(layer["router_w"]).astype(np.float64)
+    return (x.astype(np.float64) @ rw.T).astype(np.float32)
+
+
+@pytest.mark.parametrize("impl", [pkg.GEMM_SIMT, pkg.GEMM_TC])
+def test_config1_against_reference_golden(cuda, golden_dir, impl):
+    """Configuration 1: the golden output comes from the reference's unmodified Model::moe."""
+    torch = cuda
+    g = np.load(os.path.join(golden_dir, "moe_config1.npz"))
+    spec = synth.CONFIG1
+    layer = synth.make_layer(spec, seed=0)
+    xb = synth.make_x(synth.rng_for(0, 9), 16, spec.d)
+    assert crc(xb) == g["crc_x"]
+    x = synth.bf16_bits_to_f32(xb)
+    y_o, ids_o, w_o = oracle.moe_forward(spec, layer, x)
+    assert np.array_equal(bits(y_o), bits(g["y"]))
+    logits = ref_logits(layer, x)
+    op = make_op(torch, spec, 16, impl=impl, layer=layer)
+    y = run_layer(torch, op, spec, xb, logits)
+    ids = op.get_routing(16)[0]
+    assert np.array_equal(ids[:, :spec.topk], ids_o[:, :spec.topk])
+    assert_output_close(y, g["y"], "config 1 impl %d" % impl)
+
+
+@pytest.mark.parametrize("impl", [pkg.GEMM_SIMT, pkg.GEMM_TC])
+def test_tiny_layer_with_shared_expert_golden(cuda, golden_dir, impl):
+    torch = cuda
+    g = np.load(os.path.join(golden_dir, "moe_tiny.npz"))
+    spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=64, shared=True, router=True, book="random")
+    layer = synth.make_layer(spec, seed=3)
+    xb = synth.make_x(synth.rng_for(3, 9), 5, spec.d)
+    x = synth.bf16_bits_to_f32(xb)
+    op = make_op(torch, spec, 8, impl=impl, layer=layer)
+    y = run_layer(torch, op, spec, xb, ref_logits(layer, x))
+    assert_output_close(y, g["y"], "tiny layer impl %d" % impl)
+
+
+@pytest.mark.parametrize("impl", [pkg.GEMM_SIMT, pkg.GEMM_AUTO])
+def test_edge_expert_sizes(cuda, impl):
+    """Expert loads {0, 1, 63, 64, 65, 2} and a 193-row expert (one row over the GEMM tile),
+    as the reference's kernel test uses (tools/ktest.cu:2588-2768)."""
+    torch = cuda
+    counts = [0, 1, 63, 64, 65, 2, 193, 0]
+    spec = synth.LayerSpec(experts=8, topk=1, d=384, mid=256, book="random")
+    layer = synth.make_layer(spec, seed=44)
+    T = sum(counts)
+    owner = np.repeat(np.arange(8), counts)
+    synth.rng_for(44, 5).shuffle(owner)
+    logits = np.zeros((T, 8), np.float32)
+    logits[np.arange(T), owner] = 9.0
+    xb = synth.make_x(synth.rng_for(44, 9), T, spec.d)
+    y_o, ids_o, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+    op = make_op(torch, spec, T, impl=impl, layer=layer)
+    y = run_layer(torch, op, spec, xb, logits)
+    _, _, tok, pw, eoff, pid = op.get_routing(T)
+    assert np.diff(eoff).tolist() == counts
+    assert_output_close(y, y_o, "edge sizes impl %d" % impl)
+
+
+@pytest.mark.parametrize("T", [1, 5, 16])
+def test_decode_and_verify_with_shared_expert(cuda, T):
+    """Decode (T=1) and speculative verify (T=5) through the GEMV path, shared expert on."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=64, topk=10, d=512, mid=256, shared=True)
+    layer = synth.make_layer(spec, seed=50)
+    logits = synth.make_logits(synth.rng_for(50, T), T, spec.experts)
+    xb = synth.make_x(synth.rng_for(50, 9), T, spec.d)
+    y_o, ids_o, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+    op = make_op(torch, spec, 16, layer=layer)
+    y = run_layer(torch, op, spec, xb, logits)
+    assert np.array_equal(op.get_routing(T)[0][:, :spec.topk], ids_o[:, :spec.topk])
+    max_abs, mean_rel = assert_output_close(y, y_o, "decode T=%d" % T)
+    # the fp32 path is far inside the tolerance: errors come from bf16 output rounding only
+    assert mean_rel < 1e-4
+
+
+def test_prefill_zipf_tc_vs_oracle_and_simt(cuda):
+    """A skewed prefill chunk: tensor-core path against the fp32 path on every token and
+    against the CPU oracle on a sample; output fully written; bitwise repeatable."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=32, topk=4, d=1024, mid=512)
+    layer = synth.make_layer(spec, seed=60)
+    T = 1500
+    logits = synth.make_logits(synth.rng_for(60, 1), T, spec.experts, zipf=True)
+    xb = synth.make_x(synth.rng_for(60, 9), T, spec.d)
+    op_tc = make_op(torch, spec, T, impl=pkg.GEMM_AUTO, layer=layer)
+    op_simt = make_op(torch, spec, T, impl=pkg.GEMM_SIMT, layer=layer)
+    y_tc = run_layer(torch, op_tc, spec, xb, logits)
+    y_tc2 = run_layer(torch, op_tc, spec, xb, logits)
+    y_simt = run_layer(torch, op_simt, spec, xb, logits)
+    assert np.array_equal(bits(y_tc), bits(y_tc2)), "tensor-core path is not deterministic"
+    assert_output_close(y_tc, y_simt, "tc vs fp32 path")
+    sample = np.arange(0, T, 47)
+    y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb[sample]), logits=logits[sample])
+    assert_output_close(y_tc[sample], y_o, "tc vs oracle")
+    assert_output_close(y_simt[sample], y_o, "fp32 path vs oracle")
+
+
+def test_row_invariance(cuda):
+    """A token's result does not depend on what else is in the batch (reference:
+    tools/ktest.cu:920-923): rows of a 40-token call equal single-token calls bit for bit
+    on the fp32 path."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=16, topk=4, d=256, mid=128)
+    layer = synth.make_layer(spec, seed=70)
+    T = 40
+    logits = synth.make_logits(synth.rng_for(70, 1), T, spec.experts)
+    xb = synth.make_x(synth.rng_for(70, 9), T, spec.d)
+    op = make_op(torch, spec, T, impl=pkg.GEMM_SIMT, layer=layer)
+    y_all = run_layer(torch, op, spec, xb, logits)
+    for t in (0, 13, 39):
+        y_one = run_layer(torch, op, spec, xb[t:t + 1], logits[t:t + 1])
+        assert np.array_equal(bits(y_one[0]), bits(y_all[t]))
+
+
+def test_gguf_layer(cuda):
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=128, fmt="gguf")
+    layer = synth.make_layer(spec, seed=80)
+    for T in (3, 40):
+        logits = synth.make_logits(synth.rng_for(80, T), T, spec.experts)
+        xb = synth.make_x(synth.rng_for(80, 9), T, spec.d)
+        y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+        op = make_op(torch, spec, T, impl=pkg.GEMM_SIMT, layer=layer)
+        y = run_layer(torch, op, spec, xb, logits)
+        assert_output_close(y, y_o, "gguf T=%d" % T)
+
+
+def test_forward_routed_and_host_paths(cuda):
+    """The seam below the router (caller-supplied ids) and the host-buffer entry point give
+    the same bytes as the logits entry point."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=16, topk=4, d=256, mid=128)
+    layer = synth.make_layer(spec, seed=90)
+    T = 64
+    logits = synth.make_logits(synth.rng_for(90, 1), T, spec.experts)
+    xb = synth.make_x(synth.rng_for(90, 9), T, spec.d)
+    op = make_op(torch, spec, T, layer=layer)
+    y = run_layer(torch, op, spec, xb, logits)
+    ids, w = op.get_routing(T)[:2]
+    x = bf16_tensor(torch, xb, (T, spec.d))
+    out = torch.zeros((T, spec.d), dtype=torch.bfloat16, device="cuda")
+    op.moe_q4w_run(0, x, torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), out)
+    op.synchronize()
+    assert np.array_equal(bits(bf16_out_to_f32(torch, out)), bits(y))
+    out_h = np.zeros((T, spec.d), np.uint16)
+    op.moe_b_host(0, np.ascontiguousarray(xb), logits, out_h, T)
+    assert np.array_equal(bits(synth.bf16_bits_to_f32(out_h)), bits(y))
+
+
+def test_errors_are_status_codes(cuda):
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=128, mid=64)
+    op = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, 4)
+    x = torch.zeros((4, 128), dtype=torch.bfloat16, device="cuda")
+    lg = torch.zeros((4, 8), dtype=torch.float32, device="cuda")
+    with pytest.raises(pkg.B200MoeError) as e:
+        op.moe_b(0, x, lg, x)                       # weights not loaded
+    assert e.value.status == 4
+    with pytest.raises(pkg.B200MoeError) as e:
+        op.moe_b(0, x, lg, x, T=5)                  # T > max_tokens
+    assert e.value.status == 1
+    with pytest.raises(pkg.B200MoeError) as e:
+        op.load_q4cp(0, torch.zeros(100, dtype=torch.uint8, device="cuda"),
+                     torch.zeros(100, dtype=torch.uint8, device="cuda"))  # wrong blob size
+    assert e.value.status == 1
+    op.moe_b(0, x, lg, x, T=0)                      # empty batch is a no-op

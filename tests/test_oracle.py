@@ -1,0 +1,133 @@
+"""CPU: the restated oracle against the golden vectors made by the reference's own code,
+and (where the reference build is present) against that code directly."""
+import dataclasses
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from gfx1151_engine_b200 import synth
+from helpers import crc, layer_crc
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("cols", [64, 640])
+def test_q4cp_rows_golden(golden_dir, cols):
+    g = np.load(os.path.join(golden_dir, "q4cp_rows_%d.npz" % cols))
+    got = oracle.q4cp_rows(g["blob"], 6, cols, 0, 6)
+    assert np.array_equal(bits(got), bits(g["rows"]))
+    # a sub-range starts at the right row
+    assert np.array_equal(bits(oracle.q4cp_rows(g["blob"], 6, cols, 2, 3)), bits(g["rows"][2:5]))
+
+
+def test_gguf_rows_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "gguf_rows.npz"))
+    assert np.array_equal(bits(oracle.gguf_rows(12, g["q4k"], 512, 3)), bits(g["q4k_rows"]))
+    assert np.array_equal(bits(oracle.gguf_rows(7, g["q51"], 256, 3)), bits(g["q51_rows"]))
+
+
+def test_generators_reproduce_golden_inputs(golden_dir):
+    """The synthetic generator must give the bytes the golden outputs were made from."""
+    g = np.load(os.path.join(golden_dir, "moe_tiny.npz"))
+    spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=64, shared=True, router=True, book="random")
+    layer = synth.make_layer(spec, seed=3)
+    assert layer_crc(layer) == g["crc_layer"]
+    assert crc(synth.make_x(synth.rng_for(3, 9), 5, spec.d)) == g["crc_x"]
+
+
+def test_moe_tiny_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "moe_tiny.npz"))
+    spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=64, shared=True, router=True, book="random")
+    layer = synth.make_layer(spec, seed=3)
+    x = synth.bf16_bits_to_f32(synth.make_x(synth.rng_for(3, 9), 5, spec.d))
+    y, ids, w = oracle.moe_forward(spec, layer, x)
+    assert np.array_equal(bits(y), bits(g["y"]))
+    assert np.allclose(w[:, :2].sum(1), 1.0, atol=1e-6)
+
+
+def test_moe_config1_golden(golden_dir):
+    """Benchmark configuration 1 (d=2048, 64 experts, top-8, mid=512, 16 tokens, seed 0)."""
+    g = np.load(os.path.join(golden_dir, "moe_config1.npz"))
+    spec = synth.CONFIG1
+    layer = synth.make_layer(spec, seed=0)
+    assert layer_crc(layer, ("down", "gate_up", "router_w")) == g["crc_layer"]
+    xb = synth.make_x(synth.rng_for(0, 9), 16, spec.d)
+    assert crc(xb) == g["crc_x"]
+    y, ids, w = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb))
+    assert np.array_equal(bits(y), bits(g["y"]))
+
+
+def test_logits_given_equals_router_weight_path():
+    """Feeding the logits the router weight produces must not change anything."""
+    spec = synth.LayerSpec(experts=16, topk=4, d=128, mid=64, router=True)
+    layer = synth.make_layer(spec, seed=5)
+    xb = synth.make_x(synth.rng_for(5, 9), 7, spec.d)
+    x = synth.bf16_bits_to_f32(xb)
+    y0, ids0, w0 = oracle.moe_forward(spec, layer, x)
+    rw = synth.bf16_bits_to_f32(layer["router_w"]).astype(np.float64)
+    logits = (x.astype(np.float64) @ rw.T).astype(np.float32)
+    # reproduce the reference's sequential double accumulation exactly
+    for t in range(x.shape[0]):
+        for e in range(spec.experts):
+            a = 0.0
+            for c in range(spec.d):
+                a += float(rw[e, c]) * float(x[t, c])
+            logits[t, e] = np.float32(a)
+    y1, ids1, w1 = oracle.moe_forward(spec, layer, x, logits=logits)
+    assert np.array_equal(ids0, ids1) and np.array_equal(bits(y0), bits(y1))
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference build (oracle/_ref) not present")
+def test_against_reference_build():
+    spec = synth.LayerSpec(experts=8, topk=3, d=128, mid=64, shared=True, router=True, book="random")
+    layer = synth.make_layer(spec, seed=21)
+    x = synth.bf16_bits_to_f32(synth.make_x(synth.rng_for(21, 9), 6, spec.d))
+    yr = oracle.ref_moe_layer(spec, layer, x)
+    yo, _, _ = oracle.moe_forward(spec, layer, x)
+    assert np.array_equal(bits(yr), bits(yo))
+    blob = layer["down"]
+    a = oracle.q4cp_rows(blob, spec.experts * spec.d, spec.mid, 5, 9)
+    b = oracle.q4cp_rows(blob, spec.experts * spec.d, spec.mid, 5, 9, use_ref=True)
+    assert np.array_equal(bits(a), bits(b))
+
+
+def test_router_and_route_properties():
+    rng = synth.rng_for(7, 1)
+    T, E, k = 300, 64, 6
+    logits = synth.make_logits(rng, T, E, zipf=True)
+    ids, w, probs = oracle.router_topk(logits, k, want_probs=True)
+    assert oracle.count_topk_ties(probs, k) == 0
+    # descending probability, k distinct experts, weights normalised
+    p_sel = np.take_along_axis(probs, ids[:, :k], axis=1)
+    assert (np.diff(p_sel, axis=1) <= 0).all()
+    assert all(len(set(r[:k])) == k for r in ids)
+    assert np.allclose(w[:, :k].sum(1), 1, atol=1e-6)
+    tok, pw, eoff, pid = oracle.route(ids, w, k, E)
+    # eoff is the histogram's prefix sum; rows of one expert hold ascending tokens (stability)
+    hist = np.bincount(ids[:, :k].reshape(-1), minlength=E)
+    assert np.array_equal(np.diff(eoff), hist) and eoff[-1] == T * k
+    for e in range(E):
+        seg = tok[eoff[e]:eoff[e + 1]]
+        assert (np.diff(seg) > 0).all()
+    # pairids: the k rows of a token, in ascending expert order
+    row_expert = np.repeat(np.arange(E), hist)
+    for t in range(T):
+        rows = pid[t * k:(t + 1) * k]
+        assert (tok[rows] == t).all() and (np.diff(row_expert[rows]) > 0).all()
+    tl = oracle.tiles(eoff, 64)
+    assert tl[:, 2].sum() == T * k and (tl[:, 2] <= 64).all() and (tl[:, 2] > 0).all()
+
+
+def test_empty_and_single_token():
+    spec = synth.LayerSpec(experts=8, topk=2, d=128, mid=64)
+    layer = synth.make_layer(spec, seed=2)
+    lg = synth.make_logits(synth.rng_for(2, 3), 1, 8)
+    x = synth.bf16_bits_to_f32(synth.make_x(synth.rng_for(2, 9), 1, spec.d))
+    y, ids, w = oracle.moe_forward(spec, layer, x, logits=lg)
+    assert y.shape == (1, 128) and np.isfinite(y).all()
+    tok, pw, eoff, pid = oracle.route(np.zeros((0, 16), np.int32), np.zeros((0, 16), np.float32), 2, 8)
+    assert eoff.tolist() == [0] * 9
