@@ -1,0 +1,368 @@
+"""Benchmark of the routed-expert MoE FFN path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[2], "config 3"): one 512-expert top-10 q4cp MoE layer
+(d_model 4096, expert intermediate 1024, group 32, fp16 scales), a 16384-token prefill
+chunk per step and per GPU, bf16 activations ~ N(0,1), router logits ~ N(0,1) plus a
+per-expert Zipf(1.1) bias. Weights and inputs are synthetic (seeded); a step is one
+b200moe_forward call: router top-k, bucketing, activation gather, tcgen05 gate/up GEMM
++ SwiGLU, down GEMM, weighted combine.
+
+Prints ONE JSON line: value = tokens/s with inputs resident in HBM (CUDA events on the
+launching stream, max over ranks); e2e = the same call through b200moe_forward_host with
+pinned host buffers (host<->device copies inside the timed region); roofline = the gate/up
+GEMM kernel's algorithmic FLOP/s against the measured dense 16-bit peak; cpu_baseline =
+the CPU oracle timed on this host on a bounded token sample; decode = the T=1 / T=5 GEMV
+path (configs[1]) with rotated routings. `--impl reference` times the reference's own CPU
+code (oracle/_ref, built from the reference sources) instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+E, K_TOP, D, MID, T_CHUNK = 512, 10, 4096, 1024, 16384
+FLOP_PER_TOKEN = K_TOP * (2 * (2 * MID) * D + 2 * D * MID)          # 251,658,240
+FLOP_UP_PER_TOKEN = K_TOP * 2 * (2 * MID) * D                        # gate/up GEMM share
+BYTES_PER_EXPERT = 3 * MID * D * 9 // 16                             # 7,077,888 (0.5625 B / weight)
+WORKLOAD = "config3: 16384-token prefill, 512 experts top-10, d=4096, mid=1024, q4cp g32, Zipf(1.1) routing"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return float(j["bf16_tflops"]), float(j["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                pass
+        busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ synthetic layer on the GPU
+def q4cp_blob_device(torch, rows, cols, gen):
+    """A q4cp tensor blob built in device memory: linear symmetric code book, uniform codes,
+    fp16 scales |N(0, 0.02)| (no padding at these widths: the scale record is cols/16 bytes)."""
+    assert (cols // 32 * 2) % 16 == 0
+    ncode, nscale = rows * cols // 2, rows * (cols // 32)
+    blob = torch.empty(64 + ncode + nscale * 2, dtype=torch.uint8, device="cuda")
+    book = ((2.0 * torch.arange(16, dtype=torch.float32) - 15.0) / 15.0)
+    blob[:64] = book.view(torch.uint8).cuda()
+    step = 1 << 28
+    for o in range(0, ncode, step):
+        n = min(step, ncode - o)
+        blob[64 + o:64 + o + n] = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=gen)
+    sc = (torch.randn(nscale, device="cuda", generator=gen) * 0.02).abs().to(torch.float16)
+    blob[64 + ncode:] = sc.view(torch.uint8)
+    return blob
+
+
+def zipf_logits(torch, T, gen, seed):
+    from gfx1151_engine_b200 import synth
+    bias = synth.zipf_bias(synth.rng_for(seed, 77), E)
+    return (torch.randn(T, E, device="cuda", generator=gen) + torch.from_numpy(bias).cuda()[None, :]).contiguous()
+
+
+# ------------------------------------------------------------------ CPU legs
+def cpu_leg(kind, layer_host, x_bits, logits, n_tokens, threads):
+    """Times the CPU implementation on the first n_tokens of the workload. Returns tokens/s."""
+    import oracle
+    from gfx1151_engine_b200 import synth
+    spec = synth.CONFIG3
+    x = synth.bf16_bits_to_f32(x_bits[:n_tokens])
+    t0 = time.perf_counter()
+    if kind == "reference":
+        import dataclasses
+        oracle.ref_moe_layer(dataclasses.replace(spec, shared=True), layer_host, x, threads=threads)
+    else:
+        oracle.moe_forward(spec, layer_host, x, logits=logits[:n_tokens], threads=threads)
+    return n_tokens / (time.perf_counter() - t0)
+
+
+def reference_arm(args):
+    """The reference's own CPU path (Model::moe, src/ref.cpp) on this host's cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from gfx1151_engine_b200 import synth
+    cores = os.cpu_count() or 1
+    kind = "reference" if oracle.have_ref() else "port"
+    spec = synth.CONFIG3
+    layer = {"gate_up": synth.make_q4cp(synth.rng_for(0, 1), E * 2 * MID, D),
+             "down": synth.make_q4cp(synth.rng_for(0, 2), E * D, MID)}
+    n_tok = max(cores, 8) * 2     # per step: about 0.3 core-seconds per token
+    total = n_tok * (args.steps + args.warmup)
+    xb = synth.make_x(synth.rng_for(0, 9), total, D)
+    logits = synth.make_logits(synth.rng_for(0, 10), total, E, zipf=True, zipf_rng=synth.rng_for(0, 77))
+    if kind == "reference":
+        # Model::moe derives its logits from a router weight and always evaluates a shared
+        # expert: give it a random router weight and a shared expert with zero down scales.
+        layer["router_w"] = synth.f32_to_bf16_bits(synth.rng_for(0, 8).normal(0, 0.02, (E, D)).astype(np.float32))
+        layer["sh_gate"] = synth.make_q4cp(synth.rng_for(0, 4), MID, D)
+        layer["sh_up"] = synth.make_q4cp(synth.rng_for(0, 5), MID, D)
+        layer["sh_down"] = synth.make_q4cp(synth.rng_for(0, 6), D, MID, zero_scales=True)
+        layer["sh_gate_w"] = synth.f32_to_bf16_bits(np.zeros(D, np.float32))
+    times = []
+    for s in range(args.steps + args.warmup):
+        sl = slice(s * n_tok, (s + 1) * n_tok)
+        t0 = time.perf_counter()
+        if kind == "reference":
+            import dataclasses
+            oracle.ref_moe_layer(dataclasses.replace(spec, shared=True), layer,
+                                 synth.bf16_bits_to_f32(xb[sl]), threads=cores)
+        else:
+            oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb[sl]), logits=logits[sl], threads=cores)
+        if s >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    value = n_tok * len(times) / sum(times)
+    sample = ("%d tokens per step of the config-3 layer on %d host threads (OpenMP over tokens)" % (n_tok, cores))
+    if kind == "reference":
+        sample += "; unmodified Model::moe, logits from a random bf16 router weight, shared expert evaluated with zero down scales"
+    print(json.dumps({
+        "impl": "reference", "metric": "moe_prefill_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_step": n_tok},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+# ------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--tokens", type=int, default=T_CHUNK)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import gfx1151_engine_b200 as pkg
+    from gfx1151_engine_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    T = args.tokens
+    peak_tf, peak_hbm, peak_kind = measured_peaks()
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)            # one weight set shared by all ranks
+    gu = q4cp_blob_device(torch, E * 2 * MID, D, gen)
+    dn = q4cp_blob_device(torch, E * D, MID, gen)
+    op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)
+    op.load_q4cp(0, gu, dn)
+    want_cpu = rank == 0 and world == 1 and not args.no_cpu
+    layer_host = {"gate_up": gu.cpu().numpy(), "down": dn.cpu().numpy()} if want_cpu else None
+    op_dec = None
+    if rank == 0 and world == 1 and not args.no_decode:
+        gen2 = torch.Generator(device="cuda")
+        gen2.manual_seed(99)
+        op_dec = pkg.MoeOperator(E, K_TOP, D, MID, 16, has_shared=True, device=local)
+        op_dec.load_q4cp(0, gu, dn)
+        sh = [q4cp_blob_device(torch, MID, D, gen2), q4cp_blob_device(torch, MID, D, gen2),
+              q4cp_blob_device(torch, D, MID, gen2)]
+        op_dec.load_shared_q4cp(0, sh[0], sh[1], sh[2],
+                                (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16))
+    del gu, dn
+    torch.cuda.empty_cache()
+
+    gen_in = torch.Generator(device="cuda")
+    gen_in.manual_seed(1000 + rank)  # per-rank inputs
+    x = torch.randn(T, D, device="cuda", generator=gen_in).to(torch.bfloat16)
+    logits = zipf_logits(torch, T, gen_in, 0)
+    out = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        op.moe_b(0, x, logits, out, stream=stream)
+    op.synchronize(stream)
+    op.profile_enable(True)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    l0 = op.launches
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        op.moe_b(0, x, logits, out, stream=stream)
+    ev1.record(stream)
+    barrier()
+    launches = op.launches - l0
+    clocks = sampler.stop() if rank == 0 else None
+    op.synchronize(stream)
+    ms = ev0.elapsed_time(ev1)
+    stages = op.profile_read()
+    op.profile_enable(False)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * T * args.steps / (ms * 1e-3)
+
+    # end to end through the host-buffer entry point (pinned buffers, copies inside)
+    xh = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+    xh.copy_(x)
+    lh = torch.empty(T, E, dtype=torch.float32).pin_memory()
+    lh.copy_(logits)
+    oh = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    op.moe_b_host(0, xh, lh, oh, T, stream=stream)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        op.moe_b_host(0, xh, lh, oh, T, stream=stream)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * T * e2e_steps / e2e_s, "unit": "tokens/s",
+           "h2d_bytes_per_step": T * D * 2 + T * E * 4, "d2h_bytes_per_step": T * D * 2,
+           "checksum": float(oh.float().abs().mean())}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    up_s = stages["up"] * 1e-3
+    achieved = FLOP_UP_PER_TOKEN * T / up_s / 1e12 if up_s > 0 else 0.0
+    result = {
+        "metric": "moe_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
+                   "d_mid": MID, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2: 3.6 GB of expert weights + 168 MB of activations per step"},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "stage_ms": {k: round(v, 4) for k, v in stages.items()},
+        "layer_tflops": FLOP_PER_TOKEN * T * args.steps / (ms * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "k_expert_tc<up> (gate/up GEMM + SwiGLU)",
+                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                     "peak_kind": peak_kind + " dense 16-bit burst", "traffic": None},
+    }
+
+    if op_dec is not None:
+        result["decode"] = decode_leg(torch, op_dec, peak_hbm, stream)
+    if want_cpu:
+        cores = os.cpu_count() or 1
+        n_tok = max(cores, 8) * 4
+        xb = x[:n_tok].view(torch.int16).cpu().numpy().view(np.uint16)
+        lg = logits[:n_tok].cpu().numpy()
+        v = cpu_leg("port", layer_host, xb, lg, n_tok, cores)
+        result["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                  "sample": "first %d tokens of the same chunk, CPU oracle with OpenMP over tokens" % n_tok}
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def decode_leg(torch, op, peak_hbm, stream):
+    """configs[1]: T = 1 and T = 5 with the shared expert; 64 rotated routings so that the
+    selected experts are not resident in L2 from the previous call."""
+    out = {}
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    for T in (1, 5):
+        sets = 64
+        xs = torch.randn(sets, T, D, device="cuda", generator=gen).to(torch.bfloat16)
+        lgs = torch.randn(sets, T, E, device="cuda", generator=gen)
+        o = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+        for i in range(8):
+            op.moe_b(0, xs[i], lgs[i], o, stream=stream)
+        op.synchronize(stream)
+        uniq = []
+        for i in range(sets):
+            ids = torch.topk(lgs[i], K_TOP, dim=1).indices
+            uniq.append(int(torch.unique(ids).numel()))
+        iters = 4 * sets
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(iters):
+            op.moe_b(0, xs[i % sets], lgs[i % sets], o, stream=stream)
+        e1.record(stream)
+        op.synchronize(stream)
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        nbytes = (float(np.mean(uniq)) + 1) * BYTES_PER_EXPERT
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out["T%d" % T] = {"us_per_call": us, "us_per_token": us / T, "unique_experts": float(np.mean(uniq)),
+                          "algorithmic_bytes": nbytes, "hbm_gbs": gbs, "frac_of_hbm_peak": gbs / peak_hbm}
+    return out
+
+
+if __name__ == "__main__":
+    main()

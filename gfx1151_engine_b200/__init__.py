@@ -45,6 +45,8 @@ SYMBOLS = {
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_synchronize": (_I, [_P, _P]),
+    "b200moe_profile_enable": (_I, [_P, _I]),
+    "b200moe_profile_read": (_I, [_P, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
     "b200moe_launch_count": (ctypes.c_int64, [_P]),
     "b200moe_version": (ctypes.c_char_p, []),
 }
@@ -175,6 +177,20 @@ class MoeOperator:
     def synchronize(self, stream=None):
         """Wait for the stream and raise if a device-side wait gave up."""
         self._check(lib().b200moe_synchronize(self._h, _stream(stream)))
+
+    def profile_enable(self, on=True):
+        self._check(lib().b200moe_profile_enable(self._h, int(on)))
+
+    def profile_read(self):
+        """Mean stage times in ms since the last read: dict with route, gather, up, down,
+        combine, total and the number of calls averaged."""
+        ms = (ctypes.c_float * 6)()
+        n = _I(0)
+        self._check(lib().b200moe_profile_read(self._h, ms, ctypes.byref(n)))
+        names = ("route", "gather", "up", "down", "combine", "total")
+        out = {k: float(v) for k, v in zip(names, ms)}
+        out["calls"] = n.value
+        return out
 
     # -- inspection ---------------------------------------------------------------------------
     def get_routing(self, T):

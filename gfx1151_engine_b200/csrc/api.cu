@@ -17,6 +17,8 @@ using namespace b200moe;
 
 namespace {
 
+constexpr int kProfRing = 64, kProfEvents = 6;
+
 struct LayerWeights {
   Image gu, dn, sh_gu, sh_dn;
   uint16_t* sh_gate_w = nullptr;
@@ -41,6 +43,10 @@ struct b200moe_ctx {
   int32_t* status_host = nullptr;  // pinned
   TcPlan* tc = nullptr;
   int64_t launches = 0;
+  // stage timer: ring of event sets, one set (7 events) per forward call
+  bool prof = false;
+  std::vector<cudaEvent_t> prof_ev;
+  int prof_head = 0, prof_pending = 0;
   int max_rows = 0, max_tiles = 0, max_tiles_sh = 0;
   std::string err;
 };
@@ -248,6 +254,7 @@ int b200moe_destroy(b200moe_handle h) {
     if (L.sh_gate_w) cudaFree(L.sh_gate_w);
   }
   free_all(h->allocs);
+  for (auto& e : h->prof_ev) cudaEventDestroy(e);
   if (h->status_host) cudaFreeHost(h->status_host);
   if (h->tc) tc_destroy(h->tc);
   cudaGetLastError();
@@ -431,7 +438,8 @@ int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw
 }
 
 static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const int32_t* ids,
-                        const float* w, int stride, void* out, cudaStream_t st) {
+                        const float* w, int stride, void* out, cudaStream_t st,
+                        bool router_timed = false) {
   const b200moe_config& c = h->cfg;
   LayerWeights& L = h->layers[layer];
   const int k = c.topk, E = c.experts, d = c.d_model, mid = c.d_mid;
@@ -439,11 +447,18 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   if (!L.loaded || (shared && !L.shared_loaded))
     return fail(h, B200MOE_ERR_NOT_LOADED, "forward: layer weights not loaded");
   int n = 0;
+  cudaEvent_t* ev = nullptr;
+  if (h->prof) {
+    ev = &h->prof_ev[(size_t)h->prof_head * kProfEvents];
+    // ev[0] was recorded by the caller of forward_impl (before the router) when it ran one
+    if (!router_timed) CU_TRY(h, cudaEventRecord(ev[0], st));
+  }
   CU_TRY(h, launch_route(h->rb, ids, w, stride, T, k, E, h->tile_cap, st, &n));
   if (shared) {
     CU_TRY(h, launch_shared_gate(x, L.sh_gate_w, T, d, k, h->rb, st));
     n++;
   }
+  if (ev) CU_TRY(h, cudaEventRecord(ev[1], st));
   const int pairs = T * k;
   const bool simt = c.gemm_impl == B200MOE_GEMM_SIMT ||
                     (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max);
@@ -455,18 +470,25 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
   if (simt) {
     const int max_runs = std::min(E, pairs);
+    if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
     CU_TRY(h, launch_up_simt(L.gu, x, d, mid, h->rb.tokidx, h->rb.runs, h->rb.n_runs, max_runs,
                              (float*)h->hid, st));
-    CU_TRY(h, launch_down_simt(L.dn, (const float*)h->hid, d, mid, h->rb.runs, h->rb.n_runs,
-                               max_runs, (float*)h->pairs, st));
-    n += 2;
+    n++;
     if (shared) {
       CU_TRY(h, launch_up_simt(L.sh_gu, x, d, mid, h->rb.tokidx, h->rb.runs + kMaxExperts,
                                h->rb.n_runs + 1, 1, (float*)h->hid, st));
+      n++;
+    }
+    if (ev) CU_TRY(h, cudaEventRecord(ev[3], st));
+    CU_TRY(h, launch_down_simt(L.dn, (const float*)h->hid, d, mid, h->rb.runs, h->rb.n_runs,
+                               max_runs, (float*)h->pairs, st));
+    n++;
+    if (shared) {
       CU_TRY(h, launch_down_simt(L.sh_dn, (const float*)h->hid, d, mid, h->rb.runs + kMaxExperts,
                                  h->rb.n_runs + 1, 1, (float*)h->pairs, st));
-      n += 2;
+      n++;
     }
+    if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
                                  shared ? pairs : -1, out, st));
     n++;
@@ -475,21 +497,33 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     const int rows = pairs + (shared ? T : 0);
     CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, rows, d, h->x_sorted, st));
     n++;
+    if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
     CU_TRY(h, launch_up_tc(h->tc, L.gu, h->rb.tiles, h->rb.n_tiles, h->max_tiles, (__half*)h->hid,
                            h->status_dev, st));
-    CU_TRY(h, launch_down_tc(h->tc, L.dn, h->rb.tiles, h->rb.n_tiles, h->max_tiles,
-                             (__half*)h->pairs, h->status_dev, st));
-    n += 2;
+    n++;
     if (shared) {
       CU_TRY(h, launch_up_tc(h->tc, L.sh_gu, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh,
                              (__half*)h->hid, h->status_dev, st));
+      n++;
+    }
+    if (ev) CU_TRY(h, cudaEventRecord(ev[3], st));
+    CU_TRY(h, launch_down_tc(h->tc, L.dn, h->rb.tiles, h->rb.n_tiles, h->max_tiles,
+                             (__half*)h->pairs, h->status_dev, st));
+    n++;
+    if (shared) {
       CU_TRY(h, launch_down_tc(h->tc, L.sh_dn, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh,
                                (__half*)h->pairs, h->status_dev, st));
-      n += 2;
+      n++;
     }
+    if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f16((const __half*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
                                  shared ? pairs : -1, out, st));
     n++;
+  }
+  if (ev) {
+    CU_TRY(h, cudaEventRecord(ev[5], st));
+    h->prof_head = (h->prof_head + 1) % kProfRing;
+    if (h->prof_pending < kProfRing) h->prof_pending++;
   }
   h->launches += n;
   return B200MOE_OK;
@@ -502,10 +536,12 @@ int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: bad argument (null pointer or T out of range)");
   if (T == 0) return B200MOE_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (h->prof) CU_TRY(h, cudaEventRecord(h->prof_ev[(size_t)h->prof_head * kProfEvents], st));
   CU_TRY(h, launch_router_topk(logits_dev, T, h->cfg.experts, h->cfg.topk, h->rb.topids, h->rb.topw,
                                kIdStride, st));
   h->launches++;
-  return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st);
+  return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st,
+                      h->prof);
 }
 
 int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
@@ -558,6 +594,40 @@ int b200moe_debug_get_routing(b200moe_handle h, int T, int32_t* topids_host, flo
   if (pairids_host) CU_TRY(h, cudaMemcpy(pairids_host, h->rb.pairids, pairs * 4, cudaMemcpyDeviceToHost));
   CU_TRY(h, cudaMemcpy(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost));
   if (h->status_host[0] != 0) return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, "device-side wait timed out");
+  return B200MOE_OK;
+}
+
+int b200moe_profile_enable(b200moe_handle h, int on) {
+  if (!h) return B200MOE_ERR_BAD_ARG;
+  if (on && h->prof_ev.empty()) {
+    h->prof_ev.resize((size_t)kProfRing * kProfEvents);
+    for (auto& e : h->prof_ev) CU_TRY(h, cudaEventCreate(&e));
+  }
+  h->prof = on != 0;
+  h->prof_pending = 0;
+  return B200MOE_OK;
+}
+
+int b200moe_profile_read(b200moe_handle h, float* stage_ms6, int* n_calls) {
+  if (!h || !stage_ms6 || !n_calls) return B200MOE_ERR_BAD_ARG;
+  for (int i = 0; i < 6; i++) stage_ms6[i] = 0.f;
+  *n_calls = h->prof_pending;
+  if (h->prof_pending == 0) return B200MOE_OK;
+  const int last = (h->prof_head + kProfRing - 1) % kProfRing;
+  CU_TRY(h, cudaEventSynchronize(h->prof_ev[(size_t)last * kProfEvents + 5]));
+  for (int c = 0; c < h->prof_pending; c++) {
+    const int slot = (h->prof_head + kProfRing - 1 - c) % kProfRing;
+    cudaEvent_t* ev = &h->prof_ev[(size_t)slot * kProfEvents];
+    float ms;
+    for (int s = 0; s < 5; s++) {
+      CU_TRY(h, cudaEventElapsedTime(&ms, ev[s], ev[s + 1]));
+      stage_ms6[s] += ms;
+    }
+    CU_TRY(h, cudaEventElapsedTime(&ms, ev[0], ev[5]));
+    stage_ms6[5] += ms;
+  }
+  for (int i = 0; i < 6; i++) stage_ms6[i] /= (float)h->prof_pending;
+  h->prof_pending = 0;
   return B200MOE_OK;
 }
 

@@ -145,6 +145,15 @@ int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int
  * hipStreamSynchronize in the reference's layer loop). Clears the recorded condition. */
 int b200moe_synchronize(b200moe_handle h, void* stream);
 
+/* Stage timer (replaces the reference's event-ring kernel profiler KP()/kprof,
+ * src/gpu/parts/07_kprof.inc:1-134, tags moe:route/up/down/reduce). When enabled, forward
+ * records CUDA events between its stages on the caller's stream; profile_read waits for the
+ * last recorded call and returns, per stage, the mean milliseconds over the calls since the
+ * previous read (at most the last 64): [0] router top-k + bucketing, [1] activation gather,
+ * [2] gate/up GEMM + SwiGLU, [3] down GEMM, [4] combine, [5] whole call. */
+int b200moe_profile_enable(b200moe_handle h, int on);
+int b200moe_profile_read(b200moe_handle h, float* stage_ms6, int* n_calls);
+
 /* Number of kernels this library launched since the handle was created (the benchmark
  * reports the difference across its timed region). */
 int64_t b200moe_launch_count(b200moe_handle h);
