@@ -16,7 +16,7 @@ GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
 GGML_Q5_1, GGML_Q4_K = 7, 12
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
-          5: "device timeout", 6: "NCCL error", 7: "out of memory"}
+          5: "device timeout", 6: "NCCL error", 7: "out of memory", 8: "too large for the static scratch"}
 
 # Every symbol include/b200moe.h declares: name -> (restype, argtypes)
 _P, _I, _SZ = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -42,6 +42,7 @@ SYMBOLS = {
     "b200moe_forward_host": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
     "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
+    "b200moe_route_static": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_synchronize": (_I, [_P, _P]),

@@ -164,6 +164,7 @@ const char* b200moe_status_string(int s) {
     case B200MOE_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
     case B200MOE_ERR_NCCL: return "NCCL error";
     case B200MOE_ERR_ALLOC: return "out of memory";
+    case B200MOE_ERR_TOO_LARGE: return "request exceeds the fixed scratch capacity of the allocation-free entry point";
     default: return "unknown status";
   }
 }

@@ -36,7 +36,8 @@ enum {
   B200MOE_ERR_NOT_LOADED = 4,   /* forward before the layer's weights were loaded */
   B200MOE_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up */
   B200MOE_ERR_NCCL = 6,
-  B200MOE_ERR_ALLOC = 7
+  B200MOE_ERR_ALLOC = 7,
+  B200MOE_ERR_TOO_LARGE = 8     /* request exceeds the fixed capacity of b200moe_route_static */
 };
 
 /* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
@@ -125,6 +126,22 @@ int b200moe_router_topk(b200moe_handle h, const float* logits_dev, int T, int32_
  * order and tile list for the given selection. */
 int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw_dev, int stride,
                   int T, void* stream);
+
+/* The bucketing of b200moe_route for hosts that cannot allocate device memory at this point
+ * (all HBM already given to their own arena or KV pool, a fixed memory budget, or a section
+ * where cudaMalloc's implicit synchronisation is not acceptable) and therefore have no handle.
+ * It has no counterpart in the reference. Needs no handle and calls no allocator: its scratch
+ * (per-chunk expert counts) is a 256 KiB __device__ array inside the library, present on every
+ * GPU that loads it. Limits: T*topk <= 65536, experts <= 512, topk <= 16; beyond them the call
+ * returns B200MOE_ERR_TOO_LARGE and launches nothing. Outputs are caller buffers on the current
+ * device: tokidx[T*topk], pw[T*topk], eoff[experts+1], pairids[T*topk], same definitions and
+ * same bytes as b200moe_route produces. All calls on a GPU share the scratch: calls whose
+ * kernels overlap (unordered streams, several threads) race; keep them on one stream. The
+ * first call on a device looks up the scratch's device address -- make it before any stream
+ * capture. */
+int b200moe_route_static(const int32_t* topids_dev, const float* topw_dev, int stride, int T,
+                         int topk, int experts, int32_t* tokidx_dev, float* pw_dev,
+                         int32_t* eoff_dev, int32_t* pairids_dev, void* stream);
 
 /* Reads back what the last forward / route call left in the workspace (host buffers; any may
  * be NULL): tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k] as defined by
