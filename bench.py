@@ -30,7 +30,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-E, K_TOP, D, MID, T_CHUNK = 512, 10, 4096, 1024, 16384
+E, K_TOP, D, MID, T_CHUNK = 512, 10, 4096, 1024, 16384   # E is overridable for small profiling cases
 FLOP_PER_TOKEN = K_TOP * (2 * (2 * MID) * D + 2 * D * MID)          # 251,658,240
 FLOP_UP_PER_TOKEN = K_TOP * 2 * (2 * MID) * D                        # gate/up GEMM share
 BYTES_PER_EXPERT = 3 * MID * D * 9 // 16                             # 7,077,888 (0.5625 B / weight)
@@ -185,17 +185,20 @@ def reference_arm(args):
 
 # ------------------------------------------------------------------ GPU arm
 def main():
+    global E
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--tokens", type=int, default=T_CHUNK)
+    ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    E = args.experts
 
     import torch
     import torch.distributed as dist
@@ -305,7 +308,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
+        "config": {"workload": WORKLOAD if (E, T) == (512, T_CHUNK) else "reduced case for profiling (not the benchmark workload)", "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
                    "d_mid": MID, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 3.6 GB of expert weights + 168 MB of activations per step"},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
