@@ -9,9 +9,11 @@
 // nearly empty expert costs a narrow instruction instead of a padded token tile.
 //
 // One CTA per SM, 16 warps with fixed roles:
-//   warp 0      producer: bulk-async copies of packed 4-bit weight tiles (one contiguous
-//               4.5 KB object per tile and K block) and TMA tensor copies of activation
-//               tiles (128-byte swizzle) into shared-memory rings
+//   warp 0      producer of activation tiles: one TMA tensor copy (128-byte swizzle, box of
+//               16/64/128/192 rows) per K block into a shared-memory ring
+//   warp 2      producer of packed 4-bit weight tiles: one bulk-async copy of a contiguous
+//               4.5 KB object per tile and K block (a single thread can only start a copy
+//               every ~170 cycles, hence two producer threads and one copy each per K block)
 //   warp 1      issues tcgen05.mma (A from tensor memory, B from shared memory), owns the
 //               tensor-memory allocation
 //   warps 4-11  dequantise: two groups of four warps alternate K blocks; thread = one
@@ -28,11 +30,15 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 namespace b200moe {
 
 struct TcPlan {
-  CUtensorMap x16, x64, h16, h64;
+  CUtensorMap x[4], h[4];  // activation / hidden maps with boxes of 16, 64, 128, 192 rows
   int sms = 148;
+  long long* trace = nullptr;  // debug timeline of CTA 0 (environment B200MOE_TC_TRACE=<file>)
 };
 
 namespace {
@@ -47,12 +53,20 @@ constexpr int kThreads = 512;
 constexpr int kAccCols = kTcTileN;       // columns per accumulator
 constexpr int kTmemA = 2 * kAccCols;     // first column of the A stages (384)
 
-constexpr int kOffLut = 0;
-constexpr int kOffB = 2 * kLutBytes;
-constexpr int kOffW = kOffB + kNB * kBStage;
-constexpr int kOffU = kOffW + kNW * kWStage;
-constexpr int kOffBar = kOffU + 2 * 32 * 32 * 4;
-constexpr int kSmemBytes = kOffBar + 512 + 1024;  // + slack for manual 1 KB alignment
+// Shared-memory map in ABSOLUTE addresses of the CTA's shared window (the dynamic
+// allocation starts at 1 KB when the kernel has no static shared memory). The pair table
+// sits exactly at 64 KB so that the address of a lookup is a single byte permute:
+//   address = 0x00010000 | code byte << 8 | table half << 7 | lane << 2
+// i.e. entry stride 256 B = [table of tile rows 0..63: 32 lanes x 4 B][rows 64..127: 32 x 4 B].
+constexpr int kOffW = 2048;                          // packed weight stages
+constexpr int kOffU = kOffW + kNW * kWStage;         // SwiGLU exchange buffer (8 KB)
+constexpr int kOffBar = kOffU + 2 * 32 * 32 * 4;     // barriers and flags (512 B)
+constexpr int kOffLut = 65536;                       // pair tables (64 KB)
+constexpr int kOffB = 131072;                        // activation stages, 1 KB aligned
+constexpr int kSmemEnd = kOffB + kNB * kBStage;      // 229376
+constexpr int kSmemBytes = kSmemEnd - 1024;          // dynamic bytes requested
+static_assert(kOffBar + 512 <= kOffLut, "low region overflows into the pair tables");
+static_assert(kSmemEnd <= 233472, "shared memory map exceeds the SM");
 
 // barrier slots (8 bytes each) inside the barrier block
 constexpr int kBarWFull = 0, kBarWEmpty = kBarWFull + kNW, kBarBFull = kBarWEmpty + kNW,
@@ -95,11 +109,15 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one gave up).
+// `nap_ns` > 0 makes the waiting warp sleep between polls: warps that poll in a tight loop
+// take issue slots from the warp that shares their scheduler, and the thread that issues
+// the MMAs must not be slowed down by waiters.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int where) {
+                                          int32_t* status, int where, unsigned nap_ns = 0) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = now_ns();
   for (uint32_t spin = 1;; spin++) {
+    if (nap_ns) __nanosleep(nap_ns);
     if (mbar_try(bar, parity)) return true;
     if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
@@ -205,15 +223,34 @@ struct KParams {
   __half* out;
   int out_ld;   // mid (gate/up) or d (down)
   int32_t* status;
+  long long* trace;  // null, or [8 roles][kTraceSlots][4] clock samples written by CTA 0
 };
+constexpr int kTraceSlots = 512;
+#define TR(role, slot, ev)                                                            \
+  do {                                                                                \
+    if (p.trace && blockIdx.x == 0 && (slot) < (uint32_t)kTraceSlots)                 \
+      p.trace[((role) * kTraceSlots + (slot)) * 4 + (ev)] = clock64();                \
+  } while (0)
 
 template <bool UP>
 __global__ void __launch_bounds__(kThreads, 1)
 k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
+            const __grid_constant__ CUtensorMap map128, const __grid_constant__ CUtensorMap map192,
             const KParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t sbase = smem_u32(smem);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // smem + A is the generic pointer of absolute shared address A
+  const uint32_t dyn0 = smem_u32(smem_raw);
+  uint8_t* const smem = smem_raw - dyn0;
+  constexpr uint32_t sbase = 0;
+  {
+    uint32_t dyn_size;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    if (dyn0 > (uint32_t)kOffW || dyn0 + dyn_size < (uint32_t)kSmemEnd) {
+      // the fixed map does not fit this launch: refuse (uniform for the whole CTA)
+      if (threadIdx.x == 0 && atomicCAS(p.status, 0, 2) == 0) p.status[1] = (int)dyn0;
+      return;
+    }
+  }
   const uint32_t bars = sbase + kOffBar;
   volatile int* abort_flag = (volatile int*)(smem + kOffBar + kNumBars * 8);
   uint32_t* tmem_slot = (uint32_t*)(smem + kOffBar + kNumBars * 8 + 8);
@@ -249,7 +286,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   for (int i = threadIdx.x; i < 2 * 256 * 32; i += kThreads) {
     const int half_id = i >> 13, entry = (i >> 5) & 255;
     const float lo = img.book[half_id * 16 + (entry & 15)], hi = img.book[half_id * 16 + (entry >> 4)];
-    ((__half2*)(smem + kOffLut))[i] = __floats2half2_rn(lo, hi);
+    *(__half2*)(smem + kOffLut + entry * 256 + half_id * 128 + (i & 31) * 4) = __floats2half2_rn(lo, hi);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -264,34 +301,43 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
-    // ================= producer =================
+    // ================= producer of activation tiles (one tensor copy per K block) =========
+    if (lane == 0) {
+      uint32_t kbi = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+        const Tile t = p.tiles[it / img.n_mtiles];
+        const int n_pad = (t.count + 15) & ~15;
+        // smallest box that covers the tile's rows: 16, 64, 128 or 192 rows of 64 halfs
+        const CUtensorMap* map = n_pad <= 16 ? &map16 : n_pad <= 64 ? &map64 : n_pad <= 128 ? &map128 : &map192;
+        const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : 192) * 128;
+        for (int kb = 0; kb < KB && ok; kb++, kbi++) {
+          const uint32_t bs = kbi % kNB, bph = (kbi / kNB) & 1;
+          ok = mbar_wait(bars + 8 * (kBarBEmpty + bs), bph ^ 1, abort_flag, p.status, 2, 64);
+          if (!ok) break;
+          TR(0, kbi, 1);
+          const uint32_t bbar = bars + 8 * (kBarBFull + bs);
+          mbar_expect_tx(bbar, bytes);
+          tma_load_2d(sbase + kOffB + bs * kBStage, map, kb * kTileK, t.first, bbar);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ================= producer of packed weight tiles (one bulk copy per K block) ========
     if (lane == 0) {
       uint32_t kbi = 0;
       bool ok = true;
       for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
         const Tile t = p.tiles[it / img.n_mtiles];
         const int mt = it % img.n_mtiles;
-        const int n_pad = (t.count + 15) & ~15;
-        for (int kb = 0; kb < KB && ok; kb++, kbi++) {
+        const uint8_t* src = img.tile(t.expert, mt, 0);
+        for (int kb = 0; kb < KB && ok; kb++, kbi++, src += wbytes) {
           const uint32_t ws = kbi % kNW, wph = (kbi / kNW) & 1;
-          ok = mbar_wait(bars + 8 * (kBarWEmpty + ws), wph ^ 1, abort_flag, p.status, 1);
+          ok = mbar_wait(bars + 8 * (kBarWEmpty + ws), wph ^ 1, abort_flag, p.status, 1, 64);
           if (!ok) break;
+          TR(0, kbi, 0);
           mbar_expect_tx(bars + 8 * (kBarWFull + ws), wbytes);
-          bulk_copy_g2s(sbase + kOffW + ws * kWStage, img.tile(t.expert, mt, kb), wbytes,
-                        bars + 8 * (kBarWFull + ws));
-          const uint32_t bs = kbi % kNB, bph = (kbi / kNB) & 1;
-          ok = mbar_wait(bars + 8 * (kBarBEmpty + bs), bph ^ 1, abort_flag, p.status, 2);
-          if (!ok) break;
-          const uint32_t bdst = sbase + kOffB + bs * kBStage, bbar = bars + 8 * (kBarBFull + bs);
-          if (n_pad <= 16) {
-            mbar_expect_tx(bbar, 16 * 128);
-            tma_load_2d(bdst, &map16, kb * kTileK, t.first, bbar);
-          } else {
-            const int nbox = (n_pad + 63) >> 6;
-            mbar_expect_tx(bbar, nbox * 64 * 128);
-            for (int j = 0; j < nbox; j++)
-              tma_load_2d(bdst + j * 64 * 128, &map64, kb * kTileK, t.first + 64 * j, bbar);
-          }
+          bulk_copy_g2s(sbase + kOffW + ws * kWStage, src, wbytes, bars + 8 * (kBarWFull + ws));
         }
       }
     }
@@ -314,8 +360,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           const uint32_t as = kbi % kNA, aph = (kbi / kNA) & 1;
           ok = mbar_wait(bars + 8 * (kBarBFull + bs), bph, abort_flag, p.status, 4);
           if (!ok) break;
+          TR(1, kbi, 0);
           ok = mbar_wait(bars + 8 * (kBarAFull + as), aph, abort_flag, p.status, 5);
           if (!ok) break;
+          TR(1, kbi, 1);
           tc_fence_after();
           const uint64_t bdesc = b_descriptor(sbase + kOffB + bs * kBStage);
           const uint32_t a_tmem = tmem + kTmemA + as * 32;
@@ -323,8 +371,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           for (int ks = 0; ks < 4; ks++)
             tc_mma_ts(d_tmem, a_tmem + ks * 8, bdesc + (uint64_t)(ks * 2), idesc,
                       (kb | ks) != 0 ? 1u : 0u);
+          TR(1, kbi, 3);
           tc_commit(bars + 8 * (kBarAEmpty + as));
           tc_commit(bars + 8 * (kBarBEmpty + bs));
+          TR(1, kbi, 2);
         }
         if (ok) tc_commit(bars + 8 * (kBarAccFull + acc));
       }
@@ -333,16 +383,17 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // ================= dequantise into tensor memory =================
     const int grp = (warp - 4) >> 2, quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const uint32_t lut = sbase + kOffLut + (r >= 64 ? kLutBytes : 0) + lane * 4;
+    const uint32_t lut = (uint32_t)kOffLut | (uint32_t)((r >= 64 ? 128 : 0) + lane * 4);
     uint32_t kbi = 0;
     bool ok = true;
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
       for (int kb = 0; kb < KB && ok; kb++, kbi++) {
         if ((int)(kbi & 1) != grp) continue;
         const uint32_t ws = kbi % kNW, wph = (kbi / kNW) & 1;
-        ok = mbar_wait(bars + 8 * (kBarWFull + ws), wph, abort_flag, p.status, 6);
+        ok = mbar_wait(bars + 8 * (kBarWFull + ws), wph, abort_flag, p.status, 6, 32);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 0);
         const uint8_t* wt = smem + kOffW + ws * kWStage;
         uint32_t v[32];
         const uint32_t sc = *(const uint32_t*)(wt + kCodeBytes + r * 4);
@@ -356,9 +407,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           for (int q = 0; q < 4; q++) {
 #pragma unroll
             for (int b = 0; b < 4; b++) {
-              const uint32_t byte = (w4[q] >> (8 * b)) & 0xFFu;
+              // bytes (3,2,1,0) of the address = (table.3, table.2, code byte b, table.0)
+              const uint32_t addr = __byte_perm(w4[q], lut, 0x7604 | (b << 4));
               uint32_t pair;
-              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(lut + (byte << 7)));
+              asm("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(addr));
               __half2 w2 = __hmul2(*(__half2*)&pair, *(const __half2*)&s2);
               v[h * 16 + q * 4 + b] = *(uint32_t*)&w2;
             }
@@ -367,12 +419,15 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + 8 * (kBarWEmpty + ws));
         const uint32_t as = kbi % kNA, aph = (kbi / kNA) & 1;
-        ok = mbar_wait(bars + 8 * (kBarAEmpty + as), aph ^ 1, abort_flag, p.status, 7);
+        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 1);
+        ok = mbar_wait(bars + 8 * (kBarAEmpty + as), aph ^ 1, abort_flag, p.status, 7, 32);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 2);
         tc_fence_after();
         tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + as * 32, v);
         tc_wait_st();
+        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 3);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + as));
@@ -389,7 +444,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       const Tile t = p.tiles[it / img.n_mtiles];
       const int mt = it % img.n_mtiles;
       const uint32_t acc = li & 1, accph = (li >> 1) & 1;
-      ok = mbar_wait(bars + 8 * (kBarAccFull + acc), accph, abort_flag, p.status, 8);
+      ok = mbar_wait(bars + 8 * (kBarAccFull + acc), accph, abort_flag, p.status, 8, 256);
       // The four epilogue warps must take the same decision (they meet at named barriers
       // below): publish each warp's result, meet once, and combine.
       ok = __all_sync(0xffffffffu, ok);
@@ -398,6 +453,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       ok = (ep_ok[(li & 1) * 4] & ep_ok[(li & 1) * 4 + 1] & ep_ok[(li & 1) * 4 + 2] &
             ep_ok[(li & 1) * 4 + 3]) != 0;
       if (!ok) break;
+      if (lane == 0 && quarter == 0) TR(4, li, 0);
       tc_fence_after();
       const uint32_t src = tmem + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols;
       for (int c0 = 0; c0 < t.count; c0 += 32) {
@@ -429,6 +485,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
             if (c0 + j < t.count) dst[(size_t)j * p.out_ld] = __float2half_rn(__uint_as_float(v[j]));
         }
       }
+      if (lane == 0 && quarter == 0) TR(4, li, 1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarAccEmpty + acc));
@@ -463,7 +520,7 @@ cudaError_t encode_2d(PFN_cuTensorMapEncodeTiled_v12000 enc, CUtensorMap* map, c
 }
 
 template <bool UP>
-cudaError_t launch(TcPlan* plan, const CUtensorMap& m16, const CUtensorMap& m64, const Image& img,
+cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
                    const Tile* tiles, const int32_t* n_tiles, int max_tiles, __half* out, int out_ld,
                    int32_t* status, cudaStream_t st) {
   if (img.fmt != kQ4CP) return cudaErrorNotSupported;
@@ -474,11 +531,11 @@ cudaError_t launch(TcPlan* plan, const CUtensorMap& m16, const CUtensorMap& m64,
     if (e != cudaSuccess) return e;
     attr_set[UP] = true;
   }
-  KParams p{img, tiles, n_tiles, out, out_ld, status};
+  KParams p{img, tiles, n_tiles, out, out_ld, status, UP ? plan->trace : nullptr};
   long long max_items = (long long)max_tiles * img.n_mtiles;
   int grid = (int)(max_items < plan->sms ? max_items : plan->sms);
   if (grid < 1) grid = 1;
-  k_expert_tc<UP><<<grid, kThreads, kSmemBytes, st>>>(m16, m64, p);
+  k_expert_tc<UP><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
   return cudaGetLastError();
 }
 
@@ -497,29 +554,49 @@ cudaError_t tc_create(TcPlan** out, const __half* x_sorted, const __half* hid16,
   int dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&plan->sms, cudaDevAttrMultiProcessorCount, dev);
-  e = encode_2d(enc, &plan->x16, x_sorted, rows_cap, d, 16);
-  if (e == cudaSuccess) e = encode_2d(enc, &plan->x64, x_sorted, rows_cap, d, 64);
-  if (e == cudaSuccess) e = encode_2d(enc, &plan->h16, hid16, rows_cap, mid, 16);
-  if (e == cudaSuccess) e = encode_2d(enc, &plan->h64, hid16, rows_cap, mid, 64);
+  const int boxes[4] = {16, 64, 128, kTcTileN};
+  e = cudaSuccess;
+  for (int i = 0; i < 4 && e == cudaSuccess; i++) e = encode_2d(enc, &plan->x[i], x_sorted, rows_cap, d, boxes[i]);
+  for (int i = 0; i < 4 && e == cudaSuccess; i++) e = encode_2d(enc, &plan->h[i], hid16, rows_cap, mid, boxes[i]);
   if (e != cudaSuccess) {
     delete plan;
     return e;
+  }
+  if (getenv("B200MOE_TC_TRACE")) {
+    const size_t bytes = (size_t)8 * kTraceSlots * 4 * sizeof(long long);
+    if (cudaMalloc((void**)&plan->trace, bytes) == cudaSuccess) cudaMemset(plan->trace, 0, bytes);
+    else plan->trace = nullptr;
   }
   *out = plan;
   return cudaSuccess;
 }
 
-void tc_destroy(TcPlan* plan) { delete plan; }
+void tc_destroy(TcPlan* plan) {
+  if (plan && plan->trace) {
+    // debug aid: dump CTA 0's timeline of the last gate/up launch as raw int64
+    const size_t n = (size_t)8 * kTraceSlots * 4;
+    long long* host = new long long[n];
+    if (cudaMemcpy(host, plan->trace, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess) {
+      if (FILE* f = fopen(getenv("B200MOE_TC_TRACE") ? getenv("B200MOE_TC_TRACE") : "tc_trace.bin", "wb")) {
+        fwrite(host, sizeof(long long), n, f);
+        fclose(f);
+      }
+    }
+    delete[] host;
+    cudaFree(plan->trace);
+  }
+  delete plan;
+}
 
 cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                          int max_tiles, __half* hid16, int32_t* status, cudaStream_t st) {
-  return launch<true>(plan, plan->x16, plan->x64, img, tiles, n_tiles, max_tiles, hid16,
+  return launch<true>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16,
                       img.n_mtiles * 64, status, st);
 }
 
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                            int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st) {
-  return launch<false>(plan, plan->h16, plan->h64, img, tiles, n_tiles, max_tiles, pairs16,
+  return launch<false>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
                        img.n_mtiles * 128, status, st);
 }
 
