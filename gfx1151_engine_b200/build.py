@@ -18,7 +18,7 @@ FLAGS = [
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
     # the environment may point nvcc's host compiler elsewhere; use the system one
     "-ccbin", "/usr/bin/g++",
-]
+] + os.environ.get("B200MOE_NVCC_FLAGS", "").split()
 
 
 def _stale():

@@ -396,6 +396,7 @@ int b200moe_load_shared_q4cp(b200moe_handle h, int layer, const void* gate_src, 
     e = launch_repack(L.sh_dn, a, a, (int)mid, 0, 0);
     h->launches++;
   }
+  L.sh_gu.dual_book = 1;
   if (e == cudaSuccess) e = cudaMemcpy(L.sh_gu.book, g, 64, cudaMemcpyDeviceToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(L.sh_gu.book + 16, u, 64, cudaMemcpyDeviceToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(L.sh_dn.book, dn, 64, cudaMemcpyDeviceToDevice);

@@ -41,6 +41,7 @@ struct Image {
   int n_mtiles = 0;   // per expert
   int n_kblocks = 0;  // K / 64
   int paired = 0;     // 1: gate/up image (tile rows 0..63 gate, 64..127 the matching up rows)
+  int dual_book = 0;  // 1: the two halves of a tile use different code books (separate gate / up tensors)
   float* book = nullptr;  // device [32]: code book of tile rows 0..63, then of rows 64..127
   __host__ __device__ size_t tile_stride() const { return (size_t)tile_bytes(fmt); }
   __host__ __device__ size_t expert_stride() const {

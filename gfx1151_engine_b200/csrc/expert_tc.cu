@@ -8,21 +8,28 @@
 // rows per tile) and the rows of one expert on the variable N side (16..192), so that a
 // nearly empty expert costs a narrow instruction instead of a padded token tile.
 //
-// One CTA per SM, 16 warps with fixed roles:
-//   warp 0      producer of activation tiles: one TMA tensor copy (128-byte swizzle, box of
-//               16/64/128/192 rows) per K block into a shared-memory ring
-//   warp 2      producer of packed 4-bit weight tiles: one bulk-async copy of a contiguous
-//               4.5 KB object per tile and K block (a single thread can only start a copy
-//               every ~170 cycles, hence two producer threads and one copy each per K block)
-//   warp 1      issues tcgen05.mma (A from tensor memory, B from shared memory), owns the
-//               tensor-memory allocation
-//   warps 4-11  dequantise: two groups of four warps alternate K blocks; thread = one
-//               weight row; 256-entry half2 pair table replicated per lane in shared
-//               memory (bank-conflict free), one half2 multiply by the group scale, result
-//               written straight into tensor memory (tcgen05.st) as the MMA's A operand
-//   warps 12-15 epilogue: tcgen05.ld the fp32 accumulator, SwiGLU (gate/up rows live in
-//               different lanes, exchanged through shared memory) or plain convert,
-//               fp16 stores; overlaps the next tile's main loop (two accumulators)
+// One CTA per SM, 24 warps with fixed roles. K blocks (64 wide) are handled in pairs:
+//   warp 0      producer of activation tiles: TMA tensor copies (128-byte swizzle, box of
+//               16/64/128/192 rows), one per K block, into a ring of 3 pair-slots in shared
+//               memory (2 when a tile needs two code books)
+//   warp 1      issues tcgen05.mma (A from tensor memory, B from shared memory): eight per
+//               pair behind ONE barrier wait and ONE commit; owns the tensor-memory allocation
+//   warp 3      relay: folds "activations of the pair have landed" into the barrier the MMA
+//               warp waits on, so that warp polls a single barrier
+//   warps 4-19  dequantise: two sets of eight warps alternate pairs (set s owns tensor-memory
+//               slot s); thread = one weight row of one K block. Packed codes come straight
+//               from global memory (a warp's 32 rows are 512 contiguous bytes), one own pair
+//               ahead; each code byte indexes a 256-entry half2 pair table replicated per
+//               lane in shared memory (bank-conflict free); one half2 multiply by the group
+//               scale; the result goes straight into tensor memory (tcgen05.st) as the
+//               MMA's A operand
+//   warps 20-23 epilogue: tcgen05.ld the fp32 accumulator, SwiGLU (gate/up rows live in
+//               different lanes, exchanged through shared memory, work split over all four
+//               warps) or plain convert, transposed through shared memory into 16-byte
+//               global stores; overlaps the next tile's main loop (two accumulators)
+// Measured limits that shaped this: a single thread starts a TMA copy only every ~170
+// cycles; a barrier poll costs ~250 cycles under load; issuing an MMA costs the issuing
+// thread ~85 cycles.
 // Every wait on an mbarrier is bounded; when one gives up the CTA records a status
 // word, stops issuing work, and leaves after releasing its tensor memory.
 #include "tc.h"
@@ -43,37 +50,38 @@ struct TcPlan {
 
 namespace {
 
-constexpr int kNB = 4;    // activation stages
-constexpr int kNW = 6;    // packed weight stages
-constexpr int kNA = 4;    // tensor-memory A stages (32 columns each)
-constexpr int kBStage = kTcTileN * 128;  // bytes: rows x 64 halfs
-constexpr int kWStage = 6144;
-constexpr int kLutBytes = 256 * 32 * 4;
-constexpr int kThreads = 512;
+constexpr int kNS = 2;    // tensor-memory A slots; a slot holds a pair of K blocks (64 columns)
+constexpr int kBStage = kTcTileN * 128;  // bytes of one K block of activations: rows x 64 halfs
+constexpr int kThreads = 768;           // 24 warps: 4 service, 16 dequantising, 4 epilogue
 constexpr int kAccCols = kTcTileN;       // columns per accumulator
-constexpr int kTmemA = 2 * kAccCols;     // first column of the A stages (384)
+constexpr int kTmemA = 2 * kAccCols;     // first column of the A slots (384)
 
 // Shared-memory map in ABSOLUTE addresses of the CTA's shared window (the dynamic
-// allocation starts at 1 KB when the kernel has no static shared memory). The pair table
-// sits exactly at 64 KB so that the address of a lookup is a single byte permute:
-//   address = 0x00010000 | code byte << 8 | table half << 7 | lane << 2
-// i.e. entry stride 256 B = [table of tile rows 0..63: 32 lanes x 4 B][rows 64..127: 32 x 4 B].
-constexpr int kOffW = 2048;                          // packed weight stages
-constexpr int kOffU = kOffW + kNW * kWStage;         // SwiGLU exchange buffer (8 KB)
-constexpr int kOffBar = kOffU + 2 * 32 * 32 * 4;     // barriers and flags (512 B)
-constexpr int kOffLut = 65536;                       // pair tables (64 KB)
-constexpr int kOffB = 131072;                        // activation stages, 1 KB aligned
-constexpr int kSmemEnd = kOffB + kNB * kBStage;      // 229376
-constexpr int kSmemBytes = kSmemEnd - 1024;          // dynamic bytes requested
-static_assert(kOffBar + 512 <= kOffLut, "low region overflows into the pair tables");
-static_assert(kSmemEnd <= 233472, "shared memory map exceeds the SM");
+// allocation starts at 1 KB when the kernel has no static shared memory). A pair table is
+// 256 entries x 32 lanes x 4 B and sits on a 32 KB boundary, so that a lookup address is
+//   table | code byte << 7 | lane << 2        (one shift, one and-or).
+// DUAL: tile rows 0..63 and 64..127 use different code books (the shared expert's separate
+// gate and up tensors); otherwise one table serves all rows and the space goes to a third
+// activation slot.
+template <bool DUAL>
+struct Map {
+  static constexpr int kNBS = DUAL ? 2 : 3;            // activation ring depth, in pairs of K blocks
+  static constexpr int kOffLow = 2048;                 // the dynamic allocation must start at or below this
+  static constexpr int kOffLut0 = 32768;
+  static constexpr int kOffLut1 = DUAL ? 65536 : 32768;
+  static constexpr int kOffU = DUAL ? 98304 : 65536;   // epilogue exchange + output tile (12 KB)
+  static constexpr int kOffBar = kOffU + 12288;        // barriers and flags (1 KB)
+  static constexpr int kOffB = kOffBar + 1024;         // activation ring, 1 KB aligned
+  static constexpr int kSmemEnd = kOffB + kNBS * 2 * kBStage;
+  static constexpr int kSmemBytes = kSmemEnd - 1024;   // dynamic bytes requested
+  static_assert(kSmemEnd <= 233472, "shared memory map exceeds the SM");
+};
 
 // barrier slots (8 bytes each) inside the barrier block
-constexpr int kBarWFull = 0, kBarWEmpty = kBarWFull + kNW, kBarBFull = kBarWEmpty + kNW,
-              kBarBEmpty = kBarBFull + kNB, kBarAFull = kBarBEmpty + kNB,
-              kBarAEmpty = kBarAFull + kNA, kBarAccFull = kBarAEmpty + kNA,
+constexpr int kBarAFull = 0,
+              kBarBFull = kBarAFull + kNS, kBarDone = kBarBFull + 3, kBarAccFull = kBarDone + 3,
               kBarAccEmpty = kBarAccFull + 2, kNumBars = kBarAccEmpty + 2;
-static_assert(kNumBars * 8 + 16 + 32 <= 512, "barrier block too small");
+static_assert(kNumBars * 8 + 16 + 32 <= 1024, "barrier block too small");
 
 constexpr long long kWaitLimitNs = 2000000000ll;  // 2 s: far beyond any legitimate wait
 
@@ -95,12 +103,23 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(20000u)  // suspend-time hint (ns): sleep in hardware, not in a poll loop
       : "memory");
   return ok != 0;
+}
+// One lane of a converged warp. Code around it stays warp-uniform, which lets the compiler
+// keep descriptors and addresses in uniform registers instead of converting per instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
@@ -130,13 +149,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                              uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar) {
   asm volatile(
@@ -232,7 +244,7 @@ constexpr int kTraceSlots = 512;
       p.trace[((role) * kTraceSlots + (slot)) * 4 + (ev)] = clock64();                \
   } while (0)
 
-template <bool UP>
+template <bool UP, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
             const __grid_constant__ CUtensorMap map128, const __grid_constant__ CUtensorMap map192,
@@ -242,10 +254,13 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   const uint32_t dyn0 = smem_u32(smem_raw);
   uint8_t* const smem = smem_raw - dyn0;
   constexpr uint32_t sbase = 0;
+  using M = Map<DUAL>;
+  constexpr int kNBS = M::kNBS, kOffLow = M::kOffLow, kOffU = M::kOffU, kOffBar = M::kOffBar, kOffB = M::kOffB,
+                kSmemEnd = M::kSmemEnd;
   {
     uint32_t dyn_size;
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
-    if (dyn0 > (uint32_t)kOffW || dyn0 + dyn_size < (uint32_t)kSmemEnd) {
+    if (dyn0 > (uint32_t)kOffLow || dyn0 + dyn_size < (uint32_t)kSmemEnd) {
       // the fixed map does not fit this launch: refuse (uniform for the whole CTA)
       if (threadIdx.x == 0 && atomicCAS(p.status, 0, 2) == 0) p.status[1] = (int)dyn0;
       return;
@@ -257,22 +272,14 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Image img = p.img;
   const int KB = img.n_kblocks;
-  const int wbytes = tile_bytes(img.fmt);
   const int n_items = p.n_tiles[0] * img.n_mtiles;
 
   // ---- set-up ----
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNW; i++) {
-      mbar_init(bars + 8 * (kBarWFull + i), 1);
-      mbar_init(bars + 8 * (kBarWEmpty + i), 4);
-    }
-    for (int i = 0; i < kNB; i++) {
-      mbar_init(bars + 8 * (kBarBFull + i), 1);
-      mbar_init(bars + 8 * (kBarBEmpty + i), 1);
-    }
-    for (int i = 0; i < kNA; i++) {
-      mbar_init(bars + 8 * (kBarAFull + i), 4);
-      mbar_init(bars + 8 * (kBarAEmpty + i), 1);
+    for (int i = 0; i < kNS; i++) mbar_init(bars + 8 * (kBarAFull + i), 9);  // 8 dequantising warps of a set + relay
+    for (int i = 0; i < kNBS; i++) {
+      mbar_init(bars + 8 * (kBarBFull + i), 1);    // activation producer (with byte count)
+      mbar_init(bars + 8 * (kBarDone + i), 1);     // one tcgen05.commit per pair
     }
     for (int i = 0; i < 2; i++) {
       mbar_init(bars + 8 * (kBarAccFull + i), 1);
@@ -286,7 +293,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   for (int i = threadIdx.x; i < 2 * 256 * 32; i += kThreads) {
     const int half_id = i >> 13, entry = (i >> 5) & 255;
     const float lo = img.book[half_id * 16 + (entry & 15)], hi = img.book[half_id * 16 + (entry >> 4)];
-    *(__half2*)(smem + kOffLut + entry * 256 + half_id * 128 + (i & 31) * 4) = __floats2half2_rn(lo, hi);
+    if (half_id == 0 || DUAL)
+      *(__half2*)(smem + (half_id ? M::kOffLut1 : M::kOffLut0) + entry * 128 + (i & 31) * 4) = __floats2half2_rn(lo, hi);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -300,10 +308,16 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  // K blocks are handled two at a time ("pair"): one barrier wait and one commit of the MMA
+  // thread then cover eight MMAs, which keeps that thread's bookkeeping below the tensor
+  // pipe's time for the pair. A pair owns one slot of the A (tensor memory) and B (shared
+  // memory) rings and one stage of the packed-weight ring; the two dequantising groups work
+  // on the two K blocks of a pair side by side. An odd tail is a pair with one K block.
+  const int NP = (KB + 1) >> 1;
   if (warp == 0) {
     // ================= producer of activation tiles (one tensor copy per K block) =========
     if (lane == 0) {
-      uint32_t kbi = 0;
+      uint32_t pi = 0;
       bool ok = true;
       for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
         const Tile t = p.tiles[it / img.n_mtiles];
@@ -311,104 +325,107 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         // smallest box that covers the tile's rows: 16, 64, 128 or 192 rows of 64 halfs
         const CUtensorMap* map = n_pad <= 16 ? &map16 : n_pad <= 64 ? &map64 : n_pad <= 128 ? &map128 : &map192;
         const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : 192) * 128;
-        for (int kb = 0; kb < KB && ok; kb++, kbi++) {
-          const uint32_t bs = kbi % kNB, bph = (kbi / kNB) & 1;
-          ok = mbar_wait(bars + 8 * (kBarBEmpty + bs), bph ^ 1, abort_flag, p.status, 2, 64);
+        for (int pp = 0; pp < NP && ok; pp++, pi++) {
+          const uint32_t slot = pi % kNBS, sph = (pi / kNBS) & 1;
+          const int nk = min(2, KB - 2 * pp);
+          ok = mbar_wait(bars + 8 * (kBarDone + slot), sph ^ 1, abort_flag, p.status, 2, 64);
           if (!ok) break;
-          TR(0, kbi, 1);
-          const uint32_t bbar = bars + 8 * (kBarBFull + bs);
-          mbar_expect_tx(bbar, bytes);
-          tma_load_2d(sbase + kOffB + bs * kBStage, map, kb * kTileK, t.first, bbar);
-        }
-      }
-    }
-  } else if (warp == 2) {
-    // ================= producer of packed weight tiles (one bulk copy per K block) ========
-    if (lane == 0) {
-      uint32_t kbi = 0;
-      bool ok = true;
-      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-        const Tile t = p.tiles[it / img.n_mtiles];
-        const int mt = it % img.n_mtiles;
-        const uint8_t* src = img.tile(t.expert, mt, 0);
-        for (int kb = 0; kb < KB && ok; kb++, kbi++, src += wbytes) {
-          const uint32_t ws = kbi % kNW, wph = (kbi / kNW) & 1;
-          ok = mbar_wait(bars + 8 * (kBarWEmpty + ws), wph ^ 1, abort_flag, p.status, 1, 64);
-          if (!ok) break;
-          TR(0, kbi, 0);
-          mbar_expect_tx(bars + 8 * (kBarWFull + ws), wbytes);
-          bulk_copy_g2s(sbase + kOffW + ws * kWStage, src, wbytes, bars + 8 * (kBarWFull + ws));
+          TR(0, pi, 1);
+          const uint32_t bar = bars + 8 * (kBarBFull + slot);
+          mbar_expect_tx(bar, nk * bytes);
+          for (int j = 0; j < nk; j++)
+            tma_load_2d(sbase + kOffB + (slot * 2 + j) * kBStage, map, (2 * pp + j) * kTileK, t.first, bar);
         }
       }
     }
   } else if (warp == 1) {
     // ================= MMA issue =================
-    if (lane == 0) {
-      uint32_t kbi = 0, li = 0;
-      bool ok = true;
-      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, li++) {
-        const Tile t = p.tiles[it / img.n_mtiles];
-        const int n_pad = (t.count + 15) & ~15;
-        const uint32_t idesc = instr_desc(n_pad);
-        const uint32_t acc = li & 1, accph = (li >> 1) & 1;
-        ok = mbar_wait(bars + 8 * (kBarAccEmpty + acc), accph ^ 1, abort_flag, p.status, 3);
+    // The whole warp runs the loop (converged); one elected lane issues.
+    uint32_t pi = 0, li = 0;
+    bool ok = true;
+    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, li++) {
+      const Tile t = p.tiles[it / img.n_mtiles];
+      const int n_pad = (t.count + 15) & ~15;
+      const uint32_t idesc = instr_desc(n_pad);
+      const uint32_t acc = li & 1, accph = (li >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarAccEmpty + acc), accph ^ 1, abort_flag, p.status, 3));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + acc * kAccCols;
+      for (int pp = 0; pp < NP && ok; pp++, pi++) {
+        const uint32_t aslot = pi % kNS, aph = (pi / kNS) & 1, bslot = pi % kNBS;
+        const int nk = min(2, KB - 2 * pp);
+        // one wait covers both operands: the relay thread arrives only after the
+        // activation tiles of this pair have landed
+        if (lane == 0) TR(1, pi, 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBarAFull + aslot), aph, abort_flag, p.status, 4));
         if (!ok) break;
+        if (lane == 0) TR(1, pi, 0);
         tc_fence_after();
-        const uint32_t d_tmem = tmem + acc * kAccCols;
-        for (int kb = 0; kb < KB && ok; kb++, kbi++) {
-          const uint32_t bs = kbi % kNB, bph = (kbi / kNB) & 1;
-          const uint32_t as = kbi % kNA, aph = (kbi / kNA) & 1;
-          ok = mbar_wait(bars + 8 * (kBarBFull + bs), bph, abort_flag, p.status, 4);
-          if (!ok) break;
-          TR(1, kbi, 0);
-          ok = mbar_wait(bars + 8 * (kBarAFull + as), aph, abort_flag, p.status, 5);
-          if (!ok) break;
-          TR(1, kbi, 1);
-          tc_fence_after();
-          const uint64_t bdesc = b_descriptor(sbase + kOffB + bs * kBStage);
-          const uint32_t a_tmem = tmem + kTmemA + as * 32;
+        const uint64_t bdesc = b_descriptor(sbase + kOffB + bslot * 2 * kBStage);
+        const uint32_t a_tmem = tmem + kTmemA + aslot * 64;
+        if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < 4; ks++)
-            tc_mma_ts(d_tmem, a_tmem + ks * 8, bdesc + (uint64_t)(ks * 2), idesc,
-                      (kb | ks) != 0 ? 1u : 0u);
-          TR(1, kbi, 3);
-          tc_commit(bars + 8 * (kBarAEmpty + as));
-          tc_commit(bars + 8 * (kBarBEmpty + bs));
-          TR(1, kbi, 2);
+            tc_mma_ts(d_tmem, a_tmem + ks * 8, bdesc + (uint64_t)(ks * 2), idesc, (pp | ks) != 0 ? 1u : 0u);
+          if (nk == 2) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++)
+              tc_mma_ts(d_tmem, a_tmem + 32 + ks * 8, bdesc + (uint64_t)((kBStage >> 4) + ks * 2), idesc, 1u);
+          }
+          // one commit per pair: frees the activation slot for the producer and, two pairs
+          // later, the tensor-memory slot for the dequantising warps
+          tc_commit(bars + 8 * (kBarDone + bslot));
+          if (pp == NP - 1) tc_commit(bars + 8 * (kBarAccFull + acc));
         }
-        if (ok) tc_commit(bars + 8 * (kBarAccFull + acc));
+        __syncwarp();
+        if (lane == 0) TR(1, pi, 2);
       }
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < 20) {
     // ================= dequantise into tensor memory =================
-    const int grp = (warp - 4) >> 2, quarter = warp & 3;
+    // Sixteen warps = two sets of eight. Set s serves the pairs with index == s (mod 2) and
+    // therefore always fills tensor-memory slot s: while one set waits for its slot and
+    // stores, the other decodes. Inside a set, a group of four warps (one per 32-lane quarter
+    // of tensor memory) owns one K block of the pair; a thread decodes the 64 codes of its
+    // weight row for that K block and stores 32 columns.
+    // Packed codes come straight from global memory (the tile layout makes a warp's 32 rows
+    // one contiguous 512-byte read per half), one own pair ahead of their use.
+    const int set = (warp - 4) >> 3, kblk = ((warp - 4) >> 2) & 1, quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const uint32_t lut = (uint32_t)kOffLut | (uint32_t)((r >= 64 ? 128 : 0) + lane * 4);
-    uint32_t kbi = 0;
+    const uint32_t lut = (uint32_t)(r >= 64 ? M::kOffLut1 : M::kOffLut0) | (uint32_t)(lane * 4);
+    const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const uint32_t total = (uint32_t)my_items * (uint32_t)NP;
+    uint4 ca = make_uint4(0, 0, 0, 0), cb = ca, na = ca, nb = ca;
+    uint32_t sc = 0, nsc = 0;
+    auto fetch = [&](uint32_t pj, uint4& a, uint4& b, uint32_t& s2x) {
+      if (pj >= total) return;
+      const int item = blockIdx.x + (int)(pj / (uint32_t)NP) * gridDim.x, kb = 2 * (int)(pj % (uint32_t)NP) + kblk;
+      if (kb >= KB) return;
+      const uint8_t* tp = img.tile(p.tiles[item / img.n_mtiles].expert, item % img.n_mtiles, kb);
+      a = __ldg((const uint4*)(tp + r * 16));
+      b = __ldg((const uint4*)(tp + 2048 + r * 16));
+      s2x = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
+    };
+    fetch(set, ca, cb, sc);
     bool ok = true;
-    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-      for (int kb = 0; kb < KB && ok; kb++, kbi++) {
-        if ((int)(kbi & 1) != grp) continue;
-        const uint32_t ws = kbi % kNW, wph = (kbi / kNW) & 1;
-        ok = mbar_wait(bars + 8 * (kBarWFull + ws), wph, abort_flag, p.status, 6, 32);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 0);
-        const uint8_t* wt = smem + kOffW + ws * kWStage;
-        uint32_t v[32];
-        const uint32_t sc = *(const uint32_t*)(wt + kCodeBytes + r * 4);
+    for (uint32_t pi = set; pi < total && ok; pi += 2) {
+      const bool mine = 2 * (int)(pi % (uint32_t)NP) + kblk < KB;  // false only for the second K block of an odd tail
+      fetch(pi + 2, na, nb, nsc);
+      if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 0);
+      uint32_t v[32];
+      if (mine) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-          const uint4 c4 = *(const uint4*)(wt + h * 2048 + r * 16);
-          const uint32_t w4[4] = {c4.x, c4.y, c4.z, c4.w};
           const uint32_t s16 = h ? (sc >> 16) : (sc & 0xFFFFu);
           const uint32_t s2 = s16 | (s16 << 16);
+          const uint4 c4 = h ? cb : ca;
+          const uint32_t w4[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
           for (int q = 0; q < 4; q++) {
 #pragma unroll
             for (int b = 0; b < 4; b++) {
-              // bytes (3,2,1,0) of the address = (table.3, table.2, code byte b, table.0)
-              const uint32_t addr = __byte_perm(w4[q], lut, 0x7604 | (b << 4));
+              const uint32_t addr = ((b == 0 ? w4[q] << 7 : w4[q] >> (8 * b - 7)) & 0x7F80u) | lut;
               uint32_t pair;
               asm("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(addr));
               __half2 w2 = __hmul2(*(__half2*)&pair, *(const __half2*)&s2);
@@ -416,24 +433,48 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
             }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + 8 * (kBarWEmpty + ws));
-        const uint32_t as = kbi % kNA, aph = (kbi / kNA) & 1;
-        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 1);
-        ok = mbar_wait(bars + 8 * (kBarAEmpty + as), aph ^ 1, abort_flag, p.status, 7, 32);
+      }
+      if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 1);
+      if (pi >= (uint32_t)kNS) {
+        // the slot is free once the MMAs of this set's previous pair have completed
+        const uint32_t q = pi - kNS;
+        ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 7);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 2);
+      }
+      if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 2);
+      if (mine) {
         tc_fence_after();
-        tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + as * 32, v);
+        tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + set * 64 + kblk * 32, v);
         tc_wait_st();
-        if (lane == 0 && quarter == 0) TR(2 + grp, kbi, 3);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + as));
+      }
+      if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 3);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + set));
+      ca = na;
+      cb = nb;
+      sc = nsc;
+    }
+  } else if (warp == 3) {
+    // ================= relay: "activations landed" folded into the A-slot barrier ==========
+    if (lane == 0) {
+      uint32_t pi = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+        for (int pp = 0; pp < NP && ok; pp++, pi++) {
+          ok = mbar_wait(bars + 8 * (kBarBFull + pi % kNBS), (pi / kNBS) & 1, abort_flag, p.status, 9);
+          if (!ok) break;
+          if (pi >= (uint32_t)kNS) {
+            const uint32_t q = pi - kNS;
+            ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 10);
+            if (!ok) break;
+          }
+          mbar_arrive(bars + 8 * (kBarAFull + pi % kNS));
+        }
       }
     }
-  } else if (warp >= 12) {
+  } else if (warp >= 20) {
     // ================= epilogue =================
     const int quarter = warp & 3;
     float* ubuf = (float*)(smem + kOffU);
@@ -456,33 +497,63 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       if (lane == 0 && quarter == 0) TR(4, li, 0);
       tc_fence_after();
       const uint32_t src = tmem + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols;
+      // Results leave through a shared-memory tile [column = row of the expert][weight row]
+      // so that every global store is a full 16-byte piece of one output row.
+      const int e128 = quarter * 32 + lane;
       for (int c0 = 0; c0 < t.count; c0 += 32) {
         uint32_t v[32];
         tc_ld32(src + c0, v);
         tc_wait_ld();
         if (UP) {
-          if (quarter >= 2) {
+          // gate rows live in lanes 0..63 (warps 0,1), the matching up rows in lanes 64..127
+          // (warps 2,3). Each side hands half of its columns to its partner so that all four
+          // warps share the SwiGLU arithmetic: gate warps finish columns 0..15, up warps 16..31.
+          float* xg = ubuf;                 // [2][16][32] gate values of columns 16..31
+          float* xu = ubuf + 2 * 16 * 32;   // [2][16][32] up values of columns 0..15
+          __half* outs = (__half*)(ubuf + 4 * 16 * 32);  // [32][64]
+          const int pq = quarter & 1;
+          if (quarter < 2) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) ubuf[((quarter - 2) * 32 + j) * 32 + lane] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; j++) xg[(pq * 16 + j) * 32 + lane] = __uint_as_float(v[16 + j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) xu[(pq * 16 + j) * 32 + lane] = __uint_as_float(v[j]);
           }
           asm volatile("bar.sync 2, 128;" ::: "memory");
           if (quarter < 2) {
-            __half* dst = p.out + (size_t)(t.first + c0) * p.out_ld + mt * 64 + quarter * 32 + lane;
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-              if (c0 + j < t.count) {
-                const float g = __uint_as_float(v[j]);
-                const float u = ubuf[(quarter * 32 + j) * 32 + lane];
-                dst[(size_t)j * p.out_ld] = __float2half_rn(silu_f32(g) * u);
-              }
+            for (int j = 0; j < 16; j++) {
+              const float g = __uint_as_float(v[j]), u = xu[(pq * 16 + j) * 32 + lane];
+              outs[j * 64 + pq * 32 + lane] = __float2half_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              const float u = __uint_as_float(v[16 + j]), g = xg[(pq * 16 + j) * 32 + lane];
+              outs[(16 + j) * 64 + pq * 32 + lane] = __float2half_rn(__fdividef(g, 1.f + __expf(-g)) * u);
             }
           }
           asm volatile("bar.sync 3, 128;" ::: "memory");
-        } else {
-          __half* dst = p.out + (size_t)(t.first + c0) * p.out_ld + mt * 128 + quarter * 32 + lane;
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            if (c0 + j < t.count) dst[(size_t)j * p.out_ld] = __float2half_rn(__uint_as_float(v[j]));
+          for (int k = 0; k < 2; k++) {
+            const int piece = e128 + 128 * k, col = piece >> 3, seg = piece & 7;
+            if (c0 + col < t.count)
+              *(uint4*)(p.out + (size_t)(t.first + c0 + col) * p.out_ld + mt * 64 + seg * 8) =
+                  *(const uint4*)(outs + col * 64 + seg * 8);
+          }
+        } else {
+          __half* outs = (__half*)ubuf;  // [32][128]
+#pragma unroll
+          for (int j = 0; j < 32; j++) outs[j * 128 + e128] = __float2half_rn(__uint_as_float(v[j]));
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const int piece = e128 + 128 * k, col = piece >> 4, seg = piece & 15;
+            if (c0 + col < t.count)
+              *(uint4*)(p.out + (size_t)(t.first + c0 + col) * p.out_ld + mt * 128 + seg * 8) =
+                  *(const uint4*)(outs + col * 128 + seg * 8);
+          }
+          asm volatile("bar.sync 3, 128;" ::: "memory");
         }
       }
       if (lane == 0 && quarter == 0) TR(4, li, 1);
@@ -519,23 +590,24 @@ cudaError_t encode_2d(PFN_cuTensorMapEncodeTiled_v12000 enc, CUtensorMap* map, c
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <bool UP>
+template <bool UP, bool DUAL>
 cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
                    const Tile* tiles, const int32_t* n_tiles, int max_tiles, __half* out, int out_ld,
                    int32_t* status, cudaStream_t st) {
   if (img.fmt != kQ4CP) return cudaErrorNotSupported;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[UP]) {
-    cudaError_t e = cudaFuncSetAttribute(k_expert_tc<UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  constexpr int kSmemBytes = Map<DUAL>::kSmemBytes;
+  static bool attr_set = false;  // one flag per template instance
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(k_expert_tc<UP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes);
     if (e != cudaSuccess) return e;
-    attr_set[UP] = true;
+    attr_set = true;
   }
   KParams p{img, tiles, n_tiles, out, out_ld, status, UP ? plan->trace : nullptr};
   long long max_items = (long long)max_tiles * img.n_mtiles;
   int grid = (int)(max_items < plan->sms ? max_items : plan->sms);
   if (grid < 1) grid = 1;
-  k_expert_tc<UP><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
+  k_expert_tc<UP, DUAL><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
   return cudaGetLastError();
 }
 
@@ -590,13 +662,15 @@ void tc_destroy(TcPlan* plan) {
 
 cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                          int max_tiles, __half* hid16, int32_t* status, cudaStream_t st) {
-  return launch<true>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16,
+  if (img.dual_book)
+    return launch<true, true>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
+  return launch<true, false>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16,
                       img.n_mtiles * 64, status, st);
 }
 
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                            int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st) {
-  return launch<false>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
+  return launch<false, false>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
                        img.n_mtiles * 128, status, st);
 }
 
