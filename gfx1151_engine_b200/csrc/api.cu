@@ -37,6 +37,7 @@ struct b200moe_ctx {
   void* hid = nullptr;      // [rows][mid] fp32 (GEMV path) or fp16 (tensor-core path)
   void* pairs = nullptr;    // [rows][d]   fp32 or fp16
   __half* x_sorted = nullptr;
+  int dec_rows = 0;
   void *x_stage = nullptr, *out_stage = nullptr;
   float* logits_stage = nullptr;
   int32_t* status_dev = nullptr;
@@ -224,6 +225,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   A((uint8_t**)&h->hid, hid_bytes);
   A((uint8_t**)&h->pairs, pair_bytes);
   if (!simt_all) A(&h->x_sorted, rows * d);
+  h->dec_rows = (int)dec_rows;
   A((uint8_t**)&h->x_stage, (size_t)Tm * d * 2);
   A((uint8_t**)&h->out_stage, (size_t)Tm * d * 2);
   A(&h->logits_stage, (size_t)Tm * E);
@@ -439,9 +441,10 @@ int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw
   return B200MOE_OK;
 }
 
+// logits != nullptr: the router has not run yet (the fused small-T routing kernel runs it).
 static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const int32_t* ids,
                         const float* w, int stride, void* out, cudaStream_t st,
-                        bool router_timed = false) {
+                        bool router_timed = false, const float* logits = nullptr) {
   const b200moe_config& c = h->cfg;
   LayerWeights& L = h->layers[layer];
   const int k = c.topk, E = c.experts, d = c.d_model, mid = c.d_mid;
@@ -455,10 +458,23 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     // ev[0] was recorded by the caller of forward_impl (before the router) when it ran one
     if (!router_timed) CU_TRY(h, cudaEventRecord(ev[0], st));
   }
-  CU_TRY(h, launch_route(h->rb, ids, w, stride, T, k, E, h->tile_cap, st, &n));
-  if (shared) {
-    CU_TRY(h, launch_shared_gate(x, L.sh_gate_w, T, d, k, h->rb, st));
+  if (T * k <= route_small_max_pairs() && T <= 16) {
+    CU_TRY(h, launch_route_small(h->rb, logits, ids, w, stride, T, k, E, x, shared ? L.sh_gate_w : nullptr,
+                                 d, st));
     n++;
+  } else {
+    if (logits) {
+      CU_TRY(h, launch_router_topk(logits, T, E, k, h->rb.topids, h->rb.topw, kIdStride, st));
+      n++;
+      ids = h->rb.topids;
+      w = h->rb.topw;
+      stride = kIdStride;
+    }
+    CU_TRY(h, launch_route(h->rb, ids, w, stride, T, k, E, h->tile_cap, st, &n));
+    if (shared) {
+      CU_TRY(h, launch_shared_gate(x, L.sh_gate_w, T, d, k, h->rb, st));
+      n++;
+    }
   }
   if (ev) CU_TRY(h, cudaEventRecord(ev[1], st));
   const int pairs = T * k;
@@ -470,7 +486,22 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
                 "B200MOE_GEMM_SIMT for GGUF experts at T > decode_max_tokens");
   if (simt && c.gemm_impl != B200MOE_GEMM_SIMT && T > h->decode_max)
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
-  if (simt) {
+  const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO && L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP &&
+                    pairs + (shared ? T : 0) <= h->dec_rows && std::min(E, pairs) + 1 <= gemv_max_runs() &&
+                    d <= gemv_max_k() && mid <= gemv_max_k() && d % 32 == 0 && mid % 32 == 0;
+  if (gemv) {
+    // decode / verify: persistent dequant GEMV, routed and shared expert in one launch each
+    if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
+    CU_TRY(h, launch_up_gemv(L.gu, shared ? &L.sh_gu : nullptr, x, d, mid, h->rb.tokidx, h->rb.runs,
+                             h->rb.n_runs, (float*)h->hid, st));
+    if (ev) CU_TRY(h, cudaEventRecord(ev[3], st));
+    CU_TRY(h, launch_down_gemv(L.dn, shared ? &L.sh_dn : nullptr, (const float*)h->hid, d, mid, h->rb.runs,
+                               h->rb.n_runs, (float*)h->pairs, st));
+    if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
+    CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
+                                 shared ? pairs : -1, out, st));
+    n += 3;
+  } else if (simt) {
     const int max_runs = std::min(E, pairs);
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
     CU_TRY(h, launch_up_simt(L.gu, x, d, mid, h->rb.tokidx, h->rb.runs, h->rb.n_runs, max_runs,
@@ -539,11 +570,8 @@ int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
   if (T == 0) return B200MOE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (h->prof) CU_TRY(h, cudaEventRecord(h->prof_ev[(size_t)h->prof_head * kProfEvents], st));
-  CU_TRY(h, launch_router_topk(logits_dev, T, h->cfg.experts, h->cfg.topk, h->rb.topids, h->rb.topw,
-                               kIdStride, st));
-  h->launches++;
   return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st,
-                      h->prof);
+                      h->prof, logits_dev);
 }
 
 int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, int T,

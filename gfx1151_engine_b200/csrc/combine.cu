@@ -28,7 +28,7 @@ __device__ __forceinline__ void load8(const __half* p, float* v) {
   }
 }
 
-// One block per token; each thread owns 8 consecutive columns per step.
+// One block per (token, 2048-column slice); each thread owns 8 consecutive columns.
 template <typename TP>
 __global__ void __launch_bounds__(256)
 k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
@@ -51,7 +51,7 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
     n = k + 1;
   }
   __syncthreads();
-  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < d; c += gridDim.y * blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int s = 0; s < n; s++) {
       float v[8];
@@ -96,13 +96,13 @@ k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx,
 
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
-  k_combine<float><<<T, 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+  k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
   return cudaGetLastError();
 }
 
 cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
-  k_combine<__half><<<T, 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0,
+  k_combine<__half><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0,
                                        (__nv_bfloat16*)out_bf16);
   return cudaGetLastError();
 }

@@ -42,6 +42,12 @@ cudaError_t launch_router_topk(const float* logits, int T, int E, int k, int32_t
                                int stride, cudaStream_t st);
 cudaError_t launch_route(const RouteBuffers& rb, const int32_t* ids, const float* w, int stride,
                          int T, int k, int E, int tile_cap, cudaStream_t st, int* launches);
+// Whole routing stage in one launch for T*k <= route_small_max_pairs(): logits != nullptr runs
+// the router too (ids/w ignored), gate_w_bf16 != nullptr adds the shared expert's gate.
+int route_small_max_pairs();
+cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, const int32_t* ids,
+                               const float* w, int stride, int T, int k, int E, const void* x_bf16,
+                               const uint16_t* gate_w_bf16, int d, cudaStream_t st);
 cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, int T, int d,
                                int k, const RouteBuffers& rb, cudaStream_t st);
 
@@ -52,6 +58,16 @@ cudaError_t launch_up_simt(const Image& img, const void* x_bf16, int d, int mid,
 cudaError_t launch_down_simt(const Image& img, const float* hid_f32, int d, int mid, const Run* runs,
                              const int32_t* n_runs, int max_runs, float* pairs_f32,
                              cudaStream_t st);
+
+// ---- expert_gemv.cu (q4cp decode / verify path) ----
+int gemv_max_runs();
+int gemv_max_k();
+// img_sh: the shared expert's image (nullptr: none); its run is runs[kMaxExperts].
+cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_bf16, int d, int mid,
+                           const int32_t* tokidx, const Run* runs, const int32_t* n_runs,
+                           float* hid_f32, cudaStream_t st);
+cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const float* hid_f32, int d, int mid,
+                             const Run* runs, const int32_t* n_runs, float* pairs_f32, cudaStream_t st);
 
 // ---- combine.cu ----
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,

@@ -28,15 +28,11 @@ __device__ __forceinline__ double shfl_double(double v, int src) {
   return __hiloint2double(hi, lo);
 }
 
-// One warp per token, E <= 512: lane holds experts lane, lane+32, ...
-__global__ void __launch_bounds__(kRouterWarps * 32)
-k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __restrict__ ids,
-              float* __restrict__ w, int stride) {
-  __shared__ float s_p[kRouterWarps][kMaxExperts];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouterWarps + warp;
-  if (t >= T) return;
-  const float* lg = logits + (size_t)t * E;
+// Router for one token by one warp, E <= 512: lane holds experts lane, lane+32, ...
+// sp: this warp's scratch row of kMaxExperts floats in shared memory.
+__device__ __forceinline__ void router_one_token(const float* __restrict__ lg, int E, int k, int lane,
+                                                 float* sp, int32_t* __restrict__ ids_row,
+                                                 float* __restrict__ w_row, int stride) {
   float v[16];
   float mx = -INFINITY;
 #pragma unroll
@@ -52,13 +48,13 @@ k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __
   for (int j = 0; j < 16; j++) {
     int e = j * 32 + lane;
     float p = e < E ? (float)exp((double)v[j] - dmx) : 0.f;
-    if (e < E) s_p[warp][e] = p;
+    if (e < E) sp[e] = p;
     v[j] = p;
   }
   __syncwarp();
   double se = 0;
   if (lane == 0)
-    for (int i = 0; i < E; i++) se += (double)s_p[warp][i];  // index order, as the reference sums
+    for (int i = 0; i < E; i++) se += (double)sp[i];  // index order, as the reference sums
   se = shfl_double(se, 0);
 #pragma unroll
   for (int j = 0; j < 16; j++) {
@@ -98,8 +94,112 @@ k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __
   for (int i = lane; i < stride; i += 32) {
     // lanes >= k hold zeros; stride > 32 is padded with zeros as well
     bool valid = i < k && i < 32;
-    ids[(size_t)t * stride + i] = valid ? my_id : 0;
-    w[(size_t)t * stride + i] = valid ? (float)((double)my_p / kept) : 0.f;
+    ids_row[i] = valid ? my_id : 0;
+    w_row[i] = valid ? (float)((double)my_p / kept) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(kRouterWarps * 32)
+k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __restrict__ ids,
+              float* __restrict__ w, int stride) {
+  __shared__ float s_p[kRouterWarps][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouterWarps + warp;
+  if (t >= T) return;
+  router_one_token(logits + (size_t)t * E, E, k, lane, s_p[warp], ids + (size_t)t * stride,
+                   w + (size_t)t * stride, stride);
+}
+
+// Decode / verify (T*k <= 256): the whole routing stage in ONE block -- router top-k (when
+// logits are given), stable bucketing by rank counting, expert offsets, run and tile lists,
+// and the shared expert's sigmoid gate. Same results as the general kernels below.
+constexpr int kSmallPairs = 256;
+__global__ void __launch_bounds__(kMaxExperts)
+k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_in,
+              const float* __restrict__ w_in, int stride_in, int T, int E, int k, RouteBuffers rb,
+              const uint16_t* __restrict__ x, const uint16_t* __restrict__ gw, int d) {
+  __shared__ float s_p[16][kMaxExperts];  // 32 KB: router scratch, one row per warp
+  __shared__ int s_key[kSmallPairs];
+  __shared__ float s_w[kSmallPairs];
+  __shared__ int s_wcnt[17];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int P = T * k;
+  if (logits) {
+    for (int t = warp; t < T; t += 16)
+      router_one_token(logits + (size_t)t * E, E, k, lane, s_p[warp], rb.topids + (size_t)t * kIdStride,
+                       rb.topw + (size_t)t * kIdStride, kIdStride);
+    __syncthreads();
+    ids_in = rb.topids;
+    w_in = rb.topw;
+    stride_in = kIdStride;
+  }
+  for (int p = tid; p < P; p += blockDim.x) {
+    s_key[p] = ids_in[(size_t)(p / k) * stride_in + p % k];
+    s_w[p] = w_in[(size_t)(p / k) * stride_in + p % k];
+  }
+  __syncthreads();
+  // pair p -> row = number of pairs ordered before it by (expert, p)
+  if (tid < P) {
+    const int key = s_key[tid], t = tid / k;
+    int row = 0, rank = 0;
+    for (int q = 0; q < P; q++) {
+      const int kq = s_key[q];
+      row += (kq < key) || (kq == key && q < tid);
+    }
+    for (int q = t * k; q < t * k + k; q++) rank += s_key[q] < key;
+    rb.tokidx[row] = t;
+    rb.pw[row] = s_w[tid];
+    rb.pairids[(size_t)t * k + rank] = row;
+  }
+  // expert e: offset, count, position among the non-empty experts
+  int cnt = 0, lt = 0;
+  if (tid < E)
+    for (int q = 0; q < P; q++) {
+      const int kq = s_key[q];
+      cnt += kq == tid;
+      lt += kq < tid;
+    }
+  const unsigned active = __ballot_sync(0xffffffffu, cnt > 0);
+  if (lane == 0) s_wcnt[warp] = __popc(active);
+  __syncthreads();
+  int before = __popc(active & ((1u << lane) - 1u)), n_active = 0;
+  for (int w2 = 0; w2 < 16; w2++) {
+    if (w2 < warp) before += s_wcnt[w2];
+    n_active += s_wcnt[w2];
+  }
+  if (tid < E) rb.eoff[tid] = lt;
+  if (cnt > 0) {
+    rb.runs[before] = Run{tid, lt, cnt};
+    rb.tiles[before] = Tile{tid, lt, cnt};
+  }
+  if (tid == 0) {
+    rb.eoff[E] = P;
+    rb.n_runs[0] = n_active;
+    rb.n_runs[1] = 1;
+    rb.runs[kMaxExperts] = Run{0, P, T};
+    rb.n_tiles[0] = n_active;
+    rb.n_tiles[1] = 1;
+    rb.tiles_sh[0] = Tile{0, P, T};
+  }
+  // scalar sigmoid gate of the shared expert and its rows behind the routed ones
+  if (gw) {
+    for (int t = warp; t < T; t += 16) {
+      double a = 0;
+      for (int c = lane; c < d; c += 32)
+        a += (double)bf16_bits_to_f32(gw[c]) * (double)bf16_bits_to_f32(x[(size_t)t * d + c]);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        int lo = __shfl_xor_sync(0xffffffffu, __double2loint(a), o);
+        int hi = __shfl_xor_sync(0xffffffffu, __double2hiint(a), o);
+        a += __hiloint2double(hi, lo);
+      }
+      if (lane == 0) {
+        const float gate = sigmoid_f32((float)a);
+        rb.sgate[t] = gate;
+        rb.tokidx[P + t] = t;
+        rb.pw[P + t] = gate;
+      }
+    }
   }
 }
 
@@ -272,6 +372,15 @@ cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, 
   return cudaGetLastError();
 }
 
+cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, const int32_t* ids,
+                               const float* w, int stride, int T, int k, int E, const void* x_bf16,
+                               const uint16_t* gate_w_bf16, int d, cudaStream_t st) {
+  k_route_small<<<1, kMaxExperts, 0, st>>>(logits, ids, w, stride, T, E, k, rb, (const uint16_t*)x_bf16,
+                                           gate_w_bf16, d);
+  return cudaGetLastError();
+}
+
+int route_small_max_pairs() { return kSmallPairs; }
 int route_chunk() { return kChunk; }
 
 }  // namespace b200moe

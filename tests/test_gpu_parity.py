@@ -204,8 +204,8 @@ def test_decode_and_verify_with_shared_expert(cuda, T):
     y = run_layer(torch, op, spec, xb, logits)
     assert np.array_equal(op.get_routing(T)[0][:, :spec.topk], ids_o[:, :spec.topk])
     max_abs, mean_rel = assert_output_close(y, y_o, "decode T=%d" % T)
-    # the fp32 path is far inside the tolerance: errors come from bf16 output rounding only
-    assert mean_rel < 1e-4
+    # fp16 operands with fp32 scaling and accumulation: well inside the 1e-3 bar
+    assert mean_rel < 7e-4
 
 
 def test_prefill_zipf_tc_vs_oracle_and_simt(cuda):
