@@ -344,6 +344,11 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
     e = launch_repack(L.gu, sg, su, (int)d, e0, 0);
     h->launches++;
   }
+  // the tensor-core path decodes a code byte through the same pair table as q4cp: for the
+  // GGUF formats the "book" is the code itself (0..15), scale and offset are applied after
+  float ident[32];
+  for (int i = 0; i < 32; i++) ident[i] = (float)(i & 15);
+  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, ident, sizeof ident, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   free_all(tmp);
   if (e == cudaSuccess) e = stage(down_src, dn_bytes, &dn, tmp);
@@ -355,6 +360,7 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
     e = launch_repack(L.dn, a, a, (int)mid, e0, 0);
     h->launches++;
   }
+  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, ident, sizeof ident, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   free_all(tmp);
   if (e != cudaSuccess) {
@@ -480,10 +486,6 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   const int pairs = T * k;
   const bool simt = c.gemm_impl == B200MOE_GEMM_SIMT ||
                     (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max);
-  if (!simt && (L.gu.fmt != kQ4CP || L.dn.fmt != kQ4CP))
-    return fail(h, B200MOE_ERR_UNSUPPORTED,
-                "tensor-core path implements q4cp experts only; create the handle with "
-                "B200MOE_GEMM_SIMT for GGUF experts at T > decode_max_tokens");
   if (simt && c.gemm_impl != B200MOE_GEMM_SIMT && T > h->decode_max)
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
   const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO && L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP &&

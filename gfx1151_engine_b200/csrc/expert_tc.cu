@@ -244,7 +244,54 @@ constexpr int kTraceSlots = 512;
       p.trace[((role) * kTraceSlots + (slot)) * 4 + (ev)] = clock64();                \
   } while (0)
 
-template <bool UP, bool DUAL>
+// Per (row, K block) metadata of the source format, as loaded by a dequantising thread.
+struct RowMetaTc {
+  uint32_t a, b, c, d;
+};
+
+// Two fp16 weights from one code byte's table entry `pair` (the two codes as fp16 numbers
+// for the GGUF formats, the two code-book values for q4cp) and the group's constants.
+template <int FMT>
+struct GroupDecode {};
+template <>
+struct GroupDecode<kQ4CP> {  // w = f16(book) * f16(scale)
+  __half2 s2;
+  __device__ __forceinline__ void init(const RowMetaTc& m, int h) {
+    const uint32_t s16 = h ? (m.a >> 16) : (m.a & 0xFFFFu), v = s16 | (s16 << 16);
+    s2 = *(const __half2*)&v;
+  }
+  __device__ __forceinline__ __half2 weight(uint32_t pair, int) const { return __hmul2(*(__half2*)&pair, s2); }
+};
+template <>
+struct GroupDecode<kQ4K> {  // w = (d*sc)*q - (dmin*m), the packed form of src/gguf.h:423-432
+  __half2 a2, nb2;
+  __device__ __forceinline__ void init(const RowMetaTc& m, int h) {
+    const float d = half_bits_to_f32((uint16_t)(m.a & 0xFFFFu)), dmin = half_bits_to_f32((uint16_t)(m.a >> 16));
+    const float sc = (float)((m.b >> (16 * h)) & 0xFFu), mn = (float)((m.b >> (16 * h + 8)) & 0xFFu);
+    a2 = __float2half2_rn(d * sc);
+    nb2 = __float2half2_rn(-(dmin * mn));
+  }
+  __device__ __forceinline__ __half2 weight(uint32_t pair, int) const { return __hfma2(*(__half2*)&pair, a2, nb2); }
+};
+template <>
+struct GroupDecode<kQ51> {  // w = d*(q + 16*fifth bit) + m, src/gguf.h:360-374
+  __half2 d2, m2;
+  uint32_t qh;
+  __device__ __forceinline__ void init(const RowMetaTc& m, int h) {
+    const uint32_t dm = h ? m.c : m.a;
+    qh = h ? m.d : m.b;
+    d2 = __half2half2(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
+    m2 = __half2half2(__ushort_as_half((unsigned short)(dm >> 16)));
+  }
+  // byte i of the group holds elements 2i, 2i+1; their fifth bits are bits 2i, 2i+1 of qh
+  __device__ __forceinline__ __half2 weight(uint32_t pair, int i) const {
+    const uint32_t t = (qh >> (2 * i)) & 3u;
+    const uint32_t hi = (t & 1u) * 0x4C00u + (t >> 1) * 0x4C000000u;  // 16.0 in fp16 where the bit is set
+    return __hfma2(__hadd2(*(__half2*)&pair, *(const __half2*)&hi), d2, m2);
+  }
+};
+
+template <bool UP, bool DUAL, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
             const __grid_constant__ CUtensorMap map128, const __grid_constant__ CUtensorMap map192,
@@ -397,15 +444,24 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t total = (uint32_t)my_items * (uint32_t)NP;
     uint4 ca = make_uint4(0, 0, 0, 0), cb = ca, na = ca, nb = ca;
-    uint32_t sc = 0, nsc = 0;
-    auto fetch = [&](uint32_t pj, uint4& a, uint4& b, uint32_t& s2x) {
+    RowMetaTc sc = RowMetaTc{0, 0, 0, 0}, nsc = sc;
+    auto fetch = [&](uint32_t pj, uint4& a, uint4& b, RowMetaTc& s2x) {
       if (pj >= total) return;
       const int item = blockIdx.x + (int)(pj / (uint32_t)NP) * gridDim.x, kb = 2 * (int)(pj % (uint32_t)NP) + kblk;
       if (kb >= KB) return;
       const uint8_t* tp = img.tile(p.tiles[item / img.n_mtiles].expert, item % img.n_mtiles, kb);
       a = __ldg((const uint4*)(tp + r * 16));
       b = __ldg((const uint4*)(tp + 2048 + r * 16));
-      s2x = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
+      if (FMT == kQ4CP) {
+        s2x.a = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
+      } else if (FMT == kQ4K) {
+        const uint2 u = __ldg((const uint2*)(tp + kCodeBytes + r * 8));
+        s2x.a = u.x;
+        s2x.b = u.y;
+      } else {
+        const uint4 u = __ldg((const uint4*)(tp + kCodeBytes + r * 16));
+        s2x = RowMetaTc{u.x, u.y, u.z, u.w};
+      }
     };
     fetch(set, ca, cb, sc);
     bool ok = true;
@@ -417,8 +473,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       if (mine) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-          const uint32_t s16 = h ? (sc >> 16) : (sc & 0xFFFFu);
-          const uint32_t s2 = s16 | (s16 << 16);
+          GroupDecode<FMT> gd;
+          gd.init(sc, h);
           const uint4 c4 = h ? cb : ca;
           const uint32_t w4[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
@@ -428,7 +484,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
               const uint32_t addr = ((b == 0 ? w4[q] << 7 : w4[q] >> (8 * b - 7)) & 0x7F80u) | lut;
               uint32_t pair;
               asm("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(addr));
-              __half2 w2 = __hmul2(*(__half2*)&pair, *(const __half2*)&s2);
+              __half2 w2 = gd.weight(pair, q * 4 + b);
               v[h * 16 + q * 4 + b] = *(uint32_t*)&w2;
             }
           }
@@ -590,15 +646,14 @@ cudaError_t encode_2d(PFN_cuTensorMapEncodeTiled_v12000 enc, CUtensorMap* map, c
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <bool UP, bool DUAL>
+template <bool UP, bool DUAL, int FMT>
 cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
                    const Tile* tiles, const int32_t* n_tiles, int max_tiles, __half* out, int out_ld,
                    int32_t* status, cudaStream_t st) {
-  if (img.fmt != kQ4CP) return cudaErrorNotSupported;
   constexpr int kSmemBytes = Map<DUAL>::kSmemBytes;
   static bool attr_set = false;  // one flag per template instance
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(k_expert_tc<UP, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(k_expert_tc<UP, DUAL, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
@@ -607,7 +662,7 @@ cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
   long long max_items = (long long)max_tiles * img.n_mtiles;
   int grid = (int)(max_items < plan->sms ? max_items : plan->sms);
   if (grid < 1) grid = 1;
-  k_expert_tc<UP, DUAL><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
+  k_expert_tc<UP, DUAL, FMT><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
   return cudaGetLastError();
 }
 
@@ -662,15 +717,21 @@ void tc_destroy(TcPlan* plan) {
 
 cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                          int max_tiles, __half* hid16, int32_t* status, cudaStream_t st) {
+  if (img.fmt == kQ4K)
+    return launch<true, false, kQ4K>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
+  if (img.fmt != kQ4CP) return cudaErrorNotSupported;
   if (img.dual_book)
-    return launch<true, true>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
-  return launch<true, false>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16,
+    return launch<true, true, kQ4CP>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
+  return launch<true, false, kQ4CP>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16,
                       img.n_mtiles * 64, status, st);
 }
 
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                            int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st) {
-  return launch<false, false>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
+  if (img.fmt == kQ51)
+    return launch<false, false, kQ51>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16, img.n_mtiles * 128, status, st);
+  if (img.fmt != kQ4CP) return cudaErrorNotSupported;
+  return launch<false, false, kQ4CP>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
                        img.n_mtiles * 128, status, st);
 }
 

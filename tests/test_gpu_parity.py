@@ -247,17 +247,20 @@ def test_row_invariance(cuda):
         assert np.array_equal(bits(y_one[0]), bits(y_all[t]))
 
 
-def test_gguf_layer(cuda):
+@pytest.mark.parametrize("impl", [pkg.GEMM_SIMT, pkg.GEMM_AUTO])
+def test_gguf_layer(cuda, impl):
+    """GGUF experts (Q4_K gate/up, Q5_1 down): fp32 path and tensor-core path vs the oracle."""
     torch = cuda
     spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=128, fmt="gguf")
     layer = synth.make_layer(spec, seed=80)
-    for T in (3, 40):
-        logits = synth.make_logits(synth.rng_for(80, T), T, spec.experts)
+    for T in (3, 40, 300):
+        logits = synth.make_logits(synth.rng_for(80, T), T, spec.experts, zipf=T > 40)
         xb = synth.make_x(synth.rng_for(80, 9), T, spec.d)
         y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
-        op = make_op(torch, spec, T, impl=pkg.GEMM_SIMT, layer=layer)
+        op = make_op(torch, spec, T, impl=impl, layer=layer)
         y = run_layer(torch, op, spec, xb, logits)
-        assert_output_close(y, y_o, "gguf T=%d" % T)
+        max_abs, mean_rel = assert_output_close(y, y_o, "gguf T=%d impl %d" % (T, impl))
+        print("gguf T=%d impl=%d max-abs %.2e mean-rel %.2e" % (T, impl, max_abs, mean_rel))
 
 
 def test_forward_routed_and_host_paths(cuda):
