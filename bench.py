@@ -193,6 +193,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--tokens", type=int, default=T_CHUNK)
     ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
+    ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
     args = ap.parse_args()
@@ -218,8 +219,22 @@ def main():
     gen.manual_seed(1234)            # one weight set shared by all ranks
     gu = q4cp_blob_device(torch, E * 2 * MID, D, gen)
     dn = q4cp_blob_device(torch, E * D, MID, gen)
-    op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)
-    op.load_q4cp(0, gu, dn)
+    epm = None
+    if world > 1:
+        # expert parallelism: E/world experts per GPU, placed by a calibration histogram of the
+        # router (same seeded batch on every rank), NCCL all-to-all for dispatch and combine
+        from gfx1151_engine_b200 import ep
+        gcal = torch.Generator(device="cuda")
+        gcal.manual_seed(4321)
+        cal = torch.topk(zipf_logits(torch, 4096, gcal, 0), K_TOP, dim=1).indices.reshape(-1)
+        load = torch.bincount(cal, minlength=E).cpu().numpy()
+        placement = ep.greedy_placement(load, world)
+        epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement)
+        epm.load_q4cp(0, gu, dn)
+        op = epm.op
+    else:
+        op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)
+        op.load_q4cp(0, gu, dn)
     want_cpu = rank == 0 and world == 1 and not args.no_cpu
     layer_host = {"gate_up": gu.cpu().numpy(), "down": dn.cpu().numpy()} if want_cpu else None
     op_dec = None
@@ -232,6 +247,10 @@ def main():
               q4cp_blob_device(torch, D, MID, gen2)]
         op_dec.load_shared_q4cp(0, sh[0], sh[1], sh[2],
                                 (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16))
+    op_ref = None
+    if world > 1 and args.check and rank == 0:
+        op_ref = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)   # whole layer on one GPU, for the check
+        op_ref.load_q4cp(0, gu, dn)
     del gu, dn
     torch.cuda.empty_cache()
 
@@ -247,10 +266,25 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def step():
+        if epm is not None:
+            epm.forward(0, x, logits, out)
+        else:
+            op.moe_b(0, x, logits, out, stream=stream)
+
     for _ in range(args.warmup):
-        op.moe_b(0, x, logits, out, stream=stream)
+        step()
     op.synchronize(stream)
-    op.profile_enable(True)
+    check = None
+    if op_ref is not None:
+        ref_out = torch.empty_like(out)
+        op_ref.moe_b(0, x, logits, ref_out, stream=stream)
+        op_ref.synchronize(stream)
+        a, b = out.float(), ref_out.float()
+        check = {"max_abs": float((a - b).abs().max()), "mean_rel": float((a - b).abs().mean() / b.abs().mean())}
+        op_ref.close()
+    if world == 1:
+        op.profile_enable(True)
     sampler = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -259,33 +293,45 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
     for _ in range(args.steps):
-        op.moe_b(0, x, logits, out, stream=stream)
+        step()
     ev1.record(stream)
     barrier()
     launches = op.launches - l0
     clocks = sampler.stop() if rank == 0 else None
     op.synchronize(stream)
     ms = ev0.elapsed_time(ev1)
-    stages = op.profile_read()
-    op.profile_enable(False)
+    stages = op.profile_read() if world == 1 else {"up": 0.0}
+    if world == 1:
+        op.profile_enable(False)
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = world * T * args.steps / (ms * 1e-3)
 
-    # end to end through the host-buffer entry point (pinned buffers, copies inside)
+    # end to end with HOST buffers (pinned), host<->device copies inside the timed region
     xh = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
     xh.copy_(x)
     lh = torch.empty(T, E, dtype=torch.float32).pin_memory()
     lh.copy_(logits)
     oh = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
-    op.moe_b_host(0, xh, lh, oh, T, stream=stream)
+
+    def e2e_step():
+        if epm is not None:
+            x.copy_(xh, non_blocking=True)
+            logits.copy_(lh, non_blocking=True)
+            epm.forward(0, x, logits, out)
+            oh.copy_(out, non_blocking=True)
+            torch.cuda.synchronize()
+        else:
+            op.moe_b_host(0, xh, lh, oh, T, stream=stream)   # the C-ABI entry point with host buffers
+
+    e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        op.moe_b_host(0, xh, lh, oh, T, stream=stream)
+        e2e_step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     if world > 1:
@@ -295,26 +341,43 @@ def main():
     e2e = {"value": world * T * e2e_steps / e2e_s, "unit": "tokens/s",
            "h2d_bytes_per_step": T * D * 2 + T * E * 4, "d2h_bytes_per_step": T * D * 2,
            "checksum": float(oh.float().abs().mean())}
+    ep_info = None
+    if epm is not None:
+        rows = torch.tensor([float(epm.last_recv_rows)], device="cuda")
+        mx = rows.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM)
+        ep_info = {"experts_per_gpu": E // world, "placement": "greedy by calibration histogram",
+                   "recv_rows_max_over_mean": float(mx.item() / (rows.item() / world)),
+                   "exchange": "NCCL all_to_all_single (dispatch, combine), all_gather of expert offsets",
+                   "check_vs_single_gpu": check}
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    up_s = stages["up"] * 1e-3
-    achieved = FLOP_UP_PER_TOKEN * T / up_s / 1e12 if up_s > 0 else 0.0
+    if world == 1:
+        up_s = stages["up"] * 1e-3
+        achieved = FLOP_UP_PER_TOKEN * T / up_s / 1e12 if up_s > 0 else 0.0
+        roof_kernel = "k_expert_tc<up> (gate/up GEMM + SwiGLU)"
+    else:
+        # per GPU, over the whole step including both all-to-all exchanges
+        achieved = FLOP_PER_TOKEN * T * args.steps / (ms * 1e-3) / 1e12
+        roof_kernel = "whole expert-parallel step per GPU (grouped GEMMs + NCCL all-to-all)"
+        stages = {}
     result = {
         "metric": "moe_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
         "data": "synthetic",
         "config": {"workload": WORKLOAD if (E, T) == (512, T_CHUNK) else "reduced case for profiling (not the benchmark workload)", "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
-                   "d_mid": MID, "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
+                   "d_mid": MID, "parallelism": "expert-parallel x%d" % world if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 3.6 GB of expert weights + 168 MB of activations per step"},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "expert_parallel": ep_info,
         "stage_ms": {k: round(v, 4) for k, v in stages.items()},
         "layer_tflops": FLOP_PER_TOKEN * T * args.steps / (ms * 1e-3) / 1e12,
-        "roofline": {"bound": "tensor", "kernel": "k_expert_tc<up> (gate/up GEMM + SwiGLU)",
+        "roofline": {"bound": "tensor", "kernel": roof_kernel,
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                      "peak_kind": peak_kind + " dense 16-bit burst", "traffic": None},
     }

@@ -43,6 +43,12 @@ SYMBOLS = {
     "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
     "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
     "b200moe_route_static": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "b200moe_ep_set_placement": (_I, [_P, _P]),
+    "b200moe_ep_attach": (_I, [_P, _P, _P, _P, _P, ctypes.c_int64]),
+    "b200moe_ep_route": (_I, [_P, _I, _P, _I, _P, _P, _P]),
+    "b200moe_ep_offsets": (_I, [_P, ctypes.POINTER(_P)]),
+    "b200moe_ep_experts": (_I, [_P, _I, _P, _P]),
+    "b200moe_ep_combine": (_I, [_P, _I, _P, _P]),
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_synchronize": (_I, [_P, _P]),
@@ -174,6 +180,30 @@ class MoeOperator:
 
     def route(self, topids, topw, T, stride=16, stream=None):
         self._check(lib().b200moe_route(self._h, _ptr(topids), _ptr(topw), stride, T, _stream(stream)))
+
+    # -- expert parallelism: library phases; the exchanges in between belong to the caller ------
+    def ep_set_placement(self, placed_id_of_expert):
+        self._check(lib().b200moe_ep_set_placement(self._h, _ptr(placed_id_of_expert)))
+
+    def ep_attach(self, x_send, x_recv, pairs_recv, pairs_back, cap_rows):
+        self._check(lib().b200moe_ep_attach(self._h, _ptr(x_send), _ptr(x_recv), _ptr(pairs_recv),
+                                            _ptr(pairs_back), cap_rows))
+
+    def ep_route(self, layer, x, logits, eoff_out=None, T=None, stream=None):
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_ep_route(self._h, layer, _ptr(x), T, _ptr(logits), _ptr(eoff_out),
+                                           _stream(stream)))
+
+    def ep_offsets_ptr(self):
+        p = _P()
+        self._check(lib().b200moe_ep_offsets(self._h, ctypes.byref(p)))
+        return p.value
+
+    def ep_experts(self, layer, eoff_all, stream=None):
+        self._check(lib().b200moe_ep_experts(self._h, layer, _ptr(eoff_all), _stream(stream)))
+
+    def ep_combine(self, out, T, stream=None):
+        self._check(lib().b200moe_ep_combine(self._h, T, _ptr(out), _stream(stream)))
 
     def synchronize(self, stream=None):
         """Wait for the stream and raise if a device-side wait gave up."""

@@ -43,6 +43,15 @@ struct b200moe_ctx {
   int32_t* status_dev = nullptr;
   int32_t* status_host = nullptr;  // pinned
   TcPlan* tc = nullptr;
+  // expert parallelism
+  int32_t *place_dev = nullptr, *source_of_placed_dev = nullptr;
+  __half *ep_x_send = nullptr, *ep_x_recv = nullptr, *ep_pairs_recv = nullptr, *ep_pairs_back = nullptr;
+  __half* ep_hid = nullptr;
+  Tile* ep_tiles = nullptr;
+  int32_t* ep_counts = nullptr;  // [0] tiles, [1] received rows
+  long long ep_cap_rows = 0;
+  int ep_max_tiles = 0;
+  TcPlan* tc_ep = nullptr;
   int64_t launches = 0;
   // stage timer: ring of event sets, one set (7 events) per forward call
   bool prof = false;
@@ -257,6 +266,12 @@ int b200moe_destroy(b200moe_handle h) {
     if (L.sh_gate_w) cudaFree(L.sh_gate_w);
   }
   free_all(h->allocs);
+  if (h->place_dev) cudaFree(h->place_dev);
+  if (h->source_of_placed_dev) cudaFree(h->source_of_placed_dev);
+  if (h->ep_hid) cudaFree(h->ep_hid);
+  if (h->ep_tiles) cudaFree(h->ep_tiles);
+  if (h->ep_counts) cudaFree(h->ep_counts);
+  if (h->tc_ep) tc_destroy(h->tc_ep);
   for (auto& e : h->prof_ev) cudaEventDestroy(e);
   if (h->status_host) cudaFreeHost(h->status_host);
   if (h->tc) tc_destroy(h->tc);
@@ -287,7 +302,7 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
   if (e == cudaSuccess) e = alloc_image(L.gu, kQ4CP, nl, (int)mid, (int)d, 1);
   if (e == cudaSuccess) {
     SrcTensor g = q4cp_src(gu, E * 2 * mid, d, 2 * mid, 0), u = q4cp_src(gu, E * 2 * mid, d, 2 * mid, mid);
-    e = launch_repack(L.gu, g, u, (int)d, e0, 0);
+    e = launch_repack(L.gu, g, u, (int)d, e0, 0, h->source_of_placed_dev);
     h->launches++;
   }
   if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, gu, 64, cudaMemcpyDeviceToDevice);
@@ -298,7 +313,7 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
   if (e == cudaSuccess) e = alloc_image(L.dn, kQ4CP, nl, (int)d, (int)mid, 0);
   if (e == cudaSuccess) {
     SrcTensor a = q4cp_src(dn, E * d, mid, d, 0);
-    e = launch_repack(L.dn, a, a, (int)mid, e0, 0);
+    e = launch_repack(L.dn, a, a, (int)mid, e0, 0, h->source_of_placed_dev);
     h->launches++;
   }
   if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, dn, 64, cudaMemcpyDeviceToDevice);
@@ -660,6 +675,99 @@ int b200moe_profile_read(b200moe_handle h, float* stage_ms6, int* n_calls) {
   }
   for (int i = 0; i < 6; i++) stage_ms6[i] /= (float)h->prof_pending;
   h->prof_pending = 0;
+  return B200MOE_OK;
+}
+
+// ---------------------------------------------------------------- expert parallelism ----
+int b200moe_ep_set_placement(b200moe_handle h, const int32_t* place_host) {
+  if (!h || !place_host) return B200MOE_ERR_BAD_ARG;
+  const int E = h->cfg.experts;
+  std::vector<int32_t> inv(E, -1);
+  for (int e = 0; e < E; e++) {
+    const int p = place_host[e];
+    if (p < 0 || p >= E || inv[p] >= 0) return fail(h, B200MOE_ERR_BAD_ARG, "placement is not a permutation");
+    inv[p] = e;
+  }
+  CU_TRY(h, cudaSetDevice(h->cfg.device));
+  if (!h->place_dev) CU_TRY(h, cudaMalloc((void**)&h->place_dev, E * sizeof(int32_t)));
+  if (!h->source_of_placed_dev) CU_TRY(h, cudaMalloc((void**)&h->source_of_placed_dev, E * sizeof(int32_t)));
+  CU_TRY(h, cudaMemcpy(h->place_dev, place_host, E * sizeof(int32_t), cudaMemcpyHostToDevice));
+  CU_TRY(h, cudaMemcpy(h->source_of_placed_dev, inv.data(), E * sizeof(int32_t), cudaMemcpyHostToDevice));
+  for (auto& L : h->layers) L.loaded = false;  // weights must be (re)loaded under the new numbering
+  return B200MOE_OK;
+}
+
+int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_recv, void* pairs_back,
+                      int64_t cap_rows) {
+  if (!h || !x_send || !x_recv || !pairs_recv || !pairs_back || cap_rows < 1) return B200MOE_ERR_BAD_ARG;
+  if (h->cfg.has_shared) return fail(h, B200MOE_ERR_UNSUPPORTED, "expert parallelism with a shared expert is not implemented");
+  if (h->cfg.gemm_impl == B200MOE_GEMM_SIMT) return fail(h, B200MOE_ERR_UNSUPPORTED, "expert parallelism needs the tensor-core path");
+  CU_TRY(h, cudaSetDevice(h->cfg.device));
+  h->ep_x_send = (__half*)x_send;
+  h->ep_x_recv = (__half*)x_recv;
+  h->ep_pairs_recv = (__half*)pairs_recv;
+  h->ep_pairs_back = (__half*)pairs_back;
+  h->ep_cap_rows = cap_rows;
+  h->ep_max_tiles = (int)(cap_rows / h->tile_cap) + kMaxExperts + 1;
+  if (h->ep_hid) cudaFree(h->ep_hid), h->ep_hid = nullptr;
+  if (h->ep_tiles) cudaFree(h->ep_tiles), h->ep_tiles = nullptr;
+  if (h->tc_ep) tc_destroy(h->tc_ep), h->tc_ep = nullptr;
+  CU_TRY(h, cudaMalloc((void**)&h->ep_hid, (size_t)cap_rows * h->cfg.d_mid * 2 + 256));
+  CU_TRY(h, cudaMalloc((void**)&h->ep_tiles, (size_t)h->ep_max_tiles * sizeof(Tile)));
+  if (!h->ep_counts) CU_TRY(h, cudaMalloc((void**)&h->ep_counts, 16));
+  CU_TRY(h, tc_create(&h->tc_ep, h->ep_x_recv, h->ep_hid, cap_rows, h->cfg.d_model, h->cfg.d_mid));
+  return B200MOE_OK;
+}
+
+int b200moe_ep_route(b200moe_handle h, int layer, const void* x, int T, const float* logits,
+                     int32_t* eoff_out, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x || !logits || T < 1 || T > h->cfg.max_tokens || !h->ep_x_send)
+    return fail(h, B200MOE_ERR_BAD_ARG, "ep_route: bad argument or buffers not attached");
+  const b200moe_config& c = h->cfg;
+  cudaStream_t st = (cudaStream_t)stream;
+  int n = 0;
+  CU_TRY(h, launch_router_topk(logits, T, c.experts, c.topk, h->rb.topids, h->rb.topw, kIdStride, st));
+  if (h->place_dev) {
+    CU_TRY(h, launch_apply_placement(h->rb.topids, kIdStride, T, c.topk, h->place_dev, st));
+    n++;
+  }
+  CU_TRY(h, launch_route(h->rb, h->rb.topids, h->rb.topw, kIdStride, T, c.topk, c.experts, h->tile_cap, st, &n));
+  CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, T * c.topk, c.d_model, h->ep_x_send, st));
+  if (eoff_out)
+    CU_TRY(h, cudaMemcpyAsync(eoff_out, h->rb.eoff, ((size_t)c.experts + 1) * 4, cudaMemcpyDeviceToDevice, st));
+  h->launches += n + 2;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev) {
+  if (!h || !eoff_dev) return B200MOE_ERR_BAD_ARG;
+  *eoff_dev = h->rb.eoff;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!eoff_all_dev || !h->tc_ep) return fail(h, B200MOE_ERR_BAD_ARG, "ep_experts: bad argument or buffers not attached");
+  LayerWeights& L = h->layers[layer];
+  if (!L.loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "ep_experts: layer weights not loaded");
+  const b200moe_config& c = h->cfg;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int El = local_experts(c);
+  CU_TRY(h, launch_ep_tiles(eoff_all_dev, c.ep_size, c.experts, first_expert(c), El, h->tile_cap, h->ep_tiles,
+                            h->ep_counts, h->ep_counts + 1, st));
+  CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
+  CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv,
+                           h->status_dev, st));
+  h->launches += 3;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_combine(b200moe_handle h, int T, void* out, void* stream) {
+  if (!h || !out || T < 1 || T > h->cfg.max_tokens || !h->ep_pairs_back) return B200MOE_ERR_BAD_ARG;
+  CU_TRY(h, launch_combine_f16(h->ep_pairs_back, h->rb.pw, h->rb.pairids, T, h->cfg.topk, h->cfg.d_model, -1, out,
+                               (cudaStream_t)stream));
+  h->launches++;
   return B200MOE_OK;
 }
 

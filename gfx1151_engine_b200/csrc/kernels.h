@@ -17,8 +17,10 @@ struct SrcTensor {
 };
 
 // ---- repack.cu ----
+// expert_map (device, may be null): source expert of image expert i is expert_map[first_expert + i]
+// (placement for expert parallelism), else first_expert + i.
 cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
-                          int first_expert, cudaStream_t st);
+                          int first_expert, cudaStream_t st, const int32_t* expert_map = nullptr);
 cudaError_t launch_dequant_rows(const Image& img, int expert, int row0, int nrows, int mid_rows,
                                 float* out, cudaStream_t st);
 
@@ -50,6 +52,11 @@ cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, cons
                                const uint16_t* gate_w_bf16, int d, cudaStream_t st);
 cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, int T, int d,
                                int k, const RouteBuffers& rb, cudaStream_t st);
+
+cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, const int32_t* place,
+                                   cudaStream_t st);
+cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
+                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st);
 
 // ---- expert_simt.cu ----
 cudaError_t launch_up_simt(const Image& img, const void* x_bf16, int d, int mid,

@@ -22,7 +22,8 @@ __device__ __forceinline__ long long src_row(const Image& img, const SrcTensor& 
 }
 
 // q4cp: pure movement of 16-byte chunks and fp16 scale pairs.
-__global__ void k_repack_q4cp(Image img, SrcTensor a, SrcTensor b, int K, int first_expert) {
+__global__ void k_repack_q4cp(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                              const int32_t* __restrict__ emap) {
   const long long per_tile = 256 + 128;  // 256 code chunks + 128 scale pairs
   const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * per_tile;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -37,12 +38,12 @@ __global__ void k_repack_q4cp(Image img, SrcTensor a, SrcTensor b, int K, int fi
     const SrcTensor* s;
     if (j < 256) {
       int h = j >> 7, r = j & 127;
-      long long row = src_row(img, a, b, e + first_expert, mt, r, &s);
+      long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
       const uint4* src = (const uint4*)(s->codes + row * (K / 2) + kb * 32 + h * 16);
       *(uint4*)(dst + h * 2048 + r * 16) = *src;
     } else {
       int r = j - 256;
-      long long row = src_row(img, a, b, e + first_expert, mt, r, &s);
+      long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
       const uint32_t* src = (const uint32_t*)(s->scales + row * s->scale_stride + kb * 4);
       *(uint32_t*)(dst + kCodeBytes + r * 4) = *src;
     }
@@ -61,7 +62,8 @@ __device__ __forceinline__ void k4_scale_min(int j, const uint8_t* p, uint8_t& s
 
 // Q4_K: one thread per (tile, row). A 64-wide K block is half of a 128-element pair of
 // sub-blocks: low nibbles of 32 bytes are K 0..31, high nibbles K 32..63 (src/gguf.h:408-441).
-__global__ void k_repack_q4k(Image img, SrcTensor a, SrcTensor b, int K, int first_expert) {
+__global__ void k_repack_q4k(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                             const int32_t* __restrict__ emap) {
   const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 128;
   const long long row_bytes = (long long)K / 256 * 144;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -74,7 +76,7 @@ __global__ void k_repack_q4k(Image img, SrcTensor a, SrcTensor b, int K, int fir
     int e = (int)(t2 / img.n_mtiles);
     uint8_t* dst = const_cast<uint8_t*>(img.tile(e, mt, kb));
     const SrcTensor* s;
-    long long row = src_row(img, a, b, e + first_expert, mt, r, &s);
+    long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
     const uint8_t* blk = s->codes + row * row_bytes + (long long)(kb >> 2) * 144;
     const int sub = kb & 3;
     const uint8_t* ql = blk + 16 + 32 * sub;
@@ -104,7 +106,8 @@ __global__ void k_repack_q4k(Image img, SrcTensor a, SrcTensor b, int K, int fir
 
 // Q5_1: one thread per (tile, row, half). Element j of a block is the low nibble of qs[j],
 // element j+16 the high nibble (src/gguf.h:360-374); the fifth bits stay in their word.
-__global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int first_expert) {
+__global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                             const int32_t* __restrict__ emap) {
   const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 256;
   const long long row_bytes = (long long)K / 32 * 24;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -118,7 +121,7 @@ __global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int fir
     int e = (int)(t2 / img.n_mtiles);
     uint8_t* dst = const_cast<uint8_t*>(img.tile(e, mt, kb));
     const SrcTensor* s;
-    long long row = src_row(img, a, b, e + first_expert, mt, r, &s);
+    long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
     const uint8_t* blk = s->codes + row * row_bytes + (long long)(kb * 2 + h) * 24;
     const uint8_t* qs = blk + 8;
     uint8_t out[16];
@@ -188,12 +191,12 @@ __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int m
 }  // namespace
 
 cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
-                          int first_expert, cudaStream_t st) {
+                          int first_expert, cudaStream_t st, const int32_t* expert_map) {
   const int threads = 256;
   const int blocks = 148 * 8;
-  if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert);
-  else if (img.fmt == kQ4K) k_repack_q4k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert);
-  else k_repack_q51<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert);
+  if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else if (img.fmt == kQ4K) k_repack_q4k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else k_repack_q51<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   return cudaGetLastError();
 }
 

@@ -372,6 +372,82 @@ cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, 
   return cudaGetLastError();
 }
 
+// ---- expert parallelism ---------------------------------------------------------------
+// ids <- place[ids]: experts renumbered so that rank r owns the ids [r*E/G, (r+1)*E/G).
+__global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, int k,
+                                  const int32_t* __restrict__ place) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p < T * k) {
+    int32_t* q = ids + (size_t)(p / k) * stride + p % k;
+    *q = place[*q];
+  }
+}
+
+// Work list of the receiving rank. The receive buffer holds, source rank after source rank,
+// that source's rows for this rank's experts in ascending expert order; eoff_all[s] is source
+// s's expert offset table (E+1 entries). One thread per (source, local expert) segment:
+// its position in the buffer, then tiles of at most tile_cap rows (full tiles first, ragged
+// ones by descending size), exactly as the single-GPU tile list is built.
+__global__ void __launch_bounds__(kMaxExperts)
+k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, int tile_cap,
+           Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ total_rows) {
+  __shared__ int s_a[kMaxExperts], s_c[kMaxExperts];
+  const int tid = threadIdx.x;
+  const int src = tid / El, e = tid % El;
+  const bool live = tid < G * El;
+  int cnt = 0, first = 0;
+  if (live) {
+    const int32_t* eo = eoff_all + (size_t)src * (E + 1);
+    cnt = eo[e0 + e + 1] - eo[e0 + e];
+    first = eo[e0 + e] - eo[e0];                      // offset inside the source's segment
+    for (int s2 = 0; s2 < src; s2++) {                // segments of the sources before it
+      const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
+      first += e2[e0 + El] - e2[e0];
+    }
+  }
+  const int nfull = cnt / tile_cap, part = cnt % tile_cap;
+  s_c[tid] = nfull;
+  __syncthreads();
+  for (int o = 1; o < kMaxExperts; o <<= 1) {
+    const int c = tid >= o ? s_c[tid - o] : 0;
+    __syncthreads();
+    s_c[tid] += c;
+    __syncthreads();
+  }
+  const int total_full = s_c[kMaxExperts - 1], full0 = s_c[tid] - nfull;
+  for (int j = 0; j < nfull; j++) tiles[full0 + j] = Tile{e, first + j * tile_cap, tile_cap};
+  s_a[tid] = part;
+  __syncthreads();
+  int rank = 0, nparts = 0;
+  for (int o = 0; o < kMaxExperts; o++) {
+    const int pp = s_a[o];
+    nparts += pp > 0;
+    rank += (pp > part) || (pp == part && o < tid);
+  }
+  if (part > 0) tiles[total_full + rank] = Tile{e, first + nfull * tile_cap, part};
+  if (tid == 0) {
+    n_tiles[0] = total_full + nparts;
+    int rows = 0;
+    for (int s2 = 0; s2 < G; s2++) {
+      const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
+      rows += e2[e0 + El] - e2[e0];
+    }
+    *total_rows = rows;
+  }
+}
+
+cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, const int32_t* place,
+                                   cudaStream_t st) {
+  k_apply_placement<<<(T * k + 255) / 256, 256, 0, st>>>(ids, stride, T, k, place);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
+                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st) {
+  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, tiles, n_tiles, total_rows);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, const int32_t* ids,
                                const float* w, int stride, int T, int k, int E, const void* x_bf16,
                                const uint16_t* gate_w_bf16, int d, cudaStream_t st) {

@@ -143,6 +143,28 @@ int b200moe_route_static(const int32_t* topids_dev, const float* topw_dev, int s
                          int topk, int experts, int32_t* tokidx_dev, float* pw_dev,
                          int32_t* eoff_dev, int32_t* pairids_dev, void* stream);
 
+/* ---- Expert parallelism (no counterpart in the reference, which runs on one device) -------
+ * With ep_size > 1 in the config, rank r owns experts [r*E/G, (r+1)*E/G) of the PLACED
+ * numbering (b200moe_ep_set_placement; identity by default). A forward is three library
+ * phases with the two all-to-all exchanges in between done by the caller (NCCL):
+ *   ep_route:    router top-k, bucketing, gather of this rank's rows into x_send, sorted by
+ *                placed expert id and therefore by destination rank;
+ *   (all-gather of every rank's expert offsets, all-to-all of the rows into x_recv)
+ *   ep_experts:  grouped GEMMs over the received rows -> pairs_recv (same row order);
+ *   (all-to-all of pairs_recv back into pairs_back, which then has x_send's row order)
+ *   ep_combine:  weighted top-k combine of this rank's tokens.
+ * ep_attach hands the library the four fp16 row buffers [rows][d_model] (caller-owned device
+ * memory: x_send and pairs_back hold max_tokens*topk rows, x_recv and pairs_recv cap_rows). */
+int b200moe_ep_set_placement(b200moe_handle h, const int32_t* placed_id_of_expert_host);
+int b200moe_ep_attach(b200moe_handle h, void* x_send_dev, void* x_recv_dev, void* pairs_recv_dev,
+                      void* pairs_back_dev, int64_t cap_rows);
+int b200moe_ep_route(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
+                     const float* logits_dev, int32_t* eoff_out_dev /* [experts+1], may be NULL */,
+                     void* stream);
+int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev);
+int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream);
+int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream);
+
 /* Reads back what the last forward / route call left in the workspace (host buffers; any may
  * be NULL): tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k] as defined by
  * src/gpu/parts/10_ple_io.inc:790-811, and topids/topw rows of 16. Synchronises the device. */
