@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--tokens", type=int, default=T_CHUNK)
     ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
+    ap.add_argument("--chunks", type=int, default=1, help="N>1: token chunks whose exchanges overlap the GEMMs")
+    ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
@@ -229,7 +231,8 @@ def main():
         cal = torch.topk(zipf_logits(torch, 4096, gcal, 0), K_TOP, dim=1).indices.reshape(-1)
         load = torch.bincount(cal, minlength=E).cpu().numpy()
         placement = ep.greedy_placement(load, world)
-        epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement)
+        epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement,
+                                   chunks=args.chunks, sm_margin=args.sm_margin)
         epm.load_q4cp(0, gu, dn)
         op = epm.op
     else:
@@ -289,14 +292,15 @@ def main():
     barrier()
     if rank == 0:
         sampler.start()
-    l0 = op.launches
+    counter = epm if epm is not None else op
+    l0 = counter.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
     for _ in range(args.steps):
         step()
     ev1.record(stream)
     barrier()
-    launches = op.launches - l0
+    launches = counter.launches - l0
     clocks = sampler.stop() if rank == 0 else None
     op.synchronize(stream)
     ms = ev0.elapsed_time(ev1)
@@ -350,6 +354,7 @@ def main():
         ep_info = {"experts_per_gpu": E // world, "placement": "greedy by calibration histogram",
                    "recv_rows_max_over_mean": float(mx.item() / (rows.item() / world)),
                    "exchange": "NCCL all_to_all_single (dispatch, combine), all_gather of expert offsets",
+                   "chunks": args.chunks,
                    "check_vs_single_gpu": check}
 
     if rank != 0:

@@ -26,7 +26,7 @@ class Config(ctypes.Structure):
     """Field-for-field mirror of b200moe_config."""
     _fields_ = [(n, ctypes.c_int32) for n in (
         "experts", "topk", "d_model", "d_mid", "n_layers", "max_tokens", "has_shared", "device",
-        "gemm_impl", "decode_max_tokens", "ep_rank", "ep_size")] + [("reserved", ctypes.c_int32 * 4)]
+        "gemm_impl", "decode_max_tokens", "ep_rank", "ep_size", "ep_sm_margin")] + [("reserved", ctypes.c_int32 * 3)]
 
 
 SYMBOLS = {
@@ -44,6 +44,7 @@ SYMBOLS = {
     "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
     "b200moe_route_static": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_ep_set_placement": (_I, [_P, _P]),
+    "b200moe_share_weights": (_I, [_P, _P]),
     "b200moe_ep_attach": (_I, [_P, _P, _P, _P, _P, ctypes.c_int64]),
     "b200moe_ep_route": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_ep_offsets": (_I, [_P, ctypes.POINTER(_P)]),
@@ -111,9 +112,9 @@ class MoeOperator:
     """
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, n_layers=1, has_shared=False,
-                 device=0, gemm_impl=GEMM_AUTO, decode_max_tokens=0, ep_rank=0, ep_size=1):
+                 device=0, gemm_impl=GEMM_AUTO, decode_max_tokens=0, ep_rank=0, ep_size=1, ep_sm_margin=0):
         self.cfg = Config(experts, topk, d_model, d_mid, n_layers, max_tokens, int(has_shared), device,
-                          gemm_impl, decode_max_tokens, ep_rank, ep_size)
+                          gemm_impl, decode_max_tokens, ep_rank, ep_size, ep_sm_margin)
         self._h = _P()
         st = lib().b200moe_create(ctypes.byref(self.cfg), ctypes.byref(self._h))
         if st != 0:
@@ -184,6 +185,11 @@ class MoeOperator:
     # -- expert parallelism: library phases; the exchanges in between belong to the caller ------
     def ep_set_placement(self, placed_id_of_expert):
         self._check(lib().b200moe_ep_set_placement(self._h, _ptr(placed_id_of_expert)))
+
+    def share_weights(self, owner):
+        """Use `owner`'s repacked weights; keep a reference so that it outlives this handle."""
+        self._check(lib().b200moe_share_weights(self._h, owner._h))
+        self._weights_owner = owner
 
     def ep_attach(self, x_send, x_recv, pairs_recv, pairs_back, cap_rows):
         self._check(lib().b200moe_ep_attach(self._h, _ptr(x_send), _ptr(x_recv), _ptr(pairs_recv),

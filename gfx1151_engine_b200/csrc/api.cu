@@ -23,6 +23,7 @@ struct LayerWeights {
   Image gu, dn, sh_gu, sh_dn;
   uint16_t* sh_gate_w = nullptr;
   bool loaded = false, shared_loaded = false;
+  bool borrowed = false;  // images belong to another handle
 };
 
 }  // namespace
@@ -45,6 +46,7 @@ struct b200moe_ctx {
   TcPlan* tc = nullptr;
   // expert parallelism
   int32_t *place_dev = nullptr, *source_of_placed_dev = nullptr;
+  bool place_borrowed = false;
   __half *ep_x_send = nullptr, *ep_x_recv = nullptr, *ep_pairs_recv = nullptr, *ep_pairs_back = nullptr;
   __half* ep_hid = nullptr;
   Tile* ep_tiles = nullptr;
@@ -259,6 +261,7 @@ int b200moe_destroy(b200moe_handle h) {
   cudaSetDevice(h->cfg.device);
   cudaDeviceSynchronize();
   for (auto& L : h->layers) {
+    if (L.borrowed) continue;
     free_image(L.gu);
     free_image(L.dn);
     free_image(L.sh_gu);
@@ -266,8 +269,8 @@ int b200moe_destroy(b200moe_handle h) {
     if (L.sh_gate_w) cudaFree(L.sh_gate_w);
   }
   free_all(h->allocs);
-  if (h->place_dev) cudaFree(h->place_dev);
-  if (h->source_of_placed_dev) cudaFree(h->source_of_placed_dev);
+  if (h->place_dev && !h->place_borrowed) cudaFree(h->place_dev);
+  if (h->source_of_placed_dev && !h->place_borrowed) cudaFree(h->source_of_placed_dev);
   if (h->ep_hid) cudaFree(h->ep_hid);
   if (h->ep_tiles) cudaFree(h->ep_tiles);
   if (h->ep_counts) cudaFree(h->ep_counts);
@@ -697,6 +700,33 @@ int b200moe_ep_set_placement(b200moe_handle h, const int32_t* place_host) {
   return B200MOE_OK;
 }
 
+int b200moe_share_weights(b200moe_handle h, b200moe_handle owner) {
+  if (!h || !owner || h == owner) return B200MOE_ERR_BAD_ARG;
+  const b200moe_config &a = h->cfg, &b = owner->cfg;
+  if (a.experts != b.experts || a.topk != b.topk || a.d_model != b.d_model || a.d_mid != b.d_mid ||
+      a.n_layers != b.n_layers || a.device != b.device || a.ep_rank != b.ep_rank || a.ep_size != b.ep_size ||
+      a.has_shared != b.has_shared)
+    return fail(h, B200MOE_ERR_BAD_ARG, "share_weights: the two handles differ in shape or placement");
+  for (size_t i = 0; i < h->layers.size(); i++) {
+    LayerWeights& L = h->layers[i];
+    if (!L.borrowed) {
+      free_image(L.gu);
+      free_image(L.dn);
+      free_image(L.sh_gu);
+      free_image(L.sh_dn);
+      if (L.sh_gate_w) cudaFree(L.sh_gate_w);
+    }
+    L = owner->layers[i];
+    L.borrowed = true;
+  }
+  if (h->place_dev && !h->place_borrowed) cudaFree(h->place_dev);
+  if (h->source_of_placed_dev && !h->place_borrowed) cudaFree(h->source_of_placed_dev);
+  h->place_dev = owner->place_dev;
+  h->source_of_placed_dev = owner->source_of_placed_dev;
+  h->place_borrowed = true;
+  return B200MOE_OK;
+}
+
 int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_recv, void* pairs_back,
                       int64_t cap_rows) {
   if (!h || !x_send || !x_recv || !pairs_recv || !pairs_back || cap_rows < 1) return B200MOE_ERR_BAD_ARG;
@@ -716,6 +746,7 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   CU_TRY(h, cudaMalloc((void**)&h->ep_tiles, (size_t)h->ep_max_tiles * sizeof(Tile)));
   if (!h->ep_counts) CU_TRY(h, cudaMalloc((void**)&h->ep_counts, 16));
   CU_TRY(h, tc_create(&h->tc_ep, h->ep_x_recv, h->ep_hid, cap_rows, h->cfg.d_model, h->cfg.d_mid));
+  tc_set_sm_margin(h->tc_ep, h->cfg.ep_sm_margin);
   return B200MOE_OK;
 }
 

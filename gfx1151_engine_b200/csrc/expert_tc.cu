@@ -45,6 +45,7 @@ namespace b200moe {
 struct TcPlan {
   CUtensorMap x[4], h[4];  // activation / hidden maps with boxes of 16, 64, 128, 192 rows
   int sms = 148;
+  int margin = 0;
   long long* trace = nullptr;  // debug timeline of CTA 0 (environment B200MOE_TC_TRACE=<file>)
 };
 
@@ -660,7 +661,8 @@ cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
   }
   KParams p{img, tiles, n_tiles, out, out_ld, status, UP ? plan->trace : nullptr};
   long long max_items = (long long)max_tiles * img.n_mtiles;
-  int grid = (int)(max_items < plan->sms ? max_items : plan->sms);
+  const int usable = plan->sms - plan->margin > 1 ? plan->sms - plan->margin : 1;
+  int grid = (int)(max_items < usable ? max_items : usable);
   if (grid < 1) grid = 1;
   k_expert_tc<UP, DUAL, FMT><<<grid, kThreads, kSmemBytes, st>>>(m[0], m[1], m[2], m[3], p);
   return cudaGetLastError();
@@ -696,6 +698,10 @@ cudaError_t tc_create(TcPlan** out, const __half* x_sorted, const __half* hid16,
   }
   *out = plan;
   return cudaSuccess;
+}
+
+void tc_set_sm_margin(TcPlan* plan, int sms) {
+  if (plan) plan->margin = sms < 0 ? 0 : sms;
 }
 
 void tc_destroy(TcPlan* plan) {

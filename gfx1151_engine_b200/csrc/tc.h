@@ -10,6 +10,9 @@ struct TcPlan;  // tensor maps over the activation buffers + device properties
 cudaError_t tc_create(TcPlan** plan, const __half* x_sorted, const __half* hid16,
                       long long rows_cap, int d, int mid);
 void tc_destroy(TcPlan* plan);
+// Leave `sms` SMs free of the persistent GEMM CTAs (for communication kernels that must run
+// at the same time).
+void tc_set_sm_margin(TcPlan* plan, int sms);
 
 // Largest number of rows in one grouped-GEMM tile (the MMA N extent).
 constexpr int kTcTileN = 192;

@@ -56,46 +56,112 @@ def exchange_splits(eoff_all, rank, world):
 
 
 class ExpertParallelMoe:
-    """The MoE layer sharded by expert over the ranks of a torch.distributed group."""
+    """The MoE layer sharded by expert over the ranks of a torch.distributed group.
+
+    chunks > 1 splits a forward's tokens into that many chunks, each with its own library
+    handle (workspaces) sharing one set of repacked weights; the all-to-all exchanges of a
+    chunk run on a communication stream while the grouped GEMMs of its neighbours run on the
+    compute stream, so the NVLink time hides behind the tensor-core time."""
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
-                 cap_factor=2.0, placement=None, group=None):
+                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
-        self.op = pkg.MoeOperator(experts, topk, d_model, d_mid, max_tokens, device=device,
-                                  ep_rank=rank, ep_size=world)
-        if placement is not None:
-            self.op.ep_set_placement(np.ascontiguousarray(placement, dtype=np.int32))
-        pairs = max_tokens * topk
-        self.cap = int(cap_factor * pairs)
+        self.chunks = chunks
+        self.tc = (max_tokens + chunks - 1) // chunks            # tokens per chunk
         dev = torch.device("cuda", device)
-        self.x_send = torch.empty(pairs, d_model, dtype=torch.float16, device=dev)
-        self.x_recv = torch.empty(self.cap, d_model, dtype=torch.float16, device=dev)
-        self.pairs_recv = torch.empty(self.cap, d_model, dtype=torch.float16, device=dev)
-        self.pairs_back = torch.empty(pairs, d_model, dtype=torch.float16, device=dev)
-        self.op.ep_attach(self.x_send, self.x_recv, self.pairs_recv, self.pairs_back, self.cap)
-        self.eoff = torch.empty(experts + 1, dtype=torch.int32, device=dev)
-        self.eoff_all = torch.empty(world * (experts + 1), dtype=torch.int32, device=dev)
+        self.ops, self.buf = [], []
+        for c in range(chunks):
+            op = pkg.MoeOperator(experts, topk, d_model, d_mid, self.tc, device=device,
+                                 ep_rank=rank, ep_size=world, ep_sm_margin=sm_margin if chunks > 1 else 0)
+            if c == 0:
+                if placement is not None:
+                    op.ep_set_placement(np.ascontiguousarray(placement, dtype=np.int32))
+            else:
+                op.share_weights(self.ops[0])
+            pairs = self.tc * topk
+            cap = int(cap_factor * pairs)
+            b = {"cap": cap,
+                 "x_send": torch.empty(pairs, d_model, dtype=torch.float16, device=dev),
+                 "x_recv": torch.empty(cap, d_model, dtype=torch.float16, device=dev),
+                 "pairs_recv": torch.empty(cap, d_model, dtype=torch.float16, device=dev),
+                 "pairs_back": torch.empty(pairs, d_model, dtype=torch.float16, device=dev),
+                 "eoff": torch.empty(experts + 1, dtype=torch.int32, device=dev),
+                 "eoff_all": torch.empty(world * (experts + 1), dtype=torch.int32, device=dev)}
+            op.ep_attach(b["x_send"], b["x_recv"], b["pairs_recv"], b["pairs_back"], cap)
+            self.ops.append(op)
+            self.buf.append(b)
+        self.op = self.ops[0]
+        self.comm = torch.cuda.Stream(device=dev)
         self.last_recv_rows = 0
 
     def load_q4cp(self, layer, gate_up, down):
         """Every rank passes the full tensors; the library keeps this rank's experts."""
-        self.op.load_q4cp(layer, gate_up, down)
+        self.ops[0].load_q4cp(layer, gate_up, down)
+        for op in self.ops[1:]:
+            op.share_weights(self.ops[0])
+
+    @property
+    def launches(self):
+        return sum(op.launches for op in self.ops)
 
     def forward(self, layer, x, logits, out):
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
-        st = torch.cuda.current_stream()
-        self.op.ep_route(layer, x, logits, eoff_out=self.eoff, stream=st)
-        dist.all_gather_into_tensor(self.eoff_all, self.eoff, group=self.group)
-        send, recv = exchange_splits(self.eoff_all.cpu().numpy(), self.rank, self.world)
-        R = int(sum(recv))
-        if R > self.cap:
-            raise RuntimeError("expert-parallel receive buffer too small: %d rows > capacity %d" % (R, self.cap))
-        self.last_recv_rows = R
-        dist.all_to_all_single(self.x_recv[:R], self.x_send[:T * self.k], recv, send, group=self.group)
-        self.op.ep_experts(layer, self.eoff_all, stream=st)
-        dist.all_to_all_single(self.pairs_back[:T * self.k], self.pairs_recv[:R], send, recv, group=self.group)
-        self.op.ep_combine(out, T, stream=st)
+        main = torch.cuda.current_stream()
+        C = min(self.chunks, (T + self.tc - 1) // self.tc)
+        span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
+        # 1. routing + gather of every chunk, expert offsets of all ranks
+        for c, (a, b) in enumerate(span):
+            B = self.buf[c]
+            self.ops[c].ep_route(layer, x[a:b], logits[a:b], eoff_out=B["eoff"], stream=main)
+            dist.all_gather_into_tensor(B["eoff_all"], B["eoff"], group=self.group)
+        routed = torch.cuda.Event()
+        routed.record(main)
+        splits, rows = [], 0
+        for c in range(C):
+            send, recv = exchange_splits(self.buf[c]["eoff_all"].cpu().numpy(), self.rank, self.world)
+            if sum(recv) > self.buf[c]["cap"]:
+                raise RuntimeError("expert-parallel receive buffer too small: %d rows > capacity %d"
+                                   % (sum(recv), self.buf[c]["cap"]))
+            splits.append((send, recv))
+            rows += sum(recv)
+        self.last_recv_rows = rows
+        # 2. dispatch / experts / combine, exchanges on the communication stream
+        self.comm.wait_event(routed)
+        disp = [torch.cuda.Event() for _ in range(C)]
+        done = [torch.cuda.Event() for _ in range(C)]
+        back = [torch.cuda.Event() for _ in range(C)]
+
+        def dispatch(c):
+            (a, b), (send, recv), B = span[c], splits[c], self.buf[c]
+            with torch.cuda.stream(self.comm):
+                dist.all_to_all_single(B["x_recv"][:sum(recv)], B["x_send"][:(b - a) * self.k], recv, send,
+                                       group=self.group)
+                disp[c].record(self.comm)
+
+        def combine_exchange(c):
+            (a, b), (send, recv), B = span[c], splits[c], self.buf[c]
+            with torch.cuda.stream(self.comm):
+                self.comm.wait_event(done[c])
+                dist.all_to_all_single(B["pairs_back"][:(b - a) * self.k], B["pairs_recv"][:sum(recv)], send, recv,
+                                       group=self.group)
+                back[c].record(self.comm)
+
+        dispatch(0)
+        for c in range(C):
+            if c + 1 < C:
+                dispatch(c + 1)
+            main.wait_event(disp[c])
+            self.ops[c].ep_experts(layer, self.buf[c]["eoff_all"], stream=main)
+            done[c].record(main)
+            combine_exchange(c)
+            if c >= 1:
+                main.wait_event(back[c - 1])
+                a, b = span[c - 1]
+                self.ops[c - 1].ep_combine(out[a:b], b - a, stream=main)
+        main.wait_event(back[C - 1])
+        a, b = span[C - 1]
+        self.ops[C - 1].ep_combine(out[a:b], b - a, stream=main)

@@ -63,7 +63,8 @@ typedef struct {
   int32_t decode_max_tokens; /* T up to which the GEMV path runs; 0 = default 16 (moe_naive_max, src/gpu/parts/40_model.inc:1963-1966) */
   int32_t ep_rank;        /* expert-parallel rank and size; size 1 = single GPU */
   int32_t ep_size;
-  int32_t reserved[4];
+  int32_t ep_sm_margin;   /* expert parallelism: SMs the grouped GEMM leaves free for the all-to-all kernels */
+  int32_t reserved[3];
 } b200moe_config;
 
 /* Replaces: GpuModel construction of the MoE workspaces (src/gpu/parts/40_model.inc:611-655)
@@ -156,6 +157,11 @@ int b200moe_route_static(const int32_t* topids_dev, const float* topw_dev, int s
  * ep_attach hands the library the four fp16 row buffers [rows][d_model] (caller-owned device
  * memory: x_send and pairs_back hold max_tokens*topk rows, x_recv and pairs_recv cap_rows). */
 int b200moe_ep_set_placement(b200moe_handle h, const int32_t* placed_id_of_expert_host);
+/* Makes `h` use the repacked weights (and placement) of `owner` instead of holding its own:
+ * several handles with separate workspaces can then work on different token chunks of the same
+ * layer at once (the chunked, overlapped expert-parallel forward). `owner` must outlive `h` and
+ * have the same shape configuration. */
+int b200moe_share_weights(b200moe_handle h, b200moe_handle owner);
 int b200moe_ep_attach(b200moe_handle h, void* x_send_dev, void* x_recv_dev, void* pairs_recv_dev,
                       void* pairs_back_dev, int64_t cap_rows);
 int b200moe_ep_route(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
