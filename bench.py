@@ -198,6 +198,8 @@ def main():
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="profiling aid: only the decode / verify leg, eager launches (no graph), prints its numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -238,6 +240,8 @@ def main():
     else:
         op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)
         op.load_q4cp(0, gu, dn)
+    if args.decode_only:
+        args.no_cpu = True
     want_cpu = rank == 0 and world == 1 and not args.no_cpu
     layer_host = {"gate_up": gu.cpu().numpy(), "down": dn.cpu().numpy()} if want_cpu else None
     op_dec = None
@@ -250,6 +254,10 @@ def main():
               q4cp_blob_device(torch, D, MID, gen2)]
         op_dec.load_shared_q4cp(0, sh[0], sh[1], sh[2],
                                 (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16))
+    if args.decode_only and op_dec is not None:
+        del gu, dn
+        print(json.dumps({"decode": decode_leg(torch, op_dec, peak_hbm, torch.cuda.current_stream(), graph=False)}))
+        return
     op_ref = None
     if world > 1 and args.check and rank == 0:
         op_ref = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)   # whole layer on one GPU, for the check
@@ -402,7 +410,7 @@ def main():
         dist.destroy_process_group()
 
 
-def decode_leg(torch, op, peak_hbm, stream):
+def decode_leg(torch, op, peak_hbm, stream, graph=True):
     """configs[1]: T = 1 and T = 5 with the shared expert; 64 rotated routings so that the
     selected experts are not resident in L2 from the previous call."""
     out = {}
@@ -427,30 +435,33 @@ def decode_leg(torch, op, peak_hbm, stream):
         op.profile_enable(False)
         # the engine replays decode as a captured graph (no host work between kernels): capture
         # one pass over the 64 rotated routings and replay it
-        side = torch.cuda.Stream()
-        side.wait_stream(stream)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(sets):
-                    op.moe_b(0, xs[i], lgs[i], o, stream=side)
-        stream.wait_stream(side)
-        reps = 4
-        graph.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        op.synchronize(stream)
-        us = e0.elapsed_time(e1) * 1e3 / (reps * sets)
+        if graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(stream)
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(cg, stream=side):
+                    for i in range(sets):
+                        op.moe_b(0, xs[i], lgs[i], o, stream=side)
+            stream.wait_stream(side)
+            reps = 4
+            cg.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                cg.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            op.synchronize(stream)
+            us = e0.elapsed_time(e1) * 1e3 / (reps * sets)
+        else:
+            us = stages["total"] * 1e3
         nbytes = (float(np.mean(uniq)) + 1) * BYTES_PER_EXPERT
         gbs = nbytes / (us * 1e-6) / 1e9
         out["T%d" % T] = {"us_per_call": us, "us_per_token": us / T, "unique_experts": float(np.mean(uniq)),
                           "algorithmic_bytes": nbytes, "hbm_gbs": gbs, "frac_of_hbm_peak": gbs / peak_hbm,
-                          "timing": "CUDA graph replay of 64 rotated routings",
+                          "timing": "CUDA graph replay of 64 rotated routings" if graph else "eager launches, stage timer",
                           "stage_us_eager": {k: round(v * 1e3, 2) for k, v in stages.items() if k != "calls"}}
     return out
 
