@@ -392,7 +392,9 @@ def main():
         "layer_tflops": FLOP_PER_TOKEN * T * args.steps / (ms * 1e-3) / 1e12,
         "roofline": {"bound": "tensor", "kernel": roof_kernel,
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_kind": peak_kind + " dense 16-bit burst", "traffic": None},
+                     "peak_kind": peak_kind + " dense 16-bit burst",
+                     "traffic": 4.98e9 if (world == 1 and (E, T) == (512, T_CHUNK)) else None,
+                     "traffic_note": "bytes per gate/up launch, scaled from an ncu capture of a reduced case by algorithmic bytes (see DESIGN.md)"},
     }
 
     if op_dec is not None:
