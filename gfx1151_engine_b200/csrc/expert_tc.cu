@@ -11,7 +11,7 @@
 // One CTA per SM, 24 warps with fixed roles. K blocks (64 wide) are handled in pairs:
 //   warp 0      producer of activation tiles: TMA tensor copies (128-byte swizzle, box of
 //               16/64/128/192 rows), one per K block, into a ring of 3 pair-slots in shared
-//               memory (2 when a tile needs two code books)
+//               memory
 //   warp 1      issues tcgen05.mma (A from tensor memory, B from shared memory): eight per
 //               pair behind ONE barrier wait and ONE commit; owns the tensor-memory allocation
 //   warp 3      relay: folds "activations of the pair have landed" into the barrier the MMA
@@ -19,17 +19,19 @@
 //   warps 4-19  dequantise: two sets of eight warps alternate pairs (set s owns tensor-memory
 //               slot s); thread = one weight row of one K block. Packed codes come straight
 //               from global memory (a warp's 32 rows are 512 contiguous bytes), one own pair
-//               ahead; each code byte indexes a 256-entry half2 pair table replicated per
-//               lane in shared memory (bank-conflict free); one half2 multiply by the group
-//               scale; the result goes straight into tensor memory (tcgen05.st) as the
-//               MMA's A operand
+//               ahead, addressed by running counters (the tile list is read one item
+//               ahead, never on the critical path); each code byte indexes a 256-entry half2
+//               pair table replicated per lane in shared memory (bank-conflict free, the
+//               address is one byte permute); one half2 multiply by the group scale; the
+//               result goes straight into tensor memory (tcgen05.st) as the MMA's A operand
 //   warps 20-23 epilogue: tcgen05.ld the fp32 accumulator, SwiGLU (gate/up rows live in
 //               different lanes, exchanged through shared memory, work split over all four
 //               warps) or plain convert, transposed through shared memory into 16-byte
 //               global stores; overlaps the next tile's main loop (two accumulators)
 // Measured limits that shaped this: a single thread starts a TMA copy only every ~170
-// cycles; a barrier poll costs ~250 cycles under load; issuing an MMA costs the issuing
-// thread ~85 cycles.
+// cycles; a barrier check costs 150-250 cycles under load; an M=128 MMA from tensor memory
+// takes N/2 + 9.5 cycles and the MMA queue holds about four of them; the table lookups are
+// bound by shared-memory wavefronts at ~25 code bytes per cycle per SM.
 // Every wait on an mbarrier is bounded; when one gives up the CTA records a status
 // word, stops issuing work, and leaves after releasing its tensor memory.
 #include "tc.h"
@@ -52,35 +54,43 @@ struct TcPlan {
 namespace {
 
 constexpr int kNS = 2;    // tensor-memory A slots; a slot holds a pair of K blocks (64 columns)
+constexpr int kNBSMax = 3;
 constexpr int kBStage = kTcTileN * 128;  // bytes of one K block of activations: rows x 64 halfs
 constexpr int kThreads = 768;           // 24 warps: 4 service, 16 dequantising, 4 epilogue
 constexpr int kAccCols = kTcTileN;       // columns per accumulator
-constexpr int kTmemA = 2 * kAccCols;     // first column of the A slots (384)
+constexpr int kTmemA = 2 * kAccCols;     // first column of the A slots
+static_assert(kTmemA + kNS * 64 <= 512, "tensor memory: two accumulators and the A slots");
 
 // Shared-memory map in ABSOLUTE addresses of the CTA's shared window (the dynamic
-// allocation starts at 1 KB when the kernel has no static shared memory). A pair table is
-// 256 entries x 32 lanes x 4 B and sits on a 32 KB boundary, so that a lookup address is
-//   table | code byte << 7 | lane << 2        (one shift, one and-or).
-// DUAL: tile rows 0..63 and 64..127 use different code books (the shared expert's separate
-// gate and up tensors); otherwise one table serves all rows and the space goes to a third
-// activation slot.
-template <bool DUAL>
+// allocation starts at 1 KB when the kernel has no static shared memory). The pair table
+// has one 256-byte line per code byte: 32 lanes x 4 B of code book 0 (tile rows 0..63, or all
+// rows), then 32 lanes x 4 B of code book 1 (tile rows 64..127 when the halves of a tile use
+// different books: the shared expert's separate gate and up tensors). It sits on a 64 KB
+// boundary, so that a lookup address is ONE byte permute:
+//   bytes { lane*4 (+128), code byte, table >> 16, 0 }.
+// The first activation slot fits below the table, the other two above it.
 struct Map {
-  static constexpr int kNBS = DUAL ? 2 : 3;            // activation ring depth, in pairs of K blocks
+  static constexpr int kNBS = 3;                       // activation ring depth, in pairs of K blocks
   static constexpr int kOffLow = 2048;                 // the dynamic allocation must start at or below this
-  static constexpr int kOffLut0 = 32768;
-  static constexpr int kOffLut1 = DUAL ? 65536 : 32768;
-  static constexpr int kOffU = DUAL ? 98304 : 65536;   // epilogue exchange + output tile (12 KB)
-  static constexpr int kOffBar = kOffU + 12288;        // barriers and flags (1 KB)
-  static constexpr int kOffB = kOffBar + 1024;         // activation ring, 1 KB aligned
-  static constexpr int kSmemEnd = kOffB + kNBS * 2 * kBStage;
+  static constexpr int kOffBar = 2048;                 // barriers and flags (1 KB)
+  static constexpr int kOffU = 3072;                   // epilogue exchange + output tile (12 KB)
+  static constexpr int kOffB0 = 15360;                 // activation slot 0 (1 KB aligned)
+  static constexpr int kOffLut = 65536;                // 256 lines of 256 B
+  static constexpr int kOffB1 = 131072;                // activation slots 1, 2
+  static constexpr int kSmemEnd = kOffB1 + 2 * 2 * kBStage;
   static constexpr int kSmemBytes = kSmemEnd - 1024;   // dynamic bytes requested
+  static_assert(kOffB0 + 2 * kBStage <= kOffLut, "slot 0 overlaps the table");
   static_assert(kSmemEnd <= 233472, "shared memory map exceeds the SM");
+  __host__ __device__ static constexpr uint32_t slot(uint32_t s) {
+    return s == 0 ? (uint32_t)kOffB0 : (uint32_t)(kOffB1 + (s - 1) * 2 * kBStage);
+  }
 };
 
 // barrier slots (8 bytes each) inside the barrier block
-constexpr int kBarAFull = 0,
-              kBarBFull = kBarAFull + kNS, kBarDone = kBarBFull + 3, kBarAccFull = kBarDone + 3,
+constexpr int kBarAFull = 0,                   // [tensor-memory slot]: A of a pair stored, activations landed
+              kBarBFull = kBarAFull + kNS,     // [activation slot]
+              kBarDone = kBarBFull + kNBSMax,  // [activation slot]: all MMAs of a pair have completed
+              kBarAccFull = kBarDone + kNBSMax,
               kBarAccEmpty = kBarAccFull + 2, kNumBars = kBarAccEmpty + 2;
 static_assert(kNumBars * 8 + 16 + 32 <= 1024, "barrier block too small");
 
@@ -302,8 +312,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   const uint32_t dyn0 = smem_u32(smem_raw);
   uint8_t* const smem = smem_raw - dyn0;
   constexpr uint32_t sbase = 0;
-  using M = Map<DUAL>;
-  constexpr int kNBS = M::kNBS, kOffLow = M::kOffLow, kOffU = M::kOffU, kOffBar = M::kOffBar, kOffB = M::kOffB,
+  using M = Map;
+  constexpr int kNBS = M::kNBS, kOffLow = M::kOffLow, kOffU = M::kOffU, kOffBar = M::kOffBar,
                 kSmemEnd = M::kSmemEnd;
   {
     uint32_t dyn_size;
@@ -324,7 +334,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
 
   // ---- set-up ----
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNS; i++) mbar_init(bars + 8 * (kBarAFull + i), 9);  // 8 dequantising warps of a set + relay
+    for (int i = 0; i < kNS; i++) mbar_init(bars + 8 * (kBarAFull + i), 9);  // 8 dequantising warps + relay
     for (int i = 0; i < kNBS; i++) {
       mbar_init(bars + 8 * (kBarBFull + i), 1);    // activation producer (with byte count)
       mbar_init(bars + 8 * (kBarDone + i), 1);     // one tcgen05.commit per pair
@@ -342,7 +352,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     const int half_id = i >> 13, entry = (i >> 5) & 255;
     const float lo = img.book[half_id * 16 + (entry & 15)], hi = img.book[half_id * 16 + (entry >> 4)];
     if (half_id == 0 || DUAL)
-      *(__half2*)(smem + (half_id ? M::kOffLut1 : M::kOffLut0) + entry * 128 + (i & 31) * 4) = __floats2half2_rn(lo, hi);
+      *(__half2*)(smem + M::kOffLut + entry * 256 + half_id * 128 + (i & 31) * 4) = __floats2half2_rn(lo, hi);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -367,12 +377,14 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     if (lane == 0) {
       uint32_t pi = 0;
       bool ok = true;
+      Tile t_ahead = (int)blockIdx.x < n_items ? p.tiles[blockIdx.x / img.n_mtiles] : Tile{0, 0, 0};
       for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-        const Tile t = p.tiles[it / img.n_mtiles];
+        const Tile t = t_ahead;  // read one item ahead: its latency is off this loop's critical path
+        if (it + (int)gridDim.x < n_items) t_ahead = p.tiles[(it + gridDim.x) / img.n_mtiles];
         const int n_pad = (t.count + 15) & ~15;
         // smallest box that covers the tile's rows: 16, 64, 128 or 192 rows of 64 halfs
         const CUtensorMap* map = n_pad <= 16 ? &map16 : n_pad <= 64 ? &map64 : n_pad <= 128 ? &map128 : &map192;
-        const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : 192) * 128;
+        const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : kTcTileN) * 128;
         for (int pp = 0; pp < NP && ok; pp++, pi++) {
           const uint32_t slot = pi % kNBS, sph = (pi / kNBS) & 1;
           const int nk = min(2, KB - 2 * pp);
@@ -382,17 +394,21 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           const uint32_t bar = bars + 8 * (kBarBFull + slot);
           mbar_expect_tx(bar, nk * bytes);
           for (int j = 0; j < nk; j++)
-            tma_load_2d(sbase + kOffB + (slot * 2 + j) * kBStage, map, (2 * pp + j) * kTileK, t.first, bar);
+            tma_load_2d(sbase + M::slot(slot) + j * kBStage, map, (2 * pp + j) * kTileK, t.first, bar);
         }
       }
     }
   } else if (warp == 1) {
     // ================= MMA issue =================
     // The whole warp runs the loop (converged); one elected lane issues.
+    // (Measured: checking a barrier costs this warp 150-250 cycles under load even when its
+    // phase is long complete, and the MMA queue holds about four instructions.)
     uint32_t pi = 0, li = 0;
     bool ok = true;
+    Tile t_ahead = (int)blockIdx.x < n_items ? p.tiles[blockIdx.x / img.n_mtiles] : Tile{0, 0, 0};
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, li++) {
-      const Tile t = p.tiles[it / img.n_mtiles];
+      const Tile t = t_ahead;  // read one item ahead: its latency is off this loop's critical path
+      if (it + (int)gridDim.x < n_items) t_ahead = p.tiles[(it + gridDim.x) / img.n_mtiles];
       const int n_pad = (t.count + 15) & ~15;
       const uint32_t idesc = instr_desc(n_pad);
       const uint32_t acc = li & 1, accph = (li >> 1) & 1;
@@ -410,7 +426,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         if (!ok) break;
         if (lane == 0) TR(1, pi, 0);
         tc_fence_after();
-        const uint64_t bdesc = b_descriptor(sbase + kOffB + bslot * 2 * kBStage);
+        const uint64_t bdesc = b_descriptor(sbase + M::slot(bslot));
         const uint32_t a_tmem = tmem + kTmemA + aslot * 64;
         if (elect_one()) {
 #pragma unroll
@@ -421,7 +437,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
             for (int ks = 0; ks < 4; ks++)
               tc_mma_ts(d_tmem, a_tmem + 32 + ks * 8, bdesc + (uint64_t)((kBStage >> 4) + ks * 2), idesc, 1u);
           }
-          // one commit per pair: frees the activation slot for the producer and, two pairs
+          // one commit per pair: frees the activation slot for the producer and, kNS pairs
           // later, the tensor-memory slot for the dequantising warps
           tc_commit(bars + 8 * (kBarDone + bslot));
           if (pp == NP - 1) tc_commit(bars + 8 * (kBarAccFull + acc));
@@ -441,34 +457,59 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // one contiguous 512-byte read per half), one own pair ahead of their use.
     const int set = (warp - 4) >> 3, kblk = ((warp - 4) >> 2) & 1, quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const uint32_t lut = (uint32_t)(r >= 64 ? M::kOffLut1 : M::kOffLut0) | (uint32_t)(lane * 4);
+    // constant half of the lookup address: table base, code book, lane
+    const uint32_t lut = (uint32_t)M::kOffLut | (uint32_t)(DUAL && r >= 64 ? 128 : 0) | (uint32_t)(lane * 4);
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t total = (uint32_t)my_items * (uint32_t)NP;
     uint4 ca = make_uint4(0, 0, 0, 0), cb = ca, na = ca, nb = ca;
     RowMetaTc sc = RowMetaTc{0, 0, 0, 0}, nsc = sc;
-    auto fetch = [&](uint32_t pj, uint4& a, uint4& b, RowMetaTc& s2x) {
-      if (pj >= total) return;
-      const int item = blockIdx.x + (int)(pj / (uint32_t)NP) * gridDim.x, kb = 2 * (int)(pj % (uint32_t)NP) + kblk;
-      if (kb >= KB) return;
-      const uint8_t* tp = img.tile(p.tiles[item / img.n_mtiles].expert, item % img.n_mtiles, kb);
-      a = __ldg((const uint4*)(tp + r * 16));
-      b = __ldg((const uint4*)(tp + 2048 + r * 16));
-      if (FMT == kQ4CP) {
-        s2x.a = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
-      } else if (FMT == kQ4K) {
-        const uint2 u = __ldg((const uint2*)(tp + kCodeBytes + r * 8));
-        s2x.a = u.x;
-        s2x.b = u.y;
-      } else {
-        const uint4 u = __ldg((const uint4*)(tp + kCodeBytes + r * 16));
-        s2x = RowMetaTc{u.x, u.y, u.z, u.w};
+    // The fetch stream runs one own pair ahead of the decode. It walks (item, pair) with
+    // counters, and the first tile of the NEXT item is looked up when an item is entered,
+    // so that no fetch waits for the dependent read of the tile list.
+    const size_t tile_b = img.tile_stride();
+    auto item_base = [&](int io) -> const uint8_t* {
+      const int item = blockIdx.x + io * (int)gridDim.x;
+      if (io >= my_items) return nullptr;
+      return img.tile(p.tiles[item / img.n_mtiles].expert, item % img.n_mtiles, 0);
+    };
+    const int io_step = NP == 1 ? 2 : 1;  // a set visits every item, or every other one when an item is one pair
+    int f_io = set / NP, f_pp = set % NP;
+    const uint8_t* f_base = item_base(f_io);
+    const uint8_t* f_next = item_base(f_io + io_step);
+    auto fetch = [&](uint4& a, uint4& b, RowMetaTc& s2x) {
+      const int kb = 2 * f_pp + kblk;
+      if (f_base != nullptr && kb < KB) {
+        const uint8_t* tp = f_base + (size_t)kb * tile_b;
+        a = __ldg((const uint4*)(tp + r * 16));
+        b = __ldg((const uint4*)(tp + 2048 + r * 16));
+        if (FMT == kQ4CP) {
+          s2x.a = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
+        } else if (FMT == kQ4K) {
+          const uint2 u = __ldg((const uint2*)(tp + kCodeBytes + r * 8));
+          s2x.a = u.x;
+          s2x.b = u.y;
+        } else {
+          const uint4 u = __ldg((const uint4*)(tp + kCodeBytes + r * 16));
+          s2x = RowMetaTc{u.x, u.y, u.z, u.w};
+        }
+      }
+      f_pp += 2;
+      if (f_pp >= NP) {
+        f_pp -= NP * io_step;  // NP == 1: two items further, same pair
+        f_io += io_step;
+        f_base = f_next;
+        f_next = item_base(f_io + io_step);
       }
     };
-    fetch(set, ca, cb, sc);
+    fetch(ca, cb, sc);
+    int c_pp = set % NP;  // pair-in-item of the decode stream
     bool ok = true;
     for (uint32_t pi = set; pi < total && ok; pi += 2) {
-      const bool mine = 2 * (int)(pi % (uint32_t)NP) + kblk < KB;  // false only for the second K block of an odd tail
-      fetch(pi + 2, na, nb, nsc);
+      const bool mine = 2 * c_pp + kblk < KB;  // false only for the second K block of an odd tail
+      const uint32_t aslot = pi % kNS;
+      c_pp += 2;
+      if (c_pp >= NP) c_pp -= NP * io_step;
+      fetch(na, nb, nsc);
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 0);
       uint32_t v[32];
       if (mine) {
@@ -482,7 +523,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           for (int q = 0; q < 4; q++) {
 #pragma unroll
             for (int b = 0; b < 4; b++) {
-              const uint32_t addr = ((b == 0 ? w4[q] << 7 : w4[q] >> (8 * b - 7)) & 0x7F80u) | lut;
+              const uint32_t addr = __byte_perm(w4[q], lut, 0x7604u | (uint32_t)(b << 4));
               uint32_t pair;
               asm("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(addr));
               __half2 w2 = gd.weight(pair, q * 4 + b);
@@ -493,7 +534,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       }
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 1);
       if (pi >= (uint32_t)kNS) {
-        // the slot is free once the MMAs of this set's previous pair have completed
+        // the slot is free once the MMAs of the pair that used it before have completed
         const uint32_t q = pi - kNS;
         ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 7);
         ok = __all_sync(0xffffffffu, ok);
@@ -502,13 +543,13 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 2);
       if (mine) {
         tc_fence_after();
-        tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + set * 64 + kblk * 32, v);
+        tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + aslot * 64 + kblk * 32, v);
         tc_wait_st();
       }
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 3);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + set));
+      if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + aslot));
       ca = na;
       cb = nb;
       sc = nsc;
@@ -522,6 +563,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         for (int pp = 0; pp < NP && ok; pp++, pi++) {
           ok = mbar_wait(bars + 8 * (kBarBFull + pi % kNBS), (pi / kNBS) & 1, abort_flag, p.status, 9);
           if (!ok) break;
+          // an arrival must fall into the barrier's current phase: the slot's previous use is
+          // over once the MMAs of pair pi - kNS have completed
           if (pi >= (uint32_t)kNS) {
             const uint32_t q = pi - kNS;
             ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 10);
@@ -538,8 +581,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     volatile int* ep_ok = (volatile int*)(smem + kOffBar + kNumBars * 8 + 16);
     uint32_t li = 0;
     bool ok = true;
+    Tile t_ahead = (int)blockIdx.x < n_items ? p.tiles[blockIdx.x / img.n_mtiles] : Tile{0, 0, 0};
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, li++) {
-      const Tile t = p.tiles[it / img.n_mtiles];
+      const Tile t = t_ahead;
+      if (it + (int)gridDim.x < n_items) t_ahead = p.tiles[(it + gridDim.x) / img.n_mtiles];
       const int mt = it % img.n_mtiles;
       const uint32_t acc = li & 1, accph = (li >> 1) & 1;
       ok = mbar_wait(bars + 8 * (kBarAccFull + acc), accph, abort_flag, p.status, 8, 256);
@@ -651,7 +696,7 @@ template <bool UP, bool DUAL, int FMT>
 cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
                    const Tile* tiles, const int32_t* n_tiles, int max_tiles, __half* out, int out_ld,
                    int32_t* status, cudaStream_t st) {
-  constexpr int kSmemBytes = Map<DUAL>::kSmemBytes;
+  constexpr int kSmemBytes = Map::kSmemBytes;
   static bool attr_set = false;  // one flag per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(k_expert_tc<UP, DUAL, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -659,7 +704,7 @@ cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  KParams p{img, tiles, n_tiles, out, out_ld, status, UP ? plan->trace : nullptr};
+  KParams p{img, tiles, n_tiles, out, out_ld, status, (UP != (getenv("B200MOE_TC_TRACE_DOWN") != nullptr)) ? plan->trace : nullptr};
   long long max_items = (long long)max_tiles * img.n_mtiles;
   const int usable = plan->sms - plan->margin > 1 ? plan->sms - plan->margin : 1;
   int grid = (int)(max_items < usable ? max_items : usable);
