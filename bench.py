@@ -199,7 +199,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
     ap.add_argument("--decode-only", action="store_true",
-                    help="profiling aid: only the decode / verify leg, eager launches (no graph), prints its numbers")
+                    help="profiling aid: only the decode / verify leg, prints its numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -256,7 +256,7 @@ def main():
                                 (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16))
     if args.decode_only and op_dec is not None:
         del gu, dn
-        print(json.dumps({"decode": decode_leg(torch, op_dec, peak_hbm, torch.cuda.current_stream(), graph=False)}))
+        print(json.dumps({"decode": decode_leg(torch, op_dec, peak_hbm, torch.cuda.current_stream(), graph=True)}))
         return
     op_ref = None
     if world > 1 and args.check and rank == 0:

@@ -508,15 +508,15 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
   const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO && L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP &&
                     pairs + (shared ? T : 0) <= h->dec_rows && std::min(E, pairs) + 1 <= gemv_max_runs() &&
-                    d <= gemv_max_k() && mid <= gemv_max_k() && d % 32 == 0 && mid % 32 == 0;
+                    d <= gemv_max_k() && mid <= gemv_max_mid() && d % 32 == 0 && mid % 32 == 0;
   if (gemv) {
     // decode / verify: persistent dequant GEMV, routed and shared expert in one launch each
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
     CU_TRY(h, launch_up_gemv(L.gu, shared ? &L.sh_gu : nullptr, x, d, mid, h->rb.tokidx, h->rb.runs,
-                             h->rb.n_runs, (float*)h->hid, st));
+                             h->rb.n_runs, (__half*)h->hid, st));
     if (ev) CU_TRY(h, cudaEventRecord(ev[3], st));
-    CU_TRY(h, launch_down_gemv(L.dn, shared ? &L.sh_dn : nullptr, (const float*)h->hid, d, mid, h->rb.runs,
-                               h->rb.n_runs, (float*)h->pairs, st));
+    CU_TRY(h, launch_down_gemv(L.dn, shared ? &L.sh_dn : nullptr, (const __half*)h->hid, d, mid,
+                               h->rb.runs, h->rb.n_runs, (float*)h->pairs, st));
     if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
                                  shared ? pairs : -1, out, st));

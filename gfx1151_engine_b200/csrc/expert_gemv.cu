@@ -4,19 +4,27 @@
 // (token, expert) the 2*mid gate/up dot products, SwiGLU, then the d down dot products.
 //
 // At one token the whole layer is ~78 MB of 4-bit weights and 138 M multiply-adds; what
-// decides the speed is how few instructions it takes to turn a code into a multiply-add.
-//   * Like the reference's kernel, the lanes of a warp split K: lane l owns the 32-groups
-//     l, l+32, ... of a row and keeps the matching activations in registers as half2, so the
-//     inner loop reads nothing but weights.
+// decides the speed is (1) that DRAM sees long contiguous reads, (2) how many bytes each SM
+// keeps in flight, (3) how few instructions and shared-memory wavefronts turn a code into a
+// multiply-add.
+//   * A lane owns a weight ROW: in the tiled image the 32 rows of a warp are 512 contiguous
+//     bytes per half K block, so every load instruction of a warp is one long burst. (Lanes
+//     that split K instead -- the reference's mapping -- read 16-byte pieces 2 KB apart from
+//     this layout and reached 1 TB/s.) A lane's dot product needs no cross-lane reduction.
+//   * The 16 warps of a CTA split K of the same rows; their partial sums meet in shared
+//     memory and are added in a fixed order. The activations of the current token are staged
+//     in shared memory as fp16 and read by broadcast (one 16-byte load per 4 code bytes).
 //   * A code BYTE (two codes) is decoded by one lookup in a 256-entry half2 table that is
-//     replicated per lane in shared memory (no bank conflicts); the eight products of one
-//     32-bit code word are chained in half2 (one HFMA2 per byte), then widened and added in
-//     fp32; the fp16 group scale multiplies the fp32 sum of a group once.
-//   * Rows are reduced across the warp by shuffles; gate row r and up row r are handled by
-//     the same warp, so SwiGLU needs no second pass and no partial sums exist anywhere.
-//   * The kernel is persistent: the (run, token, row block) space is cut into one contiguous
-//     chunk per warp, token-major, so a warp reloads its activations only when the token
-//     changes and the tables are built once per CTA.
+//     replicated per lane in shared memory (no bank conflicts); a table line is 256 bytes, on
+//     a 64 KB boundary, so the lookup address is a single byte permute. The two products go
+//     into an fp32 accumulator with the mixed-precision multiply-add (f32 += f16 * f16):
+//     exact products, fp32 sums. The fp16 group scale multiplies the fp32 sum of a group once.
+//   * A warp's share of a task is at most four K blocks = eight 16-byte loads per lane; as
+//     soon as one K block has been consumed, the same registers receive the matching block
+//     of the CTA's NEXT task, so every SM keeps ~64 KB in flight while it computes.
+//   * Gate row r and up row r sit in lanes l and l+16 of the same warp: SwiGLU is a shuffle.
+//   * The kernels are persistent: (row of the permuted activations, row block) tasks are cut
+//     into one contiguous range per CTA; the tables are built once per CTA.
 // (mma.sync was tried here first: on this GPU it retires an m16n8k16 only every ~50 cycles
 // per SM, which made the kernel several times slower than the multiply-add form.)
 #include "kernels.h"
@@ -25,10 +33,13 @@ namespace b200moe {
 
 namespace {
 
-constexpr int kGemvThreads = 512;     // 16 warps, in teams of 1, 2 or 4
-constexpr int kGemvRows = 4;          // weight rows per task (gate/up: 4 gate + 4 up rows)
-constexpr int kGemvMaxChunks = 4;     // warps per team: K <= 4096
+constexpr int kGemvThreads = 512;     // 16 warps
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kKpw = 4;               // K blocks per warp and task, at most
 constexpr int kGemvMaxRuns = 192;
+constexpr int kGemvMaxK = 4096;       // staged activations: 8 KB of fp16
+constexpr uint32_t kTab0 = 65536;     // absolute shared addresses of the two table blocks
+constexpr uint32_t kTab1 = 131072;
 
 struct GemvParams {
   Image img;             // routed experts
@@ -39,33 +50,43 @@ struct GemvParams {
   int mid;
   const uint16_t* x;     // gate/up: bf16 [T][d]
   const int32_t* tokidx;
-  const float* hid;      // down: fp32 [rows][mid]
-  float* out;            // gate/up: hid fp32 [rows][mid]; down: pairs fp32 [rows][d]
+  __half* hid;           // gate/up writes, down reads: fp16 [rows][mid] = silu(gate) * up
+  float* out;            // down: pairs fp32 [rows][d]
 };
 
-__device__ __forceinline__ __half2 lds_half2(uint32_t addr) {
+__device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
   uint32_t v;
   asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return *(__half2*)&v;
+  return v;
+}
+
+// acc += w.lo * x.lo + w.hi * x.hi with exact products and fp32 sums
+__device__ __forceinline__ void fma_pair(float& acc, uint32_t w, uint32_t x) {
+  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+      "mov.b32 {wl, wh}, %1;\n\t"
+      "mov.b32 {xl, xh}, %2;\n\t"
+      "fma.rn.f32.f16 %0, wl, xl, %0;\n\t"
+      "fma.rn.f32.f16 %0, wh, xh, %0;\n\t}"
+      : "+f"(acc)
+      : "r"(w), "r"(x));
 }
 
 // sum over one 16-byte chunk (32 codes of one group) of w[k] * x[k], as float.
-// lut: shared-window address of this lane's column of the pair table (entry stride 128 B).
-__device__ __forceinline__ float chunk_dot(const uint4 c, uint32_t lut, const uint32_t* xh) {
+// lut: constant half of the lookup address { lane*4 (+128), -, table >> 16, 0 };
+// xs: shared address of the 32 fp16 activations of the group (same for all lanes: broadcast).
+__device__ __forceinline__ float chunk_dot(const uint4 c, uint32_t lut, uint32_t xs) {
   const uint32_t w4[4] = {c.x, c.y, c.z, c.w};
-  float sum = 0.f;
+  float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int q = 0; q < 4; q++) {
-    // two code bytes (four products) per half2 chain, then widened: keeps the fp16 rounding
-    // of the sums at the level of the operand rounding
-    __half2 a = __hmul2(lds_half2(lut + ((w4[q] & 0xFFu) << 7)), *(const __half2*)&xh[q * 4 + 0]);
-    a = __hfma2(lds_half2(lut + (((w4[q] >> 8) & 0xFFu) << 7)), *(const __half2*)&xh[q * 4 + 1], a);
-    __half2 b = __hmul2(lds_half2(lut + (((w4[q] >> 16) & 0xFFu) << 7)), *(const __half2*)&xh[q * 4 + 2]);
-    b = __hfma2(lds_half2(lut + ((w4[q] >> 24) << 7)), *(const __half2*)&xh[q * 4 + 3], b);
-    const float2 f = __half22float2(a), e = __half22float2(b);
-    sum += (f.x + f.y) + (e.x + e.y);
+    uint32_t x0, x1, x2, x3;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(xs + q * 16));
+    fma_pair(s0, lds_b32(__byte_perm(w4[q], lut, 0x7604)), x0);
+    fma_pair(s1, lds_b32(__byte_perm(w4[q], lut, 0x7614)), x1);
+    fma_pair(s0, lds_b32(__byte_perm(w4[q], lut, 0x7624)), x2);
+    fma_pair(s1, lds_b32(__byte_perm(w4[q], lut, 0x7634)), x3);
   }
-  return sum;
+  return s0 + s1;
 }
 
 __device__ __forceinline__ uint32_t pack_half2_sat(float a, float b) {
@@ -73,172 +94,208 @@ __device__ __forceinline__ uint32_t pack_half2_sat(float a, float b) {
   return *(uint32_t*)&h;
 }
 
+
+
+struct GemvShared {
+  int first[kGemvMaxRuns + 2];  // unit prefix: rows before run i ("unit" = one row of the permuted activations)
+  int units;
+  int bad;
+};
+
 template <bool UP>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 k_gemv(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t gsm[];
-  const bool has_sh = p.img_sh.data != nullptr;
-  uint32_t* lut_r = (uint32_t*)gsm;                  // routed book          [256][32] half2
-  uint32_t* lut_s0 = lut_r + 256 * 32;               // shared, tile rows 0..63
-  uint32_t* lut_s1 = lut_s0 + (p.img_sh.dual_book ? 256 * 32 : 0);
-  __shared__ __half2 s_book[3][256];
-  __shared__ int s_first[kGemvMaxRuns + 2];          // unit prefix: rows before run i
-  __shared__ int s_units;
+  __shared__ GemvShared sh;
+  __shared__ __align__(16) __half xs[kGemvMaxK];   // activations of the current unit
+  __shared__ float red[2][kGemvWarps][32];          // partial sums of the K slices, double-buffered by task
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t a_lut_r = (uint32_t)__cvta_generic_to_shared(lut_r) + lane * 4,
-                 a_lut_s0 = (uint32_t)__cvta_generic_to_shared(lut_s0) + lane * 4,
-                 a_lut_s1 = (uint32_t)__cvta_generic_to_shared(lut_s1) + lane * 4;
+  const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(gsm);
+  uint8_t* const smem = gsm - dyn0;  // smem + A is the generic pointer of absolute shared address A
+  const bool has_sh = p.img_sh.data != nullptr;
+  const bool two = UP && has_sh && p.img_sh.dual_book;
   const int n_routed = p.n_runs[0];
   const int n_runs_all = min(n_routed + (has_sh ? 1 : 0), kGemvMaxRuns);
-  auto run_of = [&](int i) { return i < n_routed ? p.runs[i] : p.runs[kMaxExperts]; };
 
-  // ---- pair tables (entry b = f16(book[b & 15]), f16(book[b >> 4])) and the unit prefix ----
-  for (int i = threadIdx.x; i < 3 * 256; i += kGemvThreads) {
-    const int b = i >> 8, e = i & 255;
-    const float* bk = b == 0 ? p.img.book : (has_sh ? p.img_sh.book + (b - 1) * 16 : nullptr);
-    if (bk) s_book[b][e] = __floats2half2_rn(bk[e & 15], bk[e >> 4]);
-  }
-  for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads) s_first[i] = run_of(i).count;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int i = 0; i < n_runs_all; i++) {
-      const int c = s_first[i];
-      s_first[i] = acc;
-      acc += c;
-    }
-    s_first[n_runs_all] = acc;
-    s_units = acc;
-  }
-  __syncthreads();
+  // ---- pair tables and unit prefix. Table lines: entry b = (f16(book[b & 15]), f16(book[b >> 4])),
+  // 256 bytes per code byte: [32 lanes x 4 B of book A][32 lanes x 4 B of book B]. Block 0 holds
+  // the routed book (A) and the shared expert's first book (B); block 1 the shared expert's
+  // second book (rows 64..127 of its gate/up tiles, when that image has two books). The blocks
+  // live at fixed absolute addresses: a launch whose dynamic allocation does not cover them is
+  // refused (uniform for the CTA; the host sizes the allocation accordingly). ----
   {
-    const int nl = has_sh ? (p.img_sh.dual_book ? 3 : 2) : 1;
-    for (int i = threadIdx.x; i < nl * 256 * 32; i += kGemvThreads)
-      lut_r[i] = *(const uint32_t*)&s_book[i >> 13][(i >> 5) & 255];
+    uint32_t dyn_size;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+    const uint32_t need_end = two ? kTab1 + 65536 : kTab0 + 65536;
+    const bool fits = dyn0 <= kTab0 && dyn0 + dyn_size >= need_end;
+    if (threadIdx.x == 0) sh.bad = fits ? 0 : 1;
+    const int nb = has_sh ? (two ? 3 : 2) : 1;
+    if (fits) {
+      for (int i = threadIdx.x; i < nb * 256 * 32; i += kGemvThreads) {
+        const int b = i >> 13, e = (i >> 5) & 255, l = i & 31;
+        const float* bk = b == 0 ? p.img.book : p.img_sh.book + (b - 1) * 16;
+        *(__half2*)(smem + (b == 2 ? kTab1 : kTab0) + e * 256 + (b == 1 ? 128 : 0) + l * 4) =
+            __floats2half2_rn(bk[e & 15], bk[e >> 4]);
+      }
+    }
+    for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads)
+      sh.first[i] = (i < n_routed ? p.runs[i] : p.runs[kMaxExperts]).count;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int i = 0; i < n_runs_all; i++) {
+        const int c = sh.first[i];
+        sh.first[i] = acc;
+        acc += c;
+      }
+      sh.first[n_runs_all] = acc;
+      sh.units = acc;
+    }
+    __syncthreads();
+    if (sh.bad) return;
   }
-  __syncthreads();
 
-  // tasks: (unit = one row of the permuted activations, block of kGemvRows outputs), handled
-  // by a TEAM of ts warps: warp wq of a team owns the 32-groups wq*32 + lane of every row, so
-  // a lane keeps only 32 activations (16 registers) and many warps fit on an SM; the ts
-  // partial sums of a row meet in shared memory and are added in a fixed order.
-  const int n_groups = p.K / 32;
-  const int n_chunks = (n_groups + 31) / 32;
-  const int ts = n_chunks <= 1 ? 1 : n_chunks <= 2 ? 2 : 4;
-  const int teams_per_cta = (kGemvThreads / 32) / ts;
-  const int team_local = warp / ts, wq = warp % ts;
+  // ---- geometry. gate/up: a task = 16 hidden outputs (lanes 0..15 the gate rows, lanes 16..31
+  // the matching up rows), every warp a K slice. down: a task = 64 output rows, warps = 2 row
+  // groups x 8 K slices. ----
+  const int KB = p.K / kTileK;
+  constexpr int kSlices = UP ? kGemvWarps : kGemvWarps / 2;
+  const int slice = UP ? warp : warp >> 1;
+  const int kpw = (KB + kSlices - 1) / kSlices;  // <= kKpw (the host checks K)
+  const int kb0 = slice * kpw;
   const int out_rows = UP ? p.mid : p.img.n_mtiles * kTileM;
-  const int per_unit = out_rows / kGemvRows;
-  const long long total = (long long)s_units * per_unit;
-  const int n_teams = gridDim.x * teams_per_cta, team = blockIdx.x * teams_per_cta + team_local;
-  const int chunk = (int)((total + n_teams - 1) / n_teams);
-  const int t0 = (int)min((long long)team * chunk, total), t1 = (int)min((long long)t0 + chunk, total);
-  const int grp = lane + 32 * wq;
-  const bool live = grp < n_groups;
-  constexpr int kR = UP ? 2 * kGemvRows : kGemvRows;
-  __shared__ float s_part[2][kGemvThreads / 32][kR];
+  const int tpu = UP ? out_rows / 16 : out_rows / 64;  // tasks per unit
+  const long long total = (long long)sh.units * tpu;
+  const long long base = total / gridDim.x, rem = total % gridDim.x;
+  const long long c0 = blockIdx.x * base + min((long long)blockIdx.x, rem), c1 = c0 + base + ((long long)blockIdx.x < rem ? 1 : 0);
+  constexpr size_t tile_b = tile_bytes(kQ4CP);  // both images are q4cp on this path
+  const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
 
-  uint32_t xh[16];  // activations of this lane's group, half2
-  int cur_unit = -1, ri = 0;
+  uint4 cw[2 * kKpw];
+  uint32_t sw[kKpw];
+  int cur_unit = -1, cur_tok = -1, buf = 0;
+  bool routed = true, have = false;
   Run run = Run{0, 0, 0};
-  for (int task = t0; task < t1; task++) {
-    const int unit = task / per_unit, j = task % per_unit;
+  const uint8_t* ebase = nullptr;  // first tile of the run's expert
+  size_t mt_b = 0;
+  uint32_t lut = 0;
+  // this lane's row of task j: tile base (first K block of the warp's slice), tile row
+  // this lane's row of task j: pointers to its codes and to its scale pair in the first K
+  // block of the warp's slice
+  auto locate = [&](int j, const uint8_t*& pc, const uint8_t*& ps) {
+    int mt, r;
+    if (UP) {
+      mt = j >> 2;
+      r = (lane < 16 ? 0 : 48) + (j & 3) * 16 + lane;  // gate rows 0..63, up rows 64..127
+    } else {
+      mt = j >> 1;
+      r = (j & 1) * 64 + (warp & 1) * 32 + lane;
+    }
+    const uint8_t* tb = ebase + (size_t)mt * mt_b + (size_t)kb0 * tile_b;
+    pc = tb + r * 16;
+    ps = tb + kCodeBytes + r * 4;
+  };
+  for (long long task = c0; task < c1; task++) {
+    const int unit = (int)(task / tpu), j = (int)(task % tpu);
     if (unit != cur_unit) {
-      // ---- new token row: find its run, reload this lane's activations ----
+      // ---- new row of the permuted activations: its run, its tables, its activations ----
       int lo = 0, hi = n_runs_all - 1;
       while (lo < hi) {
         const int m = (lo + hi + 1) >> 1;
-        if (s_first[m] <= unit) lo = m; else hi = m - 1;
+        if (sh.first[m] <= unit) lo = m; else hi = m - 1;
       }
-      ri = lo;
-      run = run_of(ri);
-      const int row = run.first + (unit - s_first[ri]);
-#pragma unroll
-      for (int q = 0; q < 16; q++) xh[q] = 0u;
-      if (live) {
-        if (UP) {
-          const uint4* src = (const uint4*)(p.x + (size_t)p.tokidx[row] * p.K + grp * 32);
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const uint4 u = __ldg(src + q);
+      routed = lo < n_routed;
+      run = routed ? p.runs[lo] : p.runs[kMaxExperts];
+      run.first += unit - sh.first[lo];
+      const Image& im = routed ? p.img : p.img_sh;
+      mt_b = (size_t)im.n_kblocks * tile_b;
+      ebase = im.data + (size_t)run.expert * im.n_mtiles * mt_b;
+      lut = (routed ? kTab0 : (UP && lane >= 16 && im.dual_book ? kTab1 : kTab0 + 128)) + lane * 4;
+      // (the previous task's reads of xs ended before its barrier)
+      if (UP) {
+        const int tok = p.tokidx[run.first];
+        if (tok != cur_tok) {
+          for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads) {
+            const uint4 u = __ldg((const uint4*)(p.x + (size_t)tok * p.K) + c);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int e = 0; e < 4; e++)
-              xh[q * 4 + e] = pack_half2_sat(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xFFFF0000u));
+            uint4 o;
+            o.x = pack_half2_sat(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u));
+            o.y = pack_half2_sat(__uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
+            o.z = pack_half2_sat(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u));
+            o.w = pack_half2_sat(__uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
+            ((uint4*)xs)[c] = o;
           }
-        } else {
-          const float4* src = (const float4*)(p.hid + (size_t)row * p.mid + grp * 32);
-#pragma unroll
-          for (int q = 0; q < 8; q++) {
-            const float4 u = src[q];
-            xh[q * 2] = pack_half2_sat(u.x, u.y);
-            xh[q * 2 + 1] = pack_half2_sat(u.z, u.w);
-          }
+          cur_tok = tok;
+          __syncthreads();
         }
+      } else {
+        for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads)
+          ((uint4*)xs)[c] = ((const uint4*)(p.hid + (size_t)run.first * p.mid))[c];  // written by the previous kernel: plain loads
+        __syncthreads();
       }
       cur_unit = unit;
+      have = false;
     }
-    const bool routed = ri < n_routed;
-    const Image& im = routed ? p.img : p.img_sh;
-    const int row_out = run.first + (unit - s_first[ri]);
-    const int o0 = j * kGemvRows;  // first output of the task
-    const int mt = UP ? o0 / 64 : o0 / kTileM, rr = UP ? o0 % 64 : o0 % kTileM;
-    float acc[kR];
+    const bool next = task + 1 < c1 && j + 1 < tpu;  // the CTA's next task belongs to the same run
+    const uint8_t *pc, *ps;
+    if (!have) {
+      locate(j, pc, ps);
 #pragma unroll
-    for (int i = 0; i < kR; i++) acc[i] = 0.f;
-    if (live) {
-      const uint8_t* tile = im.tile(run.expert, mt, grp >> 1);
-      const uint8_t* tp = tile + (grp & 1) * 2048;
-      const uint8_t* sp = tile + kCodeBytes + (grp & 1) * 2;
-      uint4 cw[kR];
-      uint32_t sw[kR];
-#pragma unroll
-      for (int i = 0; i < kR; i++) {
-        const int r = UP ? (i < kGemvRows ? rr + i : 64 + rr + (i - kGemvRows)) : rr + i;
-        cw[i] = __ldg((const uint4*)(tp + r * 16));
-        sw[i] = __ldg((const unsigned short*)(sp + r * 4));
-      }
-#pragma unroll
-      for (int i = 0; i < kR; i++) {
-        const int r = UP ? (i < kGemvRows ? rr + i : 64 + rr + (i - kGemvRows)) : rr + i;
-        const uint32_t lut = (routed ? a_lut_r : (r >= 64 ? a_lut_s1 : a_lut_s0));
-        acc[i] = half_bits_to_f32((uint16_t)sw[i]) * chunk_dot(cw[i], lut, xh);
+      for (int i = 0; i < kKpw; i++) {
+        if (i < kpw && kb0 + i < KB) {
+          cw[2 * i] = __ldg((const uint4*)(pc + i * tile_b));
+          cw[2 * i + 1] = __ldg((const uint4*)(pc + i * tile_b + 2048));
+          sw[i] = __ldg((const uint32_t*)(ps + i * tile_b));
+        }
       }
     }
-    // ---- reduce every row over the 32 lanes, then over the team's warps ----
+    locate(next ? j + 1 : j, pc, ps);
+    float acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < kR; i++) {
-#pragma unroll
-      for (int o = 16; o; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-    }
-    float mine = acc[0];
-#pragma unroll
-    for (int i = 1; i < kR; i++)
-      if (lane == i) mine = acc[i];  // lane i < kR now holds row i
-    const int buf = task & 1;
-    if (ts > 1) {
-      if (lane < kR) s_part[buf][warp][lane] = mine;
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + team_local), "r"(ts * 32) : "memory");
-      if (wq == 0 && lane < kR) {
-        mine = 0.f;
-        for (int w2 = 0; w2 < ts; w2++) mine += s_part[buf][team_local * ts + w2][lane];
+    for (int i = 0; i < kKpw; i++) {
+      if (i < kpw && kb0 + i < KB) {
+        const uint32_t xa = xs_addr + (uint32_t)(kb0 + i) * (kTileK * 2);
+        const float d0 = chunk_dot(cw[2 * i], lut, xa), d1 = chunk_dot(cw[2 * i + 1], lut, xa + 64);
+        acc += half_bits_to_f32((uint16_t)(sw[i] & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[i] >> 16)) * d1;
+        if (next) {  // refill the registers just consumed with the same K block of the next task
+          cw[2 * i] = __ldg((const uint4*)(pc + i * tile_b));
+          cw[2 * i + 1] = __ldg((const uint4*)(pc + i * tile_b + 2048));
+          sw[i] = __ldg((const uint32_t*)(ps + i * tile_b));
+        }
       }
     }
-    if (wq == 0) {
-      if (UP) {
-        const float up = __shfl_down_sync(0xffffffffu, mine, kGemvRows);  // lane i gets row kGemvRows+i
-        if (lane < kGemvRows) p.out[(size_t)row_out * p.mid + o0 + lane] = silu_f32(mine) * up;
-      } else {
-        if (lane < kGemvRows) p.out[(size_t)row_out * out_rows + o0 + lane] = mine;
+    have = next;
+    // ---- the K slices meet in shared memory; one warp per row group adds them in slice order ----
+    red[buf][warp][lane] = acc;
+    __syncthreads();
+    if (UP) {
+      if (warp == 0) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kGemvWarps; w++) tot += red[buf][w][lane];
+        const float up = __shfl_down_sync(0xffffffffu, tot, 16);
+        if (lane < 16)
+          p.hid[(size_t)run.first * p.mid + j * 16 + lane] =
+              __float2half_rn(fminf(fmaxf(silu_f32(tot) * up, -65504.f), 65504.f));
+      }
+    } else {
+      if (warp < 2) {
+        float tot = 0.f;
+#pragma unroll
+        for (int s = 0; s < kGemvWarps / 2; s++) tot += red[buf][2 * s + warp][lane];
+        p.out[(size_t)run.first * out_rows + j * 64 + warp * 32 + lane] = tot;
       }
     }
+    buf ^= 1;
   }
 }
 
 template <bool UP>
 cudaError_t launch_gemv(const GemvParams& p, cudaStream_t st) {
-  constexpr int kMaxSmem = 3 * 256 * 32 * 4;
-  const int smem = (p.img_sh.data ? 3 : 1) * 256 * 32 * 4;
+  // the dynamic allocation must reach the end of the last table, wherever it starts
+  constexpr int kMaxSmem = UP ? kTab1 + 65536 : kTab0 + 65536;
+  const bool two = UP && p.img_sh.data && p.img_sh.dual_book;
+  const int smem = two ? kTab1 + 65536 : kTab0 + 65536;
   static bool attr_done = false;
   static int sms = 0;
   if (!attr_done) {
@@ -256,26 +313,28 @@ cudaError_t launch_gemv(const GemvParams& p, cudaStream_t st) {
 }  // namespace
 
 int gemv_max_runs() { return kGemvMaxRuns; }
-int gemv_max_k() { return kGemvMaxChunks * 32 * 32; }
+int gemv_max_k() { return kGemvMaxK; }                       // 16 K slices x 4 K blocks
+int gemv_max_mid() { return (kGemvWarps / 2) * kKpw * kTileK; }  // 8 K slices x 4 K blocks = 2048
 
 cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_bf16, int d, int mid,
                            const int32_t* tokidx, const Run* runs, const int32_t* n_runs,
-                           float* hid_f32, cudaStream_t st) {
+                           __half* hid16, cudaStream_t st) {
   GemvParams p{};
   p.img = img;
   if (img_sh) p.img_sh = *img_sh;
   p.runs = runs; p.n_runs = n_runs; p.K = d; p.mid = mid;
-  p.x = (const uint16_t*)x_bf16; p.tokidx = tokidx; p.out = hid_f32;
+  p.x = (const uint16_t*)x_bf16; p.tokidx = tokidx; p.hid = hid16;
   return launch_gemv<true>(p, st);
 }
 
-cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const float* hid_f32, int d, int mid,
+cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half* hid16, int d, int mid,
                              const Run* runs, const int32_t* n_runs, float* pairs_f32, cudaStream_t st) {
   GemvParams p{};
   p.img = img;
   if (img_sh) p.img_sh = *img_sh;
   p.runs = runs; p.n_runs = n_runs; p.K = mid; p.mid = mid;
-  p.hid = hid_f32; p.out = pairs_f32;
+  p.hid = const_cast<__half*>(hid16);
+  p.out = pairs_f32;
   return launch_gemv<false>(p, st);
 }
 

@@ -68,12 +68,15 @@ cudaError_t launch_down_simt(const Image& img, const float* hid_f32, int d, int 
 
 // ---- expert_gemv.cu (q4cp decode / verify path) ----
 int gemv_max_runs();
-int gemv_max_k();
+int gemv_max_k();     // largest d
+int gemv_max_mid();   // largest mid
 // img_sh: the shared expert's image (nullptr: none); its run is runs[kMaxExperts].
+// hid16: fp16 [rows][mid] hidden activations silu(gate) * up, written by the gate/up kernel and
+// read by the down kernel.
 cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_bf16, int d, int mid,
                            const int32_t* tokidx, const Run* runs, const int32_t* n_runs,
-                           float* hid_f32, cudaStream_t st);
-cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const float* hid_f32, int d, int mid,
+                           __half* hid16, cudaStream_t st);
+cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half* hid16, int d, int mid,
                              const Run* runs, const int32_t* n_runs, float* pairs_f32, cudaStream_t st);
 
 // ---- combine.cu ----
