@@ -68,6 +68,42 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
   }
 }
 
+// Few tokens (decode): latency matters, not bandwidth. A thread owns 4 columns and issues the
+// loads of all rows before it adds them (same order of additions as k_combine).
+__global__ void __launch_bounds__(128)
+k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
+                const int32_t* __restrict__ pairids, int k, int d, int shared_row0,
+                __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= d) return;
+  const int n = k + (shared_row0 >= 0 ? 1 : 0);
+  float4 v[kMaxTopK + 1];
+  float w[kMaxTopK + 1];
+#pragma unroll
+  for (int s = 0; s < kMaxTopK + 1; s++) {
+    if (s < n) {
+      const int row = s < k ? pairids[(size_t)t * k + s] : shared_row0 + t;
+      w[s] = pw[row];
+      v[s] = *(const float4*)(pairs + (size_t)row * d + c);
+    }
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int s = 0; s < kMaxTopK + 1; s++) {
+    if (s < n) {
+      acc.x = fmaf(w[s], v[s].x, acc.x);
+      acc.y = fmaf(w[s], v[s].y, acc.y);
+      acc.z = fmaf(w[s], v[s].z, acc.z);
+      acc.w = fmaf(w[s], v[s].w, acc.w);
+    }
+  }
+  uint2 o;
+  *(__nv_bfloat162*)&o.x = __floats2bfloat162_rn(acc.x, acc.y);
+  *(__nv_bfloat162*)&o.y = __floats2bfloat162_rn(acc.z, acc.w);
+  *(uint2*)(out + (size_t)t * d + c) = o;
+}
+
 // x_sorted[row][:] = fp16(x[tokidx[row]][:]); bf16 -> fp16 is exact for 2^-14 <= |v| < 65520,
 // larger magnitudes saturate to the largest finite half.
 __global__ void __launch_bounds__(256)
@@ -96,7 +132,10 @@ k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx,
 
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
-  k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+  if (T <= 64 && d % 4 == 0)
+    k_combine_small<<<dim3(T, (d / 4 + 127) / 128), 128, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+  else
+    k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
   return cudaGetLastError();
 }
 

@@ -114,20 +114,225 @@ k_router_topk(const float* __restrict__ logits, int T, int E, int k, int32_t* __
 // logits are given), stable bucketing by rank counting, expert offsets, run and tile lists,
 // and the shared expert's sigmoid gate. Same results as the general kernels below.
 constexpr int kSmallPairs = 256;
-__global__ void __launch_bounds__(kMaxExperts)
+__global__ void __launch_bounds__(kMaxExperts, 1)
 k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_in,
               const float* __restrict__ w_in, int stride_in, int T, int E, int k, RouteBuffers rb,
               const uint16_t* __restrict__ x, const uint16_t* __restrict__ gw, int d) {
-  __shared__ float s_p[16][kMaxExperts];  // 32 KB: router scratch, one row per warp
+  __shared__ float s_p[16][kMaxExperts];  // 32 KB: router scratch, one row per token
   __shared__ int s_key[kSmallPairs];
   __shared__ float s_w[kSmallPairs];
   __shared__ int s_wcnt[17];
+  __shared__ float s_bv[2][16];
+  __shared__ int s_bi[2][16];
+  __shared__ double s_se[16], s_part[16];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int P = T * k;
+  // W = 16 / T' warps share a token (T' = T rounded up to a power of two)
+  const int Tp = T <= 1 ? 1 : T <= 2 ? 2 : T <= 4 ? 4 : T <= 8 ? 8 : 16;
+  const int W = 16 / Tp, ts = warp / W, wq = warp % W;  // token slot, warp in the token's group
+  const bool tok = ts < T;
+  if (gw) {
+    // scalar sigmoid gate of the shared expert: a d-long dot product in double, 16-byte
+    // loads spread over the token's warps, partial sums added in a fixed order
+    double a = 0;
+    if (tok) {
+      const uint4* xv = (const uint4*)(x + (size_t)ts * d);
+      const uint4* gv = (const uint4*)gw;
+      for (int c = wq * 32 + lane; c < d / 8; c += W * 32) {
+        const uint4 xa = xv[c], ga = __ldg(gv + c);
+        const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, gq[4] = {ga.x, ga.y, ga.z, ga.w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          a += (double)__uint_as_float(gq[q] << 16) * (double)__uint_as_float(xw[q] << 16);
+          a += (double)__uint_as_float(gq[q] & 0xFFFF0000u) * (double)__uint_as_float(xw[q] & 0xFFFF0000u);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1)
+      a += __hiloint2double(__shfl_xor_sync(0xffffffffu, __double2hiint(a), o),
+                            __shfl_xor_sync(0xffffffffu, __double2loint(a), o));
+    if (lane == 0) s_part[warp] = a;
+    __syncthreads();
+    if (tok && wq == 0 && lane == 0) {
+      double tot = 0;
+      for (int w2 = 0; w2 < W; w2++) tot += s_part[ts * W + w2];
+      const float gate = sigmoid_f32((float)tot);
+      rb.sgate[ts] = gate;
+      rb.tokidx[P + ts] = ts;
+      rb.pw[P + ts] = gate;
+    }
+    __syncthreads();  // s_part is reused by the router
+  }
   if (logits) {
-    for (int t = warp; t < T; t += 16)
-      router_one_token(logits + (size_t)t * E, E, k, lane, s_p[warp], rb.topids + (size_t)t * kIdStride,
-                       rb.topw + (size_t)t * kIdStride, kIdStride);
+    // Router: the token's W warps share its exponentials, divisions and the selection, so
+    // that a single token is spread over the whole block instead of one warp. Same arithmetic
+    // and tie rule as router_one_token.
+    const int NV = 16 / W;  // values per lane
+    const float* lg = logits + (size_t)(tok ? ts : 0) * E;
+    float v[16];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int e = (j * W + wq) * 32 + lane;
+      v[j] = (j < NV && tok && e < E) ? lg[e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_bv[0][warp] = mx;
+    __syncthreads();
+    for (int w2 = 0; w2 < W; w2++) mx = fmaxf(mx, s_bv[0][ts * W + w2]);
+    const double dmx = (double)mx;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int e = (j * W + wq) * 32 + lane;
+      if (j < NV && tok && e < E) {
+        v[j] = (float)exp((double)v[j] - dmx);
+        s_p[ts][e] = v[j];
+      }
+    }
+    __syncthreads();
+    // Sum of the exponentials, as the reference takes it: in double, in index order. All terms
+    // are floats in (0, 1]: when the smallest non-zero one is at least 2^(B - 30), B = bits of
+    // the total's integer part, every partial sum of ANY order is a multiple of one grid that
+    // a double holds exactly, so a tree sum gives the very same bits and the 512 dependent
+    // additions are only needed otherwise.
+    {
+      double part = 0;
+      float mn = 2.f;
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        if (j < NV && tok && (j * W + wq) * 32 + lane < E) {
+          part += (double)v[j];
+          if (v[j] > 0.f) mn = fminf(mn, v[j]);
+        }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        part += __hiloint2double(__shfl_xor_sync(0xffffffffu, __double2hiint(part), o),
+                                 __shfl_xor_sync(0xffffffffu, __double2loint(part), o));
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      }
+      if (lane == 0) {
+        s_part[warp] = part;
+        s_bv[1][warp] = mn;
+      }
+    }
+    __syncthreads();
+    if (tok && wq == 0 && lane == 0) {
+      double se = 0;
+      float mn = 2.f;
+      for (int w2 = 0; w2 < W; w2++) {
+        se += s_part[ts * W + w2];
+        mn = fminf(mn, s_bv[1][ts * W + w2]);
+      }
+      // last mantissa bit of the smallest term against the bits the total needs
+      const int e_min = (int)((__float_as_uint(mn) >> 23) & 0xFF) - 127;
+      const int bits_total = (int)((__double2hiint(se) >> 20) & 0x7FF) - 1023 + 2;  // generous by one bit
+      const bool exact = mn >= 1.17549435e-38f && bits_total - (e_min - 23) <= 53;
+      if (!exact) {
+        se = 0;
+        for (int i = 0; i < E; i++) se += (double)s_p[ts][i];  // index order, as the reference sums
+      }
+      s_se[ts] = se;
+    }
+    __syncthreads();
+    const double se = tok ? s_se[ts] : 1.0;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int e = (j * W + wq) * 32 + lane;
+      v[j] = (j < NV && tok && e < E) ? (float)((double)v[j] / se) : -1.f;
+    }
+    int my_id = 0;
+    float my_p = 0.f;
+    double kept = 0;
+    if (W >= 4) {
+      // Few tokens: every thread ranks its (at most four) probabilities against all E of the
+      // token -- rank = how many come before it in (probability descending, id ascending) --
+      // and the k first ranks are the selection, already in order.
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int e = (j * W + wq) * 32 + lane;
+        if (j < NV && tok && e < E) s_p[ts][e] = v[j];  // the exponentials were last read before the barrier above
+      }
+      if (wq == 0 && lane < 4 && E + lane < ((E + 3) & ~3)) s_p[ts][E + lane] = -1.f;  // pad to the 16-byte reads below
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int e = (j * W + wq) * 32 + lane;
+        if (j < NV && tok && e < E) {
+          const float mine = v[j];
+          int rank = 0;
+          for (int i = 0; i < E; i += 4) {
+            const float4 q = *(const float4*)&s_p[ts][i];
+            rank += (q.x > mine) || (q.x == mine && i < e);
+            rank += (q.y > mine) || (q.y == mine && i + 1 < e);
+            rank += (q.z > mine) || (q.z == mine && i + 2 < e);
+            rank += (q.w > mine) || (q.w == mine && i + 3 < e);
+          }
+          if (rank < k) {
+            s_key[ts * 16 + rank] = e;
+            s_w[ts * 16 + rank] = mine;
+          }
+        }
+      }
+      __syncthreads();
+      for (int r = 0; r < k; r++) kept += (double)s_w[(tok ? ts : 0) * 16 + r];  // in selection order
+      if (lane < k) {
+        my_id = s_key[(tok ? ts : 0) * 16 + lane];
+        my_p = s_w[(tok ? ts : 0) * 16 + lane];
+      }
+      __syncthreads();  // s_key / s_w are reused below
+    } else {
+      // W is 1 or 2: k rounds of arg-max over the group's values
+      for (int r = 0; r < k; r++) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if (v[j] > bv) {  // ascending expert id within a lane: the first maximum is the lowest id
+            bv = v[j];
+            bi = (j * W + wq) * 32 + lane;
+          }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+          }
+        }
+        if (W == 2) {
+          if (lane == 0) {
+            s_bv[r & 1][warp] = bv;
+            s_bi[r & 1][warp] = bi;
+          }
+          __syncthreads();
+          const float ov = s_bv[r & 1][warp ^ 1];
+          const int oi = s_bi[r & 1][warp ^ 1];
+          if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+          if ((j * W + wq) * 32 + lane == bi) v[j] = -1.f;
+        if (lane == r) {
+          my_id = bi;
+          my_p = bv;
+        }
+        kept += (double)bv;
+      }
+    }
+    if (tok && wq == 0) {
+      for (int i = lane; i < kIdStride; i += 32) {
+        const bool valid = i < k && i < 32;
+        rb.topids[(size_t)ts * kIdStride + i] = valid ? my_id : 0;
+        rb.topw[(size_t)ts * kIdStride + i] = valid ? (float)((double)my_p / kept) : 0.f;
+      }
+    }
     __syncthreads();
     ids_in = rb.topids;
     w_in = rb.topw;
@@ -180,26 +385,6 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
     rb.n_tiles[0] = n_active;
     rb.n_tiles[1] = 1;
     rb.tiles_sh[0] = Tile{0, P, T};
-  }
-  // scalar sigmoid gate of the shared expert and its rows behind the routed ones
-  if (gw) {
-    for (int t = warp; t < T; t += 16) {
-      double a = 0;
-      for (int c = lane; c < d; c += 32)
-        a += (double)bf16_bits_to_f32(gw[c]) * (double)bf16_bits_to_f32(x[(size_t)t * d + c]);
-#pragma unroll
-      for (int o = 16; o; o >>= 1) {
-        int lo = __shfl_xor_sync(0xffffffffu, __double2loint(a), o);
-        int hi = __shfl_xor_sync(0xffffffffu, __double2hiint(a), o);
-        a += __hiloint2double(hi, lo);
-      }
-      if (lane == 0) {
-        const float gate = sigmoid_f32((float)a);
-        rb.sgate[t] = gate;
-        rb.tokidx[P + t] = t;
-        rb.pw[P + t] = gate;
-      }
-    }
   }
 }
 
