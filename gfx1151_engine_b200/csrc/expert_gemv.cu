@@ -98,8 +98,7 @@ __device__ __forceinline__ uint32_t pack_half2_sat(float a, float b) {
 
 struct GemvShared {
   int first[kGemvMaxRuns + 2];  // unit prefix: rows before run i ("unit" = one row of the permuted activations)
-  int units;
-  int bad;
+  float book[3][16];
 };
 
 template <bool UP>
@@ -116,48 +115,36 @@ k_gemv(const GemvParams p) {
   const bool two = UP && has_sh && p.img_sh.dual_book;
   const int n_routed = p.n_runs[0];
   const int n_runs_all = min(n_routed + (has_sh ? 1 : 0), kGemvMaxRuns);
-
-  // ---- pair tables and unit prefix. Table lines: entry b = (f16(book[b & 15]), f16(book[b >> 4])),
-  // 256 bytes per code byte: [32 lanes x 4 B of book A][32 lanes x 4 B of book B]. Block 0 holds
-  // the routed book (A) and the shared expert's first book (B); block 1 the shared expert's
-  // second book (rows 64..127 of its gate/up tiles, when that image has two books). The blocks
-  // live at fixed absolute addresses: a launch whose dynamic allocation does not cover them is
-  // refused (uniform for the CTA; the host sizes the allocation accordingly). ----
   {
+    // The table blocks live at fixed absolute shared addresses: a launch whose dynamic
+    // allocation does not cover them is refused (uniform for the grid; the host sizes it).
     uint32_t dyn_size;
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
-    const uint32_t need_end = two ? kTab1 + 65536 : kTab0 + 65536;
-    const bool fits = dyn0 <= kTab0 && dyn0 + dyn_size >= need_end;
-    if (threadIdx.x == 0) sh.bad = fits ? 0 : 1;
-    const int nb = has_sh ? (two ? 3 : 2) : 1;
-    if (fits) {
-      for (int i = threadIdx.x; i < nb * 256 * 32; i += kGemvThreads) {
-        const int b = i >> 13, e = (i >> 5) & 255, l = i & 31;
-        const float* bk = b == 0 ? p.img.book : p.img_sh.book + (b - 1) * 16;
-        *(__half2*)(smem + (b == 2 ? kTab1 : kTab0) + e * 256 + (b == 1 ? 128 : 0) + l * 4) =
-            __floats2half2_rn(bk[e & 15], bk[e >> 4]);
-      }
-    }
-    for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads)
-      sh.first[i] = (i < n_routed ? p.runs[i] : p.runs[kMaxExperts]).count;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int acc = 0;
-      for (int i = 0; i < n_runs_all; i++) {
-        const int c = sh.first[i];
-        sh.first[i] = acc;
-        acc += c;
-      }
-      sh.first[n_runs_all] = acc;
-      sh.units = acc;
-    }
-    __syncthreads();
-    if (sh.bad) return;
+    if (dyn0 > kTab0 || dyn0 + dyn_size < (two ? kTab1 + 65536 : kTab0 + 65536)) return;
   }
+  // ---- unit prefix and code books ----
+  for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads)
+    sh.first[i] = (i < n_routed ? p.runs[i] : p.runs[kMaxExperts]).count;
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + 48) {
+    const int b = (threadIdx.x - 64) >> 4, e = threadIdx.x & 15;
+    if (b == 0) sh.book[0][e] = p.img.book[e];
+    else if (has_sh && (b == 1 || two)) sh.book[b][e] = p.img_sh.book[(b - 1) * 16 + e];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < n_runs_all; i++) {
+      const int c = sh.first[i];
+      sh.first[i] = acc;
+      acc += c;
+    }
+    sh.first[n_runs_all] = acc;
+  }
+  __syncthreads();
 
   // ---- geometry. gate/up: a task = 16 hidden outputs (lanes 0..15 the gate rows, lanes 16..31
   // the matching up rows), every warp a K slice. down: a task = 64 output rows, warps = 2 row
-  // groups x 8 K slices. ----
+  // groups x 8 K slices. A warp's share of a task is kpw <= 4 K blocks ("items"). ----
   const int KB = p.K / kTileK;
   constexpr int kSlices = UP ? kGemvWarps : kGemvWarps / 2;
   const int slice = UP ? warp : warp >> 1;
@@ -165,128 +152,142 @@ k_gemv(const GemvParams p) {
   const int kb0 = slice * kpw;
   const int out_rows = UP ? p.mid : p.img.n_mtiles * kTileM;
   const int tpu = UP ? out_rows / 16 : out_rows / 64;  // tasks per unit
-  const long long total = (long long)sh.units * tpu;
+  const long long total = (long long)sh.first[n_runs_all] * tpu;
   const long long base = total / gridDim.x, rem = total % gridDim.x;
   const long long c0 = blockIdx.x * base + min((long long)blockIdx.x, rem), c1 = c0 + base + ((long long)blockIdx.x < rem ? 1 : 0);
   constexpr size_t tile_b = tile_bytes(kQ4CP);  // both images are q4cp on this path
   const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
 
-  uint4 cw[2 * kKpw];
-  uint32_t sw[kKpw];
-  int cur_unit = -1, cur_tok = -1, buf = 0;
-  bool routed = true, have = false;
-  Run run = Run{0, 0, 0};
-  const uint8_t* ebase = nullptr;  // first tile of the run's expert
-  size_t mt_b = 0;
-  uint32_t lut = 0;
-  // this lane's row of task j: tile base (first K block of the warp's slice), tile row
-  // this lane's row of task j: pointers to its codes and to its scale pair in the first K
-  // block of the warp's slice
-  auto locate = [&](int j, const uint8_t*& pc, const uint8_t*& ps) {
-    int mt, r;
-    if (UP) {
-      mt = j >> 2;
-      r = (lane < 16 ? 0 : 48) + (j & 3) * 16 + lane;  // gate rows 0..63, up rows 64..127
-    } else {
-      mt = j >> 1;
-      r = (j & 1) * 64 + (warp & 1) * 32 + lane;
+  uint4 cw[2 * kKpw];  // four item slots: codes of both halves of a K block ...
+  uint32_t sw[kKpw];   // ... and the row's two fp16 scales
+  int cur_tok = -1, buf = 0;
+  bool tables = false;
+  for (long long seg = c0; seg < c1;) {
+    // ---- a segment: the CTA's tasks j0 .. j1-1 of one unit ----
+    const int unit = (int)(seg / tpu), j0 = (int)(seg % tpu);
+    const int j1 = (int)min((long long)tpu, (long long)j0 + (c1 - seg));
+    seg += j1 - j0;
+    int lo = 0, hi = n_runs_all - 1;
+    while (lo < hi) {
+      const int m = (lo + hi + 1) >> 1;
+      if (sh.first[m] <= unit) lo = m; else hi = m - 1;
     }
-    const uint8_t* tb = ebase + (size_t)mt * mt_b + (size_t)kb0 * tile_b;
-    pc = tb + r * 16;
-    ps = tb + kCodeBytes + r * 4;
-  };
-  for (long long task = c0; task < c1; task++) {
-    const int unit = (int)(task / tpu), j = (int)(task % tpu);
-    if (unit != cur_unit) {
-      // ---- new row of the permuted activations: its run, its tables, its activations ----
-      int lo = 0, hi = n_runs_all - 1;
-      while (lo < hi) {
-        const int m = (lo + hi + 1) >> 1;
-        if (sh.first[m] <= unit) lo = m; else hi = m - 1;
+    const bool routed = lo < n_routed;
+    Run run = routed ? p.runs[lo] : p.runs[kMaxExperts];
+    run.first += unit - sh.first[lo];
+    const Image& im = routed ? p.img : p.img_sh;
+    const size_t mt_b = (size_t)im.n_kblocks * tile_b;
+    const uint8_t* const ebase = im.data + (size_t)run.expert * im.n_mtiles * mt_b + (size_t)kb0 * tile_b;
+    const uint32_t lut = (routed ? kTab0 : (UP && lane >= 16 && im.dual_book ? kTab1 : kTab0 + 128)) + lane * 4;
+    // this lane's row of task j: offset of its codes in the first K block of the warp's slice
+    auto row_off = [&](int j) -> size_t {
+      if (UP) return (size_t)(j >> 2) * mt_b + ((lane < 16 ? 0 : 48) + (j & 3) * 16 + lane) * 16;  // gate rows 0..63, up rows 64..127
+      return (size_t)(j >> 1) * mt_b + ((j & 1) * 64 + (warp & 1) * 32 + lane) * 16;
+    };
+    auto fetch = [&](int s, int j, int i) {  // item (task j, K block i of the slice) into slot s
+      if (kb0 + i < KB) {
+        const uint8_t* pc = ebase + row_off(j) + (size_t)i * tile_b;
+        const size_t r16 = row_off(j) - (size_t)(UP ? j >> 2 : j >> 1) * mt_b;  // row * 16
+        cw[2 * s] = __ldg((const uint4*)pc);
+        cw[2 * s + 1] = __ldg((const uint4*)(pc + 2048));
+        sw[s] = __ldg((const uint32_t*)(pc - r16 + kCodeBytes + (r16 >> 2)));
       }
-      routed = lo < n_routed;
-      run = routed ? p.runs[lo] : p.runs[kMaxExperts];
-      run.first += unit - sh.first[lo];
-      const Image& im = routed ? p.img : p.img_sh;
-      mt_b = (size_t)im.n_kblocks * tile_b;
-      ebase = im.data + (size_t)run.expert * im.n_mtiles * mt_b;
-      lut = (routed ? kTab0 : (UP && lane >= 16 && im.dual_book ? kTab1 : kTab0 + 128)) + lane * 4;
-      // (the previous task's reads of xs ended before its barrier)
-      if (UP) {
-        const int tok = p.tokidx[run.first];
-        if (tok != cur_tok) {
-          for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads) {
-            const uint4 u = __ldg((const uint4*)(p.x + (size_t)tok * p.K) + c);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-            uint4 o;
-            o.x = pack_half2_sat(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u));
-            o.y = pack_half2_sat(__uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
-            o.z = pack_half2_sat(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u));
-            o.w = pack_half2_sat(__uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
-            ((uint4*)xs)[c] = o;
-          }
-          cur_tok = tok;
-          __syncthreads();
-        }
-      } else {
-        for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads)
-          ((uint4*)xs)[c] = ((const uint4*)(p.hid + (size_t)run.first * p.mid))[c];  // written by the previous kernel: plain loads
-        __syncthreads();
-      }
-      cur_unit = unit;
-      have = false;
-    }
-    const bool next = task + 1 < c1 && j + 1 < tpu;  // the CTA's next task belongs to the same run
-    const uint8_t *pc, *ps;
-    if (!have) {
-      locate(j, pc, ps);
+    };
+    const int nseg = (j1 - j0) * kpw;
+    // the first four items go out before anything else: they are in flight while the tables
+    // are built and the activations staged
+    int pj = j0, pi = 0;  // the fetch stream's position
 #pragma unroll
-      for (int i = 0; i < kKpw; i++) {
-        if (i < kpw && kb0 + i < KB) {
-          cw[2 * i] = __ldg((const uint4*)(pc + i * tile_b));
-          cw[2 * i + 1] = __ldg((const uint4*)(pc + i * tile_b + 2048));
-          sw[i] = __ldg((const uint32_t*)(ps + i * tile_b));
-        }
+    for (int s = 0; s < kKpw; s++) {
+      if (s < nseg) fetch(s, pj, pi);
+      if (++pi == kpw) { pi = 0; pj++; }
+    }
+    if (!tables) {
+      // pair tables: entry e = (f16(book[e & 15]), f16(book[e >> 4])), one 256-byte line per code
+      // byte: [32 lanes x 4 B of book A][32 lanes x 4 B of book B]. Block 0 holds the routed
+      // book (A) and the shared expert's first book (B); block 1 the shared expert's second
+      // book (rows 64..127 of its gate/up tiles, when that image has two books).
+      // Warp w writes the 16 lines whose high code is w; lane l writes copy l of each line.
+      const int nb = has_sh ? (two ? 3 : 2) : 1;
+      for (int b = 0; b < nb; b++) {
+        const uint32_t hi = (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][warp])) << 16;
+        uint8_t* dst = smem + (b == 2 ? kTab1 : kTab0) + (b == 1 ? 128 : 0) + (warp * 16) * 256 + lane * 4;
+#pragma unroll
+        for (int lo = 0; lo < 16; lo++)
+          *(uint32_t*)(dst + lo * 256) = hi | (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][lo]));
       }
     }
-    locate(next ? j + 1 : j, pc, ps);
+    // activations of the unit (the previous segment's reads of xs ended before its last barrier)
+    bool staged = false;
+    if (UP) {
+      const int tok = p.tokidx[run.first];
+      if (tok != cur_tok) {
+        for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads) {
+          const uint4 u = __ldg((const uint4*)(p.x + (size_t)tok * p.K) + c);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+          uint4 o;
+          o.x = pack_half2_sat(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xFFFF0000u));
+          o.y = pack_half2_sat(__uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xFFFF0000u));
+          o.z = pack_half2_sat(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xFFFF0000u));
+          o.w = pack_half2_sat(__uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xFFFF0000u));
+          ((uint4*)xs)[c] = o;
+        }
+        cur_tok = tok;
+        staged = true;
+      }
+    } else {
+      for (int c = threadIdx.x; c < p.K / 8; c += kGemvThreads)
+        ((uint4*)xs)[c] = ((const uint4*)(p.hid + (size_t)run.first * p.mid))[c];  // written by the previous kernel: plain loads
+      staged = true;
+    }
+    if (staged || !tables) __syncthreads();
+    tables = true;
+
+    int cj = j0, ci = 0;  // the compute stream's position
     float acc = 0.f;
+    for (int n0 = 0; n0 < nseg; n0 += kKpw) {
 #pragma unroll
-    for (int i = 0; i < kKpw; i++) {
-      if (i < kpw && kb0 + i < KB) {
-        const uint32_t xa = xs_addr + (uint32_t)(kb0 + i) * (kTileK * 2);
-        const float d0 = chunk_dot(cw[2 * i], lut, xa), d1 = chunk_dot(cw[2 * i + 1], lut, xa + 64);
-        acc += half_bits_to_f32((uint16_t)(sw[i] & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[i] >> 16)) * d1;
-        if (next) {  // refill the registers just consumed with the same K block of the next task
-          cw[2 * i] = __ldg((const uint4*)(pc + i * tile_b));
-          cw[2 * i + 1] = __ldg((const uint4*)(pc + i * tile_b + 2048));
-          sw[i] = __ldg((const uint32_t*)(ps + i * tile_b));
+      for (int s = 0; s < kKpw; s++) {
+        if (n0 + s < nseg) {
+          if (kb0 + ci < KB) {
+            const uint32_t xa = xs_addr + (uint32_t)(kb0 + ci) * (kTileK * 2);
+            const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
+            acc += half_bits_to_f32((uint16_t)(sw[s] & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s] >> 16)) * d1;
+          }
+          // the slot just consumed receives the item four further down the stream
+          if (n0 + s + kKpw < nseg) fetch(s, pj, pi);
+          if (++pi == kpw) { pi = 0; pj++; }
+          if (++ci == kpw) {
+            // ---- end of a task: the K slices meet in shared memory; one warp per row group
+            // adds them in slice order ----
+            red[buf][warp][lane] = acc;
+            __syncthreads();
+            if (UP) {
+              if (warp == 0) {
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; w++) tot += red[buf][w][lane];
+                const float up = __shfl_down_sync(0xffffffffu, tot, 16);
+                if (lane < 16)
+                  p.hid[(size_t)run.first * p.mid + cj * 16 + lane] =
+                      __float2half_rn(fminf(fmaxf(silu_f32(tot) * up, -65504.f), 65504.f));
+              }
+            } else {
+              if (warp < 2) {
+                float tot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGemvWarps / 2; w++) tot += red[buf][2 * w + warp][lane];
+                p.out[(size_t)run.first * out_rows + cj * 64 + warp * 32 + lane] = tot;
+              }
+            }
+            buf ^= 1;
+            acc = 0.f;
+            ci = 0;
+            cj++;
+          }
         }
       }
     }
-    have = next;
-    // ---- the K slices meet in shared memory; one warp per row group adds them in slice order ----
-    red[buf][warp][lane] = acc;
-    __syncthreads();
-    if (UP) {
-      if (warp == 0) {
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < kGemvWarps; w++) tot += red[buf][w][lane];
-        const float up = __shfl_down_sync(0xffffffffu, tot, 16);
-        if (lane < 16)
-          p.hid[(size_t)run.first * p.mid + j * 16 + lane] =
-              __float2half_rn(fminf(fmaxf(silu_f32(tot) * up, -65504.f), 65504.f));
-      }
-    } else {
-      if (warp < 2) {
-        float tot = 0.f;
-#pragma unroll
-        for (int s = 0; s < kGemvWarps / 2; s++) tot += red[buf][2 * s + warp][lane];
-        p.out[(size_t)run.first * out_rows + j * 64 + warp * 32 + lane] = tot;
-      }
-    }
-    buf ^= 1;
   }
 }
 

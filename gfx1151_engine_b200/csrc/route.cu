@@ -246,45 +246,64 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
     int my_id = 0;
     float my_p = 0.f;
     double kept = 0;
-    if (W >= 4) {
-      // Few tokens: every thread ranks its (at most four) probabilities against all E of the
-      // token -- rank = how many come before it in (probability descending, id ascending) --
-      // and the k first ranks are the selection, already in order.
+    if (W == 16) {
+      // One token, one probability per thread (expert = tid). The k-th largest of the 16 warp
+      // maxima is a lower bound of the k-th largest probability (k <= 16), so every selected
+      // expert is among the values >= that bound: usually a few dozen candidates, which are
+      // then ranked against each other in (probability descending, id ascending) order.
+      const float mine = v[0];
+      float wm = mine;
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int e = (j * W + wq) * 32 + lane;
-        if (j < NV && tok && e < E) s_p[ts][e] = v[j];  // the exponentials were last read before the barrier above
-      }
-      if (wq == 0 && lane < 4 && E + lane < ((E + 3) & ~3)) s_p[ts][E + lane] = -1.f;  // pad to the 16-byte reads below
+      for (int o = 16; o; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+      if (lane == 0) s_bv[0][warp] = wm;
+      if (tid == 0) s_wcnt[16] = 0;
       __syncthreads();
+      if (warp == 0) {
+        const float m = lane < 16 ? s_bv[0][lane] : -1.f;
+        int rank = 0;
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int e = (j * W + wq) * 32 + lane;
-        if (j < NV && tok && e < E) {
-          const float mine = v[j];
-          int rank = 0;
-          for (int i = 0; i < E; i += 4) {
-            const float4 q = *(const float4*)&s_p[ts][i];
-            rank += (q.x > mine) || (q.x == mine && i < e);
-            rank += (q.y > mine) || (q.y == mine && i + 1 < e);
-            rank += (q.z > mine) || (q.z == mine && i + 2 < e);
-            rank += (q.w > mine) || (q.w == mine && i + 3 < e);
-          }
-          if (rank < k) {
-            s_key[ts * 16 + rank] = e;
-            s_w[ts * 16 + rank] = mine;
-          }
+        for (int i = 0; i < 16; i++) {
+          const float o = __shfl_sync(0xffffffffu, m, i);
+          rank += (o > m) || (o == m && i < lane);
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, lane < 16 && rank == min(k, 16) - 1);
+        const float bound = __shfl_sync(0xffffffffu, m, __ffs(hit) - 1);
+        if (lane == 0) s_bv[1][0] = bound;
+      }
+      __syncthreads();
+      const bool cand = tid < E && mine >= s_bv[1][0];
+      const unsigned cm = __ballot_sync(0xffffffffu, cand);
+      int cbase = 0;
+      if (lane == 0 && cm) cbase = atomicAdd(&s_wcnt[16], __popc(cm));
+      cbase = __shfl_sync(0xffffffffu, cbase, 0);
+      if (cand) {
+        const int pos = cbase + __popc(cm & ((1u << lane) - 1u));
+        s_p[1][pos] = mine;           // rows 1 and 2 of the scratch are free with one token
+        ((int*)s_p[2])[pos] = tid;
+      }
+      __syncthreads();
+      const int C = s_wcnt[16];
+      if (cand) {
+        int rank = 0;
+        for (int i = 0; i < C; i++) {
+          const float o = s_p[1][i];
+          const int oi = ((const int*)s_p[2])[i];
+          rank += (o > mine) || (o == mine && oi < tid);
+        }
+        if (rank < k) {
+          s_key[rank] = tid;
+          s_w[rank] = mine;
         }
       }
       __syncthreads();
-      for (int r = 0; r < k; r++) kept += (double)s_w[(tok ? ts : 0) * 16 + r];  // in selection order
+      for (int r = 0; r < k; r++) kept += (double)s_w[r];  // in selection order
       if (lane < k) {
-        my_id = s_key[(tok ? ts : 0) * 16 + lane];
-        my_p = s_w[(tok ? ts : 0) * 16 + lane];
+        my_id = s_key[lane];
+        my_p = s_w[lane];
       }
       __syncthreads();  // s_key / s_w are reused below
     } else {
-      // W is 1 or 2: k rounds of arg-max over the group's values
+      // k rounds of arg-max over the group's values: lanes, then the group's warps
       for (int r = 0; r < k; r++) {
         float bv = -1.f;
         int bi = 0x7fffffff;
@@ -303,18 +322,26 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
             bi = oi;
           }
         }
-        if (W == 2) {
+        if (W > 1) {
           if (lane == 0) {
             s_bv[r & 1][warp] = bv;
             s_bi[r & 1][warp] = bi;
           }
           __syncthreads();
-          const float ov = s_bv[r & 1][warp ^ 1];
-          const int oi = s_bi[r & 1][warp ^ 1];
-          if (ov > bv || (ov == bv && oi < bi)) {
-            bv = ov;
-            bi = oi;
+          // lane l < W takes the candidate of the group's warp l; W <= 8 lanes are merged
+          bv = lane < W ? s_bv[r & 1][ts * W + lane] : -1.f;
+          bi = lane < W ? s_bi[r & 1][ts * W + lane] : 0x7fffffff;
+#pragma unroll
+          for (int o = 4; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+              bv = ov;
+              bi = oi;
+            }
           }
+          bv = __shfl_sync(0xffffffffu, bv, 0);
+          bi = __shfl_sync(0xffffffffu, bi, 0);
         }
 #pragma unroll
         for (int j = 0; j < 16; j++)
