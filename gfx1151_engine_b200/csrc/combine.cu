@@ -76,6 +76,8 @@ k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
                 __nv_bfloat16* __restrict__ out) {
   const int t = blockIdx.x;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  pdl_trigger();
+  pdl_wait();
   if (c >= d) return;
   const int n = k + (shared_row0 >= 0 ? 1 : 0);
   float4 v[kMaxTopK + 1];
@@ -133,7 +135,8 @@ k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx,
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
   if (T <= 64 && d % 4 == 0)
-    k_combine_small<<<dim3(T, (d / 4 + 127) / 128), 128, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+    return launch_pdl(k_combine_small, dim3(T, (d / 4 + 127) / 128), dim3(128), 0, st, pairs, pw, pairids, k, d, shared_row0,
+                      (__nv_bfloat16*)out_bf16);
   else
     k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
   return cudaGetLastError();

@@ -113,8 +113,7 @@ k_gemv(const GemvParams p) {
   uint8_t* const smem = gsm - dyn0;  // smem + A is the generic pointer of absolute shared address A
   const bool has_sh = p.img_sh.data != nullptr;
   const bool two = UP && has_sh && p.img_sh.dual_book;
-  const int n_routed = p.n_runs[0];
-  const int n_runs_all = min(n_routed + (has_sh ? 1 : 0), kGemvMaxRuns);
+  pdl_trigger();
   {
     // The table blocks live at fixed absolute shared addresses: a launch whose dynamic
     // allocation does not cover them is refused (uniform for the grid; the host sizes it).
@@ -122,14 +121,35 @@ k_gemv(const GemvParams p) {
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
     if (dyn0 > kTab0 || dyn0 + dyn_size < (two ? kTab1 + 65536 : kTab0 + 65536)) return;
   }
-  // ---- unit prefix and code books ----
-  for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads)
-    sh.first[i] = (i < n_routed ? p.runs[i] : p.runs[kMaxExperts]).count;
-  if (threadIdx.x >= 64 && threadIdx.x < 64 + 48) {
-    const int b = (threadIdx.x - 64) >> 4, e = threadIdx.x & 15;
+  // ---- code books and pair tables: weights only, nothing an earlier kernel of the stream
+  // writes, so this part may overlap that kernel's tail ----
+  if (threadIdx.x < 48) {
+    const int b = threadIdx.x >> 4, e = threadIdx.x & 15;
     if (b == 0) sh.book[0][e] = p.img.book[e];
     else if (has_sh && (b == 1 || two)) sh.book[b][e] = p.img_sh.book[(b - 1) * 16 + e];
   }
+  __syncthreads();
+  {
+    // entry e = (f16(book[e & 15]), f16(book[e >> 4])), one 256-byte line per code byte:
+    // [32 lanes x 4 B of book A][32 lanes x 4 B of book B]. Block 0 holds the routed book (A)
+    // and the shared expert's first book (B); block 1 the shared expert's second book (rows
+    // 64..127 of its gate/up tiles, when that image has two books).
+    // Warp w writes the 16 lines whose high code is w; lane l writes copy l of each line.
+    const int nb = has_sh ? (two ? 3 : 2) : 1;
+    for (int b = 0; b < nb; b++) {
+      const uint32_t hi16 = (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][warp])) << 16;
+      uint8_t* dst = smem + (b == 2 ? kTab1 : kTab0) + (b == 1 ? 128 : 0) + (warp * 16) * 256 + lane * 4;
+#pragma unroll
+      for (int c = 0; c < 16; c++)
+        *(uint32_t*)(dst + c * 256) = hi16 | (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][c]));
+    }
+  }
+  pdl_wait();
+  // ---- unit prefix ----
+  const int n_routed = p.n_runs[0];
+  const int n_runs_all = min(n_routed + (has_sh ? 1 : 0), kGemvMaxRuns);
+  for (int i = threadIdx.x; i < n_runs_all; i += kGemvThreads)
+    sh.first[i] = (i < n_routed ? p.runs[i] : p.runs[kMaxExperts]).count;
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -161,7 +181,6 @@ k_gemv(const GemvParams p) {
   uint4 cw[2 * kKpw];  // four item slots: codes of both halves of a K block ...
   uint32_t sw[kKpw];   // ... and the row's two fp16 scales
   int cur_tok = -1, buf = 0;
-  bool tables = false;
   for (long long seg = c0; seg < c1;) {
     // ---- a segment: the CTA's tasks j0 .. j1-1 of one unit ----
     const int unit = (int)(seg / tpu), j0 = (int)(seg % tpu);
@@ -202,21 +221,6 @@ k_gemv(const GemvParams p) {
       if (s < nseg) fetch(s, pj, pi);
       if (++pi == kpw) { pi = 0; pj++; }
     }
-    if (!tables) {
-      // pair tables: entry e = (f16(book[e & 15]), f16(book[e >> 4])), one 256-byte line per code
-      // byte: [32 lanes x 4 B of book A][32 lanes x 4 B of book B]. Block 0 holds the routed
-      // book (A) and the shared expert's first book (B); block 1 the shared expert's second
-      // book (rows 64..127 of its gate/up tiles, when that image has two books).
-      // Warp w writes the 16 lines whose high code is w; lane l writes copy l of each line.
-      const int nb = has_sh ? (two ? 3 : 2) : 1;
-      for (int b = 0; b < nb; b++) {
-        const uint32_t hi = (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][warp])) << 16;
-        uint8_t* dst = smem + (b == 2 ? kTab1 : kTab0) + (b == 1 ? 128 : 0) + (warp * 16) * 256 + lane * 4;
-#pragma unroll
-        for (int lo = 0; lo < 16; lo++)
-          *(uint32_t*)(dst + lo * 256) = hi | (uint32_t)__half_as_ushort(__float2half_rn(sh.book[b][lo]));
-      }
-    }
     // activations of the unit (the previous segment's reads of xs ended before its last barrier)
     bool staged = false;
     if (UP) {
@@ -240,8 +244,7 @@ k_gemv(const GemvParams p) {
         ((uint4*)xs)[c] = ((const uint4*)(p.hid + (size_t)run.first * p.mid))[c];  // written by the previous kernel: plain loads
       staged = true;
     }
-    if (staged || !tables) __syncthreads();
-    tables = true;
+    if (staged) __syncthreads();
 
     int cj = j0, ci = 0;  // the compute stream's position
     float acc = 0.f;
@@ -307,8 +310,7 @@ cudaError_t launch_gemv(const GemvParams& p, cudaStream_t st) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     attr_done = true;
   }
-  k_gemv<UP><<<sms, kGemvThreads, smem, st>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(k_gemv<UP>, dim3(sms), dim3(kGemvThreads), (size_t)smem, st, p);
 }
 
 }  // namespace

@@ -4,7 +4,38 @@
 #pragma once
 #include "common.cuh"
 
+#include <cstdlib>
+#include <utility>
+
 namespace b200moe {
+
+// Programmatic dependent launch for the decode chain (route -> gate/up -> down -> combine):
+// the next kernel of the stream may start its prologue (code-book tables, index setup) while
+// this one drains. A kernel launched this way must call pdl_wait() before it touches anything
+// an earlier kernel of the stream wrote (or still reads); pdl_trigger() lets its own successor
+// start early. B200MOE_NO_PDL=1 in the environment turns the attribute off (plain launches).
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  static const bool off = std::getenv("B200MOE_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+#endif
+
 
 // Source of one half (tile rows 0..63 or 64..127) of a repacked image, in the layout of
 // the reference's files.

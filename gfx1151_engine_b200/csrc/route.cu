@@ -127,6 +127,8 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
   __shared__ double s_se[16], s_part[16];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int P = T * k;
+  pdl_trigger();
+  pdl_wait();  // inputs may come from the previous kernel; the buffers written here may still be read by it
   // W = 16 / T' warps share a token (T' = T rounded up to a power of two)
   const int Tp = T <= 1 ? 1 : T <= 2 ? 2 : T <= 4 ? 4 : T <= 8 ? 8 : 16;
   const int W = 16 / Tp, ts = warp / W, wq = warp % W;  // token slot, warp in the token's group
@@ -663,9 +665,8 @@ cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int E
 cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, const int32_t* ids,
                                const float* w, int stride, int T, int k, int E, const void* x_bf16,
                                const uint16_t* gate_w_bf16, int d, cudaStream_t st) {
-  k_route_small<<<1, kMaxExperts, 0, st>>>(logits, ids, w, stride, T, E, k, rb, (const uint16_t*)x_bf16,
+  return launch_pdl(k_route_small, dim3(1), dim3(kMaxExperts), 0, st, logits, ids, w, stride, T, E, k, rb, (const uint16_t*)x_bf16,
                                            gate_w_bf16, d);
-  return cudaGetLastError();
 }
 
 int route_small_max_pairs() { return kSmallPairs; }
