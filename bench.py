@@ -195,6 +195,8 @@ def main():
     ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
     ap.add_argument("--chunks", type=int, default=1, help="N>1: token chunks whose exchanges overlap the GEMMs")
     ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
+    ap.add_argument("--transport", default="nccl", choices=["nccl", "p2p"],
+                    help="N>1: exchanges by NCCL all-to-all or by peer copies (copy engines) through CUDA IPC")
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
@@ -234,7 +236,7 @@ def main():
         load = torch.bincount(cal, minlength=E).cpu().numpy()
         placement = ep.greedy_placement(load, world)
         epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement,
-                                   chunks=args.chunks, sm_margin=args.sm_margin)
+                                   chunks=args.chunks, sm_margin=args.sm_margin, transport=args.transport)
         epm.load_q4cp(0, gu, dn)
         op = epm.op
     else:
@@ -362,7 +364,7 @@ def main():
         ep_info = {"experts_per_gpu": E // world, "placement": "greedy by calibration histogram",
                    "recv_rows_max_over_mean": float(mx.item() / (rows.item() / world)),
                    "exchange": "NCCL all_to_all_single (dispatch, combine), all_gather of expert offsets",
-                   "chunks": args.chunks,
+                   "chunks": args.chunks, "transport": args.transport,
                    "check_vs_single_gpu": check}
 
     if rank != 0:

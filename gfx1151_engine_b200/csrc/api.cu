@@ -43,6 +43,10 @@ struct b200moe_ctx {
   float* logits_stage = nullptr;
   int32_t* status_dev = nullptr;
   int32_t* status_host = nullptr;  // pinned
+  // forward_host: copy streams and per-chunk events of the pipelined host path
+  static constexpr int kHostChunks = 4;
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[kHostChunks] = {}, ev_done[kHostChunks] = {}, ev_out[kHostChunks] = {}, ev_start = nullptr;
   TcPlan* tc = nullptr;
   // expert parallelism
   int32_t *place_dev = nullptr, *source_of_placed_dev = nullptr;
@@ -276,6 +280,14 @@ int b200moe_destroy(b200moe_handle h) {
   if (h->ep_counts) cudaFree(h->ep_counts);
   if (h->tc_ep) tc_destroy(h->tc_ep);
   for (auto& e : h->prof_ev) cudaEventDestroy(e);
+  if (h->s_in) cudaStreamDestroy(h->s_in);
+  if (h->s_out) cudaStreamDestroy(h->s_out);
+  for (int i = 0; i < b200moe_ctx::kHostChunks; i++) {
+    if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+    if (h->ev_done[i]) cudaEventDestroy(h->ev_done[i]);
+    if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+  }
+  if (h->ev_start) cudaEventDestroy(h->ev_start);
   if (h->status_host) cudaFreeHost(h->status_host);
   if (h->tc) tc_destroy(h->tc);
   cudaGetLastError();
@@ -613,12 +625,66 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
     return fail(h, B200MOE_ERR_BAD_ARG, "forward_host: bad argument");
   if (T == 0) return B200MOE_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t xb = (size_t)T * h->cfg.d_model * 2;
-  CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_bf16_host, xb, cudaMemcpyHostToDevice, st));
-  CU_TRY(h, cudaMemcpyAsync(h->logits_stage, logits_host, (size_t)T * h->cfg.experts * 4,
-                            cudaMemcpyHostToDevice, st));
-  if (int s = b200moe_forward(h, layer, h->x_stage, T, h->logits_stage, h->out_stage, stream)) return s;
-  CU_TRY(h, cudaMemcpyAsync(out_bf16_host, h->out_stage, xb, cudaMemcpyDeviceToHost, st));
+  const int d = h->cfg.d_model, E = h->cfg.experts;
+  // Large chunks are cut into up to four token ranges: the copy of range c+1 to the device
+  // and the copy of range c-1 back run on their own streams while range c computes. A
+  // token's result does not depend on which other tokens share its call, so the output is
+  // the same as for one call. B200MOE_HOST_CHUNKS overrides the number of ranges.
+  static const int forced = getenv("B200MOE_HOST_CHUNKS") ? atoi(getenv("B200MOE_HOST_CHUNKS")) : 0;
+  int C = forced > 0 ? forced : (T >= 8192 ? 4 : T >= 2048 ? 2 : 1);
+  C = std::min(C, (int)b200moe_ctx::kHostChunks);
+  if (C > 1 && !h->s_in) {
+    CU_TRY(h, cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking));
+    CU_TRY(h, cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking));
+    CU_TRY(h, cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming));
+    for (int i = 0; i < b200moe_ctx::kHostChunks; i++) {
+      CU_TRY(h, cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+      CU_TRY(h, cudaEventCreateWithFlags(&h->ev_done[i], cudaEventDisableTiming));
+      CU_TRY(h, cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+    }
+  }
+  if (C == 1) {
+    const size_t xb = (size_t)T * d * 2;
+    CU_TRY(h, cudaMemcpyAsync(h->x_stage, x_bf16_host, xb, cudaMemcpyHostToDevice, st));
+    CU_TRY(h, cudaMemcpyAsync(h->logits_stage, logits_host, (size_t)T * E * 4, cudaMemcpyHostToDevice, st));
+    if (int s = b200moe_forward(h, layer, h->x_stage, T, h->logits_stage, h->out_stage, stream)) return s;
+    CU_TRY(h, cudaMemcpyAsync(out_bf16_host, h->out_stage, xb, cudaMemcpyDeviceToHost, st));
+  } else {
+    const int per = (T + C - 1) / C;
+    // the copy streams start after whatever the caller's stream has queued (the staging
+    // buffers may still be in use by an earlier call)
+    CU_TRY(h, cudaEventRecord(h->ev_start, st));
+    CU_TRY(h, cudaStreamWaitEvent(h->s_in, h->ev_start, 0));
+    CU_TRY(h, cudaStreamWaitEvent(h->s_out, h->ev_start, 0));
+    for (int c = 0; c < C; c++) {
+      const int a = c * per, n = std::min(per, T - a);
+      if (n <= 0) break;
+      CU_TRY(h, cudaMemcpyAsync((uint8_t*)h->x_stage + (size_t)a * d * 2, (const uint8_t*)x_bf16_host + (size_t)a * d * 2,
+                                (size_t)n * d * 2, cudaMemcpyHostToDevice, h->s_in));
+      CU_TRY(h, cudaMemcpyAsync(h->logits_stage + (size_t)a * E, logits_host + (size_t)a * E, (size_t)n * E * 4,
+                                cudaMemcpyHostToDevice, h->s_in));
+      CU_TRY(h, cudaEventRecord(h->ev_in[c], h->s_in));
+    }
+    for (int c = 0; c < C; c++) {
+      const int a = c * per, n = std::min(per, T - a);
+      if (n <= 0) break;
+      CU_TRY(h, cudaStreamWaitEvent(st, h->ev_in[c], 0));
+      if (int s = b200moe_forward(h, layer, (uint8_t*)h->x_stage + (size_t)a * d * 2, n, h->logits_stage + (size_t)a * E,
+                                  (uint8_t*)h->out_stage + (size_t)a * d * 2, stream))
+        return s;
+      CU_TRY(h, cudaEventRecord(h->ev_done[c], st));
+      CU_TRY(h, cudaStreamWaitEvent(h->s_out, h->ev_done[c], 0));
+      CU_TRY(h, cudaMemcpyAsync((uint8_t*)out_bf16_host + (size_t)a * d * 2, (uint8_t*)h->out_stage + (size_t)a * d * 2,
+                                (size_t)n * d * 2, cudaMemcpyDeviceToHost, h->s_out));
+      CU_TRY(h, cudaEventRecord(h->ev_out[c], h->s_out));
+    }
+    // the caller's stream ends after the last copy back (the copies of one stream are ordered)
+    for (int c = C - 1; c >= 0; c--)
+      if (c * per < T) {
+        CU_TRY(h, cudaStreamWaitEvent(st, h->ev_out[c], 0));
+        break;
+      }
+  }
   CU_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost, st));
   CU_TRY(h, cudaStreamSynchronize(st));
   if (h->status_host[0] != 0) {

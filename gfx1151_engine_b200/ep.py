@@ -64,10 +64,11 @@ class ExpertParallelMoe:
     compute stream, so the NVLink time hides behind the tensor-core time."""
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
-                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16):
+                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl"):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
+        self.transport = transport
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
         self.chunks = chunks
         self.tc = (max_tokens + chunks - 1) // chunks            # tokens per chunk
@@ -75,7 +76,8 @@ class ExpertParallelMoe:
         self.ops, self.buf = [], []
         for c in range(chunks):
             op = pkg.MoeOperator(experts, topk, d_model, d_mid, self.tc, device=device,
-                                 ep_rank=rank, ep_size=world, ep_sm_margin=sm_margin if chunks > 1 else 0)
+                                 ep_rank=rank, ep_size=world,
+                                 ep_sm_margin=sm_margin if (chunks > 1 and transport == "nccl") else 0)
             if c == 0:
                 if placement is not None:
                     op.ep_set_placement(np.ascontiguousarray(placement, dtype=np.int32))
@@ -96,6 +98,123 @@ class ExpertParallelMoe:
         self.op = self.ops[0]
         self.comm = torch.cuda.Stream(device=dev)
         self.last_recv_rows = 0
+        if transport == "p2p":
+            self._p2p_setup(dev)
+
+    # ---- copy-engine transport -------------------------------------------------------------
+    # The exchanges are peer copies (DMA over NVLink, no SM) straight into the destination
+    # rank's receive buffer, so that they overlap the grouped GEMMs, which occupy every SM.
+    # Buffers and events are shared between the processes through CUDA IPC; "all data of chunk
+    # c has arrived" is an interprocess event per rank, recorded after the rank's copies. A
+    # wait on such an event refers to its latest record at the time of the call, so a host
+    # barrier (gloo) separates "every rank has recorded" from "every rank waits".
+    def _p2p_setup(self, dev):
+        torch, dist = self.torch, self.torch.distributed
+        self.comm2 = torch.cuda.Stream(device=dev)
+        self.host_group = dist.new_group(backend="gloo")
+        mine = []
+        for b in self.buf:
+            b["sent"] = torch.cuda.Event(enable_timing=False, interprocess=True)
+            b["returned"] = torch.cuda.Event(enable_timing=False, interprocess=True)
+            b["sent"].record(torch.cuda.current_stream())
+            b["returned"].record(torch.cuda.current_stream())
+            mine.append({"x_recv": b["x_recv"].untyped_storage()._share_cuda_(),
+                         "pairs_back": b["pairs_back"].untyped_storage()._share_cuda_(),
+                         "sent": b["sent"].ipc_handle(), "returned": b["returned"].ipc_handle(),
+                         "device": dev.index})
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        self._keep = []
+        for c, b in enumerate(self.buf):
+            b["peer_x_recv"], b["peer_back"], b["peer_sent"], b["peer_returned"] = [], [], [], []
+            for r in range(self.world):
+                if r == self.rank:
+                    b["peer_x_recv"].append(b["x_recv"])
+                    b["peer_back"].append(b["pairs_back"])
+                    b["peer_sent"].append(None)
+                    b["peer_returned"].append(None)
+                    continue
+                info = everyone[r][c]
+                pdev = torch.device("cuda", info["device"])
+                for key, like in (("x_recv", b["x_recv"]), ("pairs_back", b["pairs_back"])):
+                    st = torch.UntypedStorage._new_shared_cuda(*info[key])
+                    self._keep.append(st)
+                    t = torch._utils._rebuild_tensor(
+                        torch.storage.TypedStorage(wrap_storage=st, dtype=like.dtype, _internal=True),
+                        0, like.shape, like.stride())
+                    b["peer_x_recv" if key == "x_recv" else "peer_back"].append(t)
+                b["peer_sent"].append(torch.cuda.Event.from_ipc_handle(pdev, info["sent"]))
+                b["peer_returned"].append(torch.cuda.Event.from_ipc_handle(pdev, info["returned"]))
+        dist.barrier(group=self.host_group)
+
+    def _forward_p2p(self, layer, x, logits, out):
+        torch, dist = self.torch, self.torch.distributed
+        T = x.shape[0]
+        main = torch.cuda.current_stream()
+        C = min(self.chunks, (T + self.tc - 1) // self.tc)
+        span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
+        per = self.E // self.world
+        for c, (a, b) in enumerate(span):
+            B = self.buf[c]
+            self.ops[c].ep_route(layer, x[a:b], logits[a:b], eoff_out=B["eoff"], stream=main)
+            dist.all_gather_into_tensor(B["eoff_all"], B["eoff"], group=self.group)
+        routed = torch.cuda.Event()
+        routed.record(main)
+        bounds, rows = [], 0
+        for c in range(C):
+            eo = self.buf[c]["eoff_all"].cpu().numpy().reshape(self.world, -1)
+            bd = eo[:, ::per].astype(np.int64)           # [source rank][dest rank] row offsets in the source's send buffer
+            cnt = bd[:, 1:] - bd[:, :-1]                 # rows source s sends to dest p
+            if cnt[:, self.rank].sum() > self.buf[c]["cap"]:
+                raise RuntimeError("expert-parallel receive buffer too small: %d rows > capacity %d"
+                                   % (cnt[:, self.rank].sum(), self.buf[c]["cap"]))
+            bounds.append((bd, cnt))
+            rows += int(cnt[:, self.rank].sum())
+        self.last_recv_rows = rows
+        order = [(self.rank + i) % self.world for i in range(self.world)]
+        # 1. dispatch: my rows for rank p go behind the rows of the ranks before me in p's buffer
+        self.comm.wait_event(routed)
+        with torch.cuda.stream(self.comm):
+            for c in range(C):
+                bd, cnt = bounds[c]
+                B = self.buf[c]
+                for p in order:
+                    n = int(cnt[self.rank, p])
+                    if n:
+                        dst0 = int(cnt[:self.rank, p].sum())
+                        src0 = int(bd[self.rank, p])
+                        B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
+                B["sent"].record(self.comm)
+        dist.barrier(group=self.host_group)
+        # 2. experts per chunk as its rows arrive; results go straight back to their owners
+        for c in range(C):
+            bd, cnt = bounds[c]
+            B = self.buf[c]
+            for p in range(self.world):
+                if p != self.rank:
+                    main.wait_event(B["peer_sent"][p])
+            main.wait_event(B["sent"])
+            self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
+            done = torch.cuda.Event()
+            done.record(main)
+            self.comm2.wait_event(done)
+            with torch.cuda.stream(self.comm2):
+                for s in order:
+                    n = int(cnt[s, self.rank])
+                    if n:
+                        src0 = int(cnt[:s, self.rank].sum())
+                        dst0 = int(bd[s, self.rank])
+                        B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
+                B["returned"].record(self.comm2)
+        dist.barrier(group=self.host_group)
+        # 3. combine
+        for c, (a, b) in enumerate(span):
+            B = self.buf[c]
+            for p in range(self.world):
+                if p != self.rank:
+                    main.wait_event(B["peer_returned"][p])
+            main.wait_event(B["returned"])
+            self.ops[c].ep_combine(out[a:b], b - a, stream=main)
 
     def load_q4cp(self, layer, gate_up, down):
         """Every rank passes the full tensors; the library keeps this rank's experts."""
@@ -108,6 +227,8 @@ class ExpertParallelMoe:
         return sum(op.launches for op in self.ops)
 
     def forward(self, layer, x, logits, out):
+        if self.transport == "p2p":
+            return self._forward_p2p(layer, x, logits, out)
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
         main = torch.cuda.current_stream()

@@ -285,6 +285,24 @@ def test_forward_routed_and_host_paths(cuda):
     assert np.array_equal(bits(synth.bf16_bits_to_f32(out_h)), bits(y))
 
 
+@pytest.mark.parametrize("T", [2500, 8200])
+def test_host_path_pipelined_ranges(cuda, T):
+    """Large host calls are cut into token ranges whose copies overlap the compute of their
+    neighbours; the bytes are those of the single device call."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=16, topk=4, d=256, mid=128)
+    layer = synth.make_layer(spec, seed=91)
+    logits = synth.make_logits(synth.rng_for(91, 1), T, spec.experts)
+    xb = synth.make_x(synth.rng_for(91, 9), T, spec.d)
+    op = make_op(torch, spec, T, layer=layer)
+    y = run_layer(torch, op, spec, xb, logits)
+    out_h = np.zeros((T, spec.d), np.uint16)
+    for _ in range(2):  # the second call reuses the staging buffers and the copy streams
+        out_h[:] = 0
+        op.moe_b_host(0, np.ascontiguousarray(xb), logits, out_h, T)
+        assert np.array_equal(bits(synth.bf16_bits_to_f32(out_h)), bits(y))
+
+
 def test_errors_are_status_codes(cuda):
     torch = cuda
     spec = synth.LayerSpec(experts=8, topk=2, d=128, mid=64)
