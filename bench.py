@@ -46,8 +46,9 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clock / throttle-reason samples (every 25 ms, with nvidia-smi's own time
+    stamps); stop(t0, t1) keeps the samples that fall inside the timed region."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -60,8 +61,11 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            deadline = time.time() + 3.0          # nvidia-smi needs a moment before its first line
+            while not self.rows and time.time() < deadline:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
 
@@ -69,27 +73,41 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
-    def stop(self):
+    @staticmethod
+    def _epoch(stamp):
+        import datetime
+        try:
+            return datetime.datetime.strptime(stamp, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
+    def stop(self, t0=None, t1=None):
         if self.proc:
+            time.sleep(0.06)                      # let the last samples of the region arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        sm, mx, reasons = [], 0, set()
+        sm, mx, power, reasons, total = [], 0, [], set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             try:
-                sm.append(float(r[0]))
-                mx = max(mx, float(r[1]))
-                for n, v in zip(names, r[3:7]):
+                total += 1
+                ts = self._epoch(r[0])
+                if t0 is not None and ts is not None and not (t0 - 0.005 <= ts <= t1 + 0.03):
+                    continue
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+                power.append(float(r[3]))
+                for n, v in zip(names, r[4:8]):
                     if v.lower().startswith("active"):
                         reasons.add(n)
             except (ValueError, IndexError):
                 pass
-        busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
-        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "power_w": float(np.median(power)) if power else None,
+                "reasons": sorted(reasons), "samples": len(sm), "samples_total": total}
 
 
 # ------------------------------------------------------------------ synthetic layer on the GPU
@@ -305,13 +323,15 @@ def main():
     counter = epm if epm is not None else op
     l0 = counter.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
     ev0.record(stream)
     for _ in range(args.steps):
         step()
     ev1.record(stream)
     barrier()
+    wall1 = time.time()
     launches = counter.launches - l0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     op.synchronize(stream)
     ms = ev0.elapsed_time(ev1)
     stages = op.profile_read() if world == 1 else {"up": 0.0}
