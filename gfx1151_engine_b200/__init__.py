@@ -50,6 +50,7 @@ SYMBOLS = {
     "b200moe_ep_offsets": (_I, [_P, ctypes.POINTER(_P)]),
     "b200moe_ep_experts": (_I, [_P, _I, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _P, _P]),
+    "b200moe_ep_wait_flags": (_I, [_P, _P, _I, _I, _P]),
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_synchronize": (_I, [_P, _P]),
@@ -210,6 +211,10 @@ class MoeOperator:
 
     def ep_combine(self, out, T, stream=None):
         self._check(lib().b200moe_ep_combine(self._h, T, _ptr(out), _stream(stream)))
+
+    def ep_wait_flags(self, flags, n, expected, stream=None):
+        """Enqueue a bounded wait until flags[0..n) (int32, written by peer GPUs) reach `expected`."""
+        self._check(lib().b200moe_ep_wait_flags(self._h, _ptr(flags), n, expected, _stream(stream)))
 
     def synchronize(self, stream=None):
         """Wait for the stream and raise if a device-side wait gave up."""

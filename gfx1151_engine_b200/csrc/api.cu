@@ -868,6 +868,13 @@ int b200moe_ep_combine(b200moe_handle h, int T, void* out, void* stream) {
   return B200MOE_OK;
 }
 
+int b200moe_ep_wait_flags(b200moe_handle h, const int32_t* flags_dev, int n, int32_t expected, void* stream) {
+  if (!h || !flags_dev || n < 1 || n > 32) return B200MOE_ERR_BAD_ARG;
+  CU_TRY(h, launch_wait_flags(flags_dev, n, expected, h->status_dev, (cudaStream_t)stream));
+  h->launches++;
+  return B200MOE_OK;
+}
+
 int b200moe_synchronize(b200moe_handle h, void* stream) {
   if (!h) return B200MOE_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;

@@ -110,6 +110,10 @@ cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_
 cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half* hid16, int d, int mid,
                              const Run* runs, const int32_t* n_runs, float* pairs_f32, cudaStream_t st);
 
+// Bounded wait (2 s) until n <= 32 flags written by other GPUs have reached `expected`; a
+// timeout sets status {3, flag index}.
+cudaError_t launch_wait_flags(const int32_t* flags, int n, int32_t expected, int32_t* status, cudaStream_t st);
+
 // ---- combine.cu ----
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);

@@ -669,6 +669,35 @@ cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, cons
                                            gate_w_bf16, d);
 }
 
+// Waits until every one of n flags (written by peer GPUs' copy engines behind their data)
+// has reached `expected`. Bounded: after 2 s the kernel records status {3, index of the
+// missing flag} and returns, so that the context stays usable and the host sees the timeout.
+__global__ void k_wait_flags(const int32_t* flags, int n, int32_t expected, int32_t* status) {
+  const int i = threadIdx.x;
+  if (i >= n) return;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t spin = 0;; spin++) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+    if (v - expected >= 0) return;
+    if ((spin & 63u) == 63u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {
+        if (atomicCAS(status, 0, 3) == 0) status[1] = i;
+        return;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+cudaError_t launch_wait_flags(const int32_t* flags, int n, int32_t expected, int32_t* status, cudaStream_t st) {
+  k_wait_flags<<<1, 32, 0, st>>>(flags, n, expected, status);
+  return cudaGetLastError();
+}
+
 int route_small_max_pairs() { return kSmallPairs; }
 int route_chunk() { return kChunk; }
 

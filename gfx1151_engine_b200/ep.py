@@ -104,48 +104,43 @@ class ExpertParallelMoe:
     # ---- copy-engine transport -------------------------------------------------------------
     # The exchanges are peer copies (DMA over NVLink, no SM) straight into the destination
     # rank's receive buffer, so that they overlap the grouped GEMMs, which occupy every SM.
-    # Buffers and events are shared between the processes through CUDA IPC; "all data of chunk
-    # c has arrived" is an interprocess event per rank, recorded after the rank's copies. A
-    # wait on such an event refers to its latest record at the time of the call, so a host
-    # barrier (gloo) separates "every rank has recorded" from "every rank waits".
+    # The buffers are shared between the processes through CUDA IPC. "The rows of rank s have
+    # arrived" is a flag in the receiver's memory: s copies its sequence number there behind
+    # its data on the same stream (the copy engine runs a stream's copies in order), and the
+    # receiver enqueues a bounded device-side wait on its flags (b200moe_ep_wait_flags).
     def _p2p_setup(self, dev):
         torch, dist = self.torch, self.torch.distributed
         self.comm2 = torch.cuda.Stream(device=dev)
-        self.host_group = dist.new_group(backend="gloo")
+        self.seq = 0
+        self.seq_src = torch.arange(1 << 16, dtype=torch.int32, device=dev)   # element i holds i
         mine = []
         for b in self.buf:
-            b["sent"] = torch.cuda.Event(enable_timing=False, interprocess=True)
-            b["returned"] = torch.cuda.Event(enable_timing=False, interprocess=True)
-            b["sent"].record(torch.cuda.current_stream())
-            b["returned"].record(torch.cuda.current_stream())
+            b["flags"] = torch.zeros(2, 32, dtype=torch.int32, device=dev)    # [dispatch | return][source rank]
             mine.append({"x_recv": b["x_recv"].untyped_storage()._share_cuda_(),
                          "pairs_back": b["pairs_back"].untyped_storage()._share_cuda_(),
-                         "sent": b["sent"].ipc_handle(), "returned": b["returned"].ipc_handle(),
+                         "flags": b["flags"].untyped_storage()._share_cuda_(),
                          "device": dev.index})
+        torch.cuda.synchronize(dev)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=self.group)
         self._keep = []
         for c, b in enumerate(self.buf):
-            b["peer_x_recv"], b["peer_back"], b["peer_sent"], b["peer_returned"] = [], [], [], []
+            b["peer_x_recv"], b["peer_back"], b["peer_flags"] = [], [], []
             for r in range(self.world):
                 if r == self.rank:
                     b["peer_x_recv"].append(b["x_recv"])
                     b["peer_back"].append(b["pairs_back"])
-                    b["peer_sent"].append(None)
-                    b["peer_returned"].append(None)
+                    b["peer_flags"].append(b["flags"])
                     continue
                 info = everyone[r][c]
-                pdev = torch.device("cuda", info["device"])
-                for key, like in (("x_recv", b["x_recv"]), ("pairs_back", b["pairs_back"])):
+                for key, like, dst in (("x_recv", b["x_recv"], "peer_x_recv"), ("pairs_back", b["pairs_back"], "peer_back"),
+                                       ("flags", b["flags"], "peer_flags")):
                     st = torch.UntypedStorage._new_shared_cuda(*info[key])
                     self._keep.append(st)
-                    t = torch._utils._rebuild_tensor(
+                    b[dst].append(torch._utils._rebuild_tensor(
                         torch.storage.TypedStorage(wrap_storage=st, dtype=like.dtype, _internal=True),
-                        0, like.shape, like.stride())
-                    b["peer_x_recv" if key == "x_recv" else "peer_back"].append(t)
-                b["peer_sent"].append(torch.cuda.Event.from_ipc_handle(pdev, info["sent"]))
-                b["peer_returned"].append(torch.cuda.Event.from_ipc_handle(pdev, info["returned"]))
-        dist.barrier(group=self.host_group)
+                        0, like.shape, like.stride()))
+        dist.barrier(group=self.group)
 
     def _forward_p2p(self, layer, x, logits, out):
         torch, dist = self.torch, self.torch.distributed
@@ -154,6 +149,10 @@ class ExpertParallelMoe:
         C = min(self.chunks, (T + self.tc - 1) // self.tc)
         span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
         per = self.E // self.world
+        self.seq += 1
+        if self.seq >= (1 << 16):
+            raise RuntimeError("sequence numbers of the copy-engine transport exhausted")
+        seq = self.seq
         for c, (a, b) in enumerate(span):
             B = self.buf[c]
             self.ops[c].ep_route(layer, x[a:b], logits[a:b], eoff_out=B["eoff"], stream=main)
@@ -171,8 +170,10 @@ class ExpertParallelMoe:
             bounds.append((bd, cnt))
             rows += int(cnt[:, self.rank].sum())
         self.last_recv_rows = rows
-        order = [(self.rank + i) % self.world for i in range(self.world)]
-        # 1. dispatch: my rows for rank p go behind the rows of the ranks before me in p's buffer
+        order = [(self.rank + i) % self.world for i in range(1, self.world + 1)]   # peers first, myself last
+        # 1. dispatch: my rows for rank p go behind the rows of the ranks before me in p's buffer.
+        #    (p has finished reading that buffer: I waited for p's results of the previous
+        #    forward, which p sent after its GEMMs.)
         self.comm.wait_event(routed)
         with torch.cuda.stream(self.comm):
             for c in range(C):
@@ -184,16 +185,12 @@ class ExpertParallelMoe:
                         dst0 = int(cnt[:self.rank, p].sum())
                         src0 = int(bd[self.rank, p])
                         B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
-                B["sent"].record(self.comm)
-        dist.barrier(group=self.host_group)
-        # 2. experts per chunk as its rows arrive; results go straight back to their owners
+                    B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
+        # 2. experts per chunk once its rows have arrived; results go straight back to their owners
         for c in range(C):
             bd, cnt = bounds[c]
             B = self.buf[c]
-            for p in range(self.world):
-                if p != self.rank:
-                    main.wait_event(B["peer_sent"][p])
-            main.wait_event(B["sent"])
+            self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
             self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
             done = torch.cuda.Event()
             done.record(main)
@@ -205,15 +202,11 @@ class ExpertParallelMoe:
                         src0 = int(cnt[:s, self.rank].sum())
                         dst0 = int(bd[s, self.rank])
                         B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
-                B["returned"].record(self.comm2)
-        dist.barrier(group=self.host_group)
+                    B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
         # 3. combine
         for c, (a, b) in enumerate(span):
             B = self.buf[c]
-            for p in range(self.world):
-                if p != self.rank:
-                    main.wait_event(B["peer_returned"][p])
-            main.wait_event(B["returned"])
+            self.ops[c].ep_wait_flags(B["flags"][1], self.world, seq, stream=main)
             self.ops[c].ep_combine(out[a:b], b - a, stream=main)
 
     def load_q4cp(self, layer, gate_up, down):

@@ -170,6 +170,12 @@ int b200moe_ep_route(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
 int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev);
 int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream);
 int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream);
+/* For hosts that move the rows with peer copies (copy engines) instead of a collective: every
+ * sender writes its sequence number into the receiver's flag array behind its data (same
+ * stream, so the copy engine orders them); this enqueues a wait until all n <= 32 flags have
+ * reached `expected`. The wait is bounded (2 s): a timeout is reported by b200moe_synchronize as
+ * B200MOE_ERR_DEVICE_TIMEOUT and the stream continues. */
+int b200moe_ep_wait_flags(b200moe_handle h, const int32_t* flags_dev, int n, int32_t expected, void* stream);
 
 /* Reads back what the last forward / route call left in the workspace (host buffers; any may
  * be NULL): tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k] as defined by
