@@ -211,9 +211,9 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--tokens", type=int, default=T_CHUNK)
     ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
-    ap.add_argument("--chunks", type=int, default=1, help="N>1: token chunks whose exchanges overlap the GEMMs")
+    ap.add_argument("--chunks", type=int, default=2, help="N>1: token chunks whose exchanges overlap the GEMMs")
     ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
-    ap.add_argument("--transport", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--transport", default="p2p", choices=["nccl", "p2p"],
                     help="N>1: exchanges by NCCL all-to-all or by peer copies (copy engines) through CUDA IPC")
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -320,6 +320,7 @@ def main():
     barrier()
     if rank == 0:
         sampler.start()
+    barrier()   # the sampler's start-up must not skew the ranks against each other
     counter = epm if epm is not None else op
     l0 = counter.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -383,7 +384,8 @@ def main():
         dist.all_reduce(rows, op=dist.ReduceOp.SUM)
         ep_info = {"experts_per_gpu": E // world, "placement": "greedy by calibration histogram",
                    "recv_rows_max_over_mean": float(mx.item() / (rows.item() / world)),
-                   "exchange": "NCCL all_to_all_single (dispatch, combine), all_gather of expert offsets",
+                   "exchange": ("peer copies by the copy engines into symmetric-memory receive buffers, arrival flags + bounded device-side wait"
+                                if args.transport == "p2p" else "NCCL all_to_all_single (dispatch, combine)") + "; NCCL all_gather of expert offsets",
                    "chunks": args.chunks, "transport": args.transport,
                    "check_vs_single_gpu": check}
 

@@ -2,8 +2,10 @@
 
 One process per GPU (torch.distributed, NCCL). The 512 experts are partitioned evenly; a
 forward is three library phases (route+gather, grouped GEMMs on the received rows, combine)
-with two NCCL all-to-all exchanges of fp16 rows in between. The reference engine is a
-single-device program and has no counterpart of this file.
+with two exchanges of fp16 rows in between: NCCL all-to-all (transport "nccl") or peer copies
+by the copy engines into symmetric-memory buffers (transport "p2p"), which overlap the GEMMs
+because they need no SM. The reference engine is a single-device program and has no
+counterpart of this file.
 
 Placement: under a skewed router a contiguous split of the expert ids leaves the ranks with
 very different loads, so experts are renumbered ("placed") by a greedy longest-first
@@ -85,11 +87,17 @@ class ExpertParallelMoe:
                 op.share_weights(self.ops[0])
             pairs = self.tc * topk
             cap = int(cap_factor * pairs)
+            if transport == "p2p":
+                # written by the peers' copy engines: symmetric memory (mapped into every rank)
+                import torch.distributed._symmetric_memory as symm_mem
+                remote = lambda *shape, dtype=torch.float16: symm_mem.empty(*shape, dtype=dtype, device=dev)
+            else:
+                remote = lambda *shape, dtype=torch.float16: torch.empty(*shape, dtype=dtype, device=dev)
             b = {"cap": cap,
                  "x_send": torch.empty(pairs, d_model, dtype=torch.float16, device=dev),
-                 "x_recv": torch.empty(cap, d_model, dtype=torch.float16, device=dev),
+                 "x_recv": remote(cap, d_model),
                  "pairs_recv": torch.empty(cap, d_model, dtype=torch.float16, device=dev),
-                 "pairs_back": torch.empty(pairs, d_model, dtype=torch.float16, device=dev),
+                 "pairs_back": remote(pairs, d_model),
                  "eoff": torch.empty(experts + 1, dtype=torch.int32, device=dev),
                  "eoff_all": torch.empty(world * (experts + 1), dtype=torch.int32, device=dev)}
             op.ep_attach(b["x_send"], b["x_recv"], b["pairs_recv"], b["pairs_back"], cap)
@@ -104,42 +112,30 @@ class ExpertParallelMoe:
     # ---- copy-engine transport -------------------------------------------------------------
     # The exchanges are peer copies (DMA over NVLink, no SM) straight into the destination
     # rank's receive buffer, so that they overlap the grouped GEMMs, which occupy every SM.
-    # The buffers are shared between the processes through CUDA IPC. "The rows of rank s have
+    # The receive buffers are symmetric memory (torch.distributed._symmetric_memory: mapped into
+    # every rank through the driver's virtual-memory interface; plain cudaIpc mappings reached
+    # only 23 GB/s here, these 685 GB/s per direction). "The rows of rank s have
     # arrived" is a flag in the receiver's memory: s copies its sequence number there behind
     # its data on the same stream (the copy engine runs a stream's copies in order), and the
     # receiver enqueues a bounded device-side wait on its flags (b200moe_ep_wait_flags).
     def _p2p_setup(self, dev):
         torch, dist = self.torch, self.torch.distributed
+        import torch.distributed._symmetric_memory as symm_mem
+        group = self.group if self.group is not None else dist.group.WORLD
         self.comm2 = torch.cuda.Stream(device=dev)
         self.seq = 0
         self.seq_src = torch.arange(1 << 16, dtype=torch.int32, device=dev)   # element i holds i
-        mine = []
+        self._handles = []
         for b in self.buf:
-            b["flags"] = torch.zeros(2, 32, dtype=torch.int32, device=dev)    # [dispatch | return][source rank]
-            mine.append({"x_recv": b["x_recv"].untyped_storage()._share_cuda_(),
-                         "pairs_back": b["pairs_back"].untyped_storage()._share_cuda_(),
-                         "flags": b["flags"].untyped_storage()._share_cuda_(),
-                         "device": dev.index})
-        torch.cuda.synchronize(dev)
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=self.group)
-        self._keep = []
-        for c, b in enumerate(self.buf):
+            b["flags"] = symm_mem.empty(2, 32, dtype=torch.int32, device=dev)  # [dispatch | return][source rank]
+            b["flags"].zero_()
+            torch.cuda.synchronize(dev)
             b["peer_x_recv"], b["peer_back"], b["peer_flags"] = [], [], []
-            for r in range(self.world):
-                if r == self.rank:
-                    b["peer_x_recv"].append(b["x_recv"])
-                    b["peer_back"].append(b["pairs_back"])
-                    b["peer_flags"].append(b["flags"])
-                    continue
-                info = everyone[r][c]
-                for key, like, dst in (("x_recv", b["x_recv"], "peer_x_recv"), ("pairs_back", b["pairs_back"], "peer_back"),
-                                       ("flags", b["flags"], "peer_flags")):
-                    st = torch.UntypedStorage._new_shared_cuda(*info[key])
-                    self._keep.append(st)
-                    b[dst].append(torch._utils._rebuild_tensor(
-                        torch.storage.TypedStorage(wrap_storage=st, dtype=like.dtype, _internal=True),
-                        0, like.shape, like.stride()))
+            for key, dst in (("x_recv", "peer_x_recv"), ("pairs_back", "peer_back"), ("flags", "peer_flags")):
+                hdl = symm_mem.rendezvous(b[key], group)
+                self._handles.append(hdl)
+                for r in range(self.world):
+                    b[dst].append(b[key] if r == self.rank else hdl.get_buffer(r, list(b[key].shape), b[key].dtype))
         dist.barrier(group=self.group)
 
     def _forward_p2p(self, layer, x, logits, out):
