@@ -128,6 +128,26 @@ def q4cp_blob_device(torch, rows, cols, gen):
     return blob
 
 
+def gguf_blocks_device(torch, rows, cols, kind, gen):
+    """GGUF blocks built in device memory with the magnitudes of the q4cp configs: per block
+    a = |N(0, 0.02)|; Q4_K (144 B / 256): d = a/(63*15), dmin = a/(63*2), the other 140 bytes
+    uniform; Q5_1 (24 B / 32): d = a/31, m = -a/2, the other 20 bytes uniform."""
+    per, bb = (256, 144) if kind == "q4k" else (32, 24)
+    nb = rows * cols // per
+    blob = torch.empty(nb, bb, dtype=torch.uint8, device="cuda")
+    step = 1 << 22
+    for o in range(0, nb, step):
+        n = min(step, nb - o)
+        blob[o:o + n] = torch.randint(0, 256, (n, bb), dtype=torch.uint8, device="cuda", generator=gen)
+        a = (torch.randn(n, device="cuda", generator=gen) * 0.02).abs()
+        if kind == "q4k":
+            hdr = torch.stack([a / (63.0 * 15.0), a / (63.0 * 2.0)], dim=1)
+        else:
+            hdr = torch.stack([a / 31.0, -a / 2.0], dim=1)
+        blob[o:o + n, 0:4] = hdr.to(torch.float16).view(torch.uint8).reshape(n, 4)
+    return blob.reshape(-1)
+
+
 def zipf_logits(torch, T, gen, seed):
     from gfx1151_engine_b200 import synth
     bias = synth.zipf_bias(synth.rng_for(seed, 77), E)
@@ -211,6 +231,9 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--tokens", type=int, default=T_CHUNK)
     ap.add_argument("--experts", type=int, default=E, help="smaller layer for profiler captures (not a bench line)")
+    ap.add_argument("--format", default="q4cp", choices=["q4cp", "gguf"],
+                    help="expert tensors: hgn q4cp (the benchmark workload) or GGUF Q4_K gate/up + Q5_1 down "
+                         "(the GGUF variant; with --tokens 8192 --no-decode --no-cpu, single GPU)")
     ap.add_argument("--chunks", type=int, default=2, help="N>1: token chunks whose exchanges overlap the GEMMs")
     ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
     ap.add_argument("--transport", default="p2p", choices=["nccl", "p2p"],
@@ -241,8 +264,16 @@ def main():
 
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234)            # one weight set shared by all ranks
-    gu = q4cp_blob_device(torch, E * 2 * MID, D, gen)
-    dn = q4cp_blob_device(torch, E * D, MID, gen)
+    gguf = args.format == "gguf"
+    if gguf:
+        if world > 1:
+            raise SystemExit("--format gguf is a single-GPU measurement")
+        args.no_decode = args.no_cpu = True
+        gu = (gguf_blocks_device(torch, E * MID, D, "q4k", gen), gguf_blocks_device(torch, E * MID, D, "q4k", gen))
+        dn = gguf_blocks_device(torch, E * D, MID, "q51", gen)
+    else:
+        gu = q4cp_blob_device(torch, E * 2 * MID, D, gen)
+        dn = q4cp_blob_device(torch, E * D, MID, gen)
     epm = None
     if world > 1:
         # expert parallelism: E/world experts per GPU, placed by a calibration histogram of the
@@ -259,7 +290,10 @@ def main():
         op = epm.op
     else:
         op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)
-        op.load_q4cp(0, gu, dn)
+        if gguf:
+            op.load_gguf(0, gu[0], gu[1], dn)
+        else:
+            op.load_q4cp(0, gu, dn)
     if args.decode_only:
         args.no_cpu = True
     want_cpu = rank == 0 and world == 1 and not args.no_cpu
@@ -408,7 +442,8 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD if (E, T) == (512, T_CHUNK) else "reduced case for profiling (not the benchmark workload)", "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
+        "config": {"workload": ("GGUF variant (Q4_K gate/up, Q5_1 down), not the benchmark workload" if gguf else
+                                WORKLOAD if (E, T) == (512, T_CHUNK) else "reduced case for profiling (not the benchmark workload)"), "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
                    "d_mid": MID, "parallelism": "expert-parallel x%d" % world if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 3.6 GB of expert weights + 168 MB of activations per step"},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "expert_parallel": ep_info,

@@ -518,7 +518,9 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
                     (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max);
   if (simt && c.gemm_impl != B200MOE_GEMM_SIMT && T > h->decode_max)
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
-  const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO && L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP &&
+  // (the shared expert's images are q4cp: it can ride along only with q4cp routed experts)
+  const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO &&
+                    (!shared || (L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP)) &&
                     pairs + (shared ? T : 0) <= h->dec_rows && std::min(E, pairs) + 1 <= gemv_max_runs() &&
                     d <= gemv_max_k() && mid <= gemv_max_mid() && d % 32 == 0 && mid % 32 == 0;
   if (gemv) {

@@ -89,6 +89,27 @@ __device__ __forceinline__ float chunk_dot(const uint4 c, uint32_t lut, uint32_t
   return s0 + s1;
 }
 
+// Q5_1: the same with the fifth bits (bits 2i, 2i+1 of qh belong to code byte i) added to
+// the looked-up pair as 16.0 before the multiply-add: q + 16*bit <= 31 is exact in fp16.
+__device__ __forceinline__ float chunk_dot5(const uint4 c, uint32_t qh, uint32_t lut, uint32_t xs) {
+  const uint32_t w4[4] = {c.x, c.y, c.z, c.w};
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    uint32_t x[4];
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xs + q * 16));
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const uint32_t t = (qh >> (2 * (q * 4 + b))) & 3u;
+      const uint32_t hi = (t & 1u) * 0x4C00u + (t >> 1) * 0x4C000000u;  // 16.0 in fp16 where the bit is set
+      const uint32_t pair = lds_b32(__byte_perm(w4[q], lut, 0x7604 | (b << 4)));
+      const __half2 w2 = __hadd2(*(const __half2*)&pair, *(const __half2*)&hi);
+      fma_pair((b & 1) ? s1 : s0, *(const uint32_t*)&w2, x[b]);
+    }
+  }
+  return s0 + s1;
+}
+
 __device__ __forceinline__ uint32_t pack_half2_sat(float a, float b) {
   __half2 h = __floats2half2_rn(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f));
   return *(uint32_t*)&h;
@@ -101,12 +122,18 @@ struct GemvShared {
   float book[3][16];
 };
 
-template <bool UP>
+// FMT: format of the image this kernel reads (gate/up: q4cp or Q4_K; down: q4cp or Q5_1). The
+// GGUF formats use the identity code book (table entry = the two code values) and fold their
+// affine constants into the group sums: Q4_K  sum w x = (d*sc) * sum q x - (dmin*m) * sum x,
+// Q5_1  sum w x = d * sum (q + 16 bit) x + m * sum x, with sum x per 32-group staged next to
+// the activations.
+template <bool UP, int FMT>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 k_gemv(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t gsm[];
   __shared__ GemvShared sh;
   __shared__ __align__(16) __half xs[kGemvMaxK];   // activations of the current unit
+  __shared__ float xsum[kGemvMaxK / 32];            // their sums per 32-group (GGUF formats)
   __shared__ float red[2][kGemvWarps][32];          // partial sums of the K slices, double-buffered by task
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t dyn0 = (uint32_t)__cvta_generic_to_shared(gsm);
@@ -175,11 +202,12 @@ k_gemv(const GemvParams p) {
   const long long total = (long long)sh.first[n_runs_all] * tpu;
   const long long base = total / gridDim.x, rem = total % gridDim.x;
   const long long c0 = blockIdx.x * base + min((long long)blockIdx.x, rem), c1 = c0 + base + ((long long)blockIdx.x < rem ? 1 : 0);
-  constexpr size_t tile_b = tile_bytes(kQ4CP);  // both images are q4cp on this path
+  constexpr size_t tile_b = tile_bytes(FMT);     // the routed and the shared image have the same format
+  constexpr int kMetaRow = FMT == kQ4CP ? 4 : FMT == kQ4K ? 8 : 16;  // bytes of metadata per tile row
   const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
 
   uint4 cw[2 * kKpw];  // four item slots: codes of both halves of a K block ...
-  uint32_t sw[kKpw];   // ... and the row's two fp16 scales
+  uint4 sw[kKpw];      // ... and the row's metadata of the K block (q4cp: .x = two fp16 scales)
   int cur_tok = -1, buf = 0;
   for (long long seg = c0; seg < c1;) {
     // ---- a segment: the CTA's tasks j0 .. j1-1 of one unit ----
@@ -209,7 +237,16 @@ k_gemv(const GemvParams p) {
         const size_t r16 = row_off(j) - (size_t)(UP ? j >> 2 : j >> 1) * mt_b;  // row * 16
         cw[2 * s] = __ldg((const uint4*)pc);
         cw[2 * s + 1] = __ldg((const uint4*)(pc + 2048));
-        sw[s] = __ldg((const uint32_t*)(pc - r16 + kCodeBytes + (r16 >> 2)));
+        const uint8_t* pm = pc - r16 + kCodeBytes + (r16 >> 4) * kMetaRow;
+        if (FMT == kQ4CP) {
+          sw[s].x = __ldg((const uint32_t*)pm);
+        } else if (FMT == kQ4K) {
+          const uint2 u = __ldg((const uint2*)pm);
+          sw[s].x = u.x;
+          sw[s].y = u.y;
+        } else {
+          sw[s] = __ldg((const uint4*)pm);
+        }
       }
     };
     const int nseg = (j1 - j0) * kpw;
@@ -244,7 +281,17 @@ k_gemv(const GemvParams p) {
         ((uint4*)xs)[c] = ((const uint4*)(p.hid + (size_t)run.first * p.mid))[c];  // written by the previous kernel: plain loads
       staged = true;
     }
-    if (staged) __syncthreads();
+    if (staged) {
+      __syncthreads();
+      if (FMT != kQ4CP) {
+        for (int g = threadIdx.x; g < p.K / 32; g += kGemvThreads) {
+          float t = 0.f;
+          for (int i = 0; i < 32; i++) t += __half2float(xs[g * 32 + i]);
+          xsum[g] = t;
+        }
+        __syncthreads();
+      }
+    }
 
     int cj = j0, ci = 0;  // the compute stream's position
     float acc = 0.f;
@@ -254,8 +301,23 @@ k_gemv(const GemvParams p) {
         if (n0 + s < nseg) {
           if (kb0 + ci < KB) {
             const uint32_t xa = xs_addr + (uint32_t)(kb0 + ci) * (kTileK * 2);
-            const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
-            acc += half_bits_to_f32((uint16_t)(sw[s] & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s] >> 16)) * d1;
+            if (FMT == kQ4CP) {
+              const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
+              acc += half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s].x >> 16)) * d1;
+            } else if (FMT == kQ4K) {
+              // metadata {fp16 d, fp16 dmin, u8 sc0, u8 m0, u8 sc1, u8 m1}
+              const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
+              const float dd = half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)), dm = half_bits_to_f32((uint16_t)(sw[s].x >> 16));
+              const float x0 = xsum[2 * (kb0 + ci)], x1 = xsum[2 * (kb0 + ci) + 1];
+              acc += (dd * (float)(sw[s].y & 0xFFu)) * d0 - (dm * (float)((sw[s].y >> 8) & 0xFFu)) * x0;
+              acc += (dd * (float)((sw[s].y >> 16) & 0xFFu)) * d1 - (dm * (float)(sw[s].y >> 24)) * x1;
+            } else {
+              // metadata [2]{fp16 d, fp16 m, u32 fifth bits}
+              const float d0 = chunk_dot5(cw[2 * s], sw[s].y, lut, xa), d1 = chunk_dot5(cw[2 * s + 1], sw[s].w, lut, xa + 64);
+              const float x0 = xsum[2 * (kb0 + ci)], x1 = xsum[2 * (kb0 + ci) + 1];
+              acc += half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s].x >> 16)) * x0;
+              acc += half_bits_to_f32((uint16_t)(sw[s].z & 0xFFFFu)) * d1 + half_bits_to_f32((uint16_t)(sw[s].z >> 16)) * x1;
+            }
           }
           // the slot just consumed receives the item four further down the stream
           if (n0 + s + kKpw < nseg) fetch(s, pj, pi);
@@ -294,7 +356,7 @@ k_gemv(const GemvParams p) {
   }
 }
 
-template <bool UP>
+template <bool UP, int FMT>
 cudaError_t launch_gemv(const GemvParams& p, cudaStream_t st) {
   // the dynamic allocation must reach the end of the last table, wherever it starts
   constexpr int kMaxSmem = UP ? kTab1 + 65536 : kTab0 + 65536;
@@ -303,14 +365,14 @@ cudaError_t launch_gemv(const GemvParams& p, cudaStream_t st) {
   static bool attr_done = false;
   static int sms = 0;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemv<UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    cudaError_t e = cudaFuncSetAttribute(k_gemv<UP, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return e;
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     attr_done = true;
   }
-  return launch_pdl(k_gemv<UP>, dim3(sms), dim3(kGemvThreads), (size_t)smem, st, p);
+  return launch_pdl(k_gemv<UP, FMT>, dim3(sms), dim3(kGemvThreads), (size_t)smem, st, p);
 }
 
 }  // namespace
@@ -327,7 +389,9 @@ cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_
   if (img_sh) p.img_sh = *img_sh;
   p.runs = runs; p.n_runs = n_runs; p.K = d; p.mid = mid;
   p.x = (const uint16_t*)x_bf16; p.tokidx = tokidx; p.hid = hid16;
-  return launch_gemv<true>(p, st);
+  if (img.fmt == kQ4K) return launch_gemv<true, kQ4K>(p, st);
+  if (img.fmt == kQ51) return launch_gemv<true, kQ51>(p, st);
+  return launch_gemv<true, kQ4CP>(p, st);
 }
 
 cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half* hid16, int d, int mid,
@@ -338,7 +402,9 @@ cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half
   p.runs = runs; p.n_runs = n_runs; p.K = mid; p.mid = mid;
   p.hid = const_cast<__half*>(hid16);
   p.out = pairs_f32;
-  return launch_gemv<false>(p, st);
+  if (img.fmt == kQ4K) return launch_gemv<false, kQ4K>(p, st);
+  if (img.fmt == kQ51) return launch_gemv<false, kQ51>(p, st);
+  return launch_gemv<false, kQ4CP>(p, st);
 }
 
 }  // namespace b200moe
