@@ -52,10 +52,36 @@ __device__ __forceinline__ void router_one_token(const float* __restrict__ lg, i
     v[j] = p;
   }
   __syncwarp();
+  // Sum of the exponentials, as the reference takes it: in double, in index order. All terms
+  // are floats in (0, 1]: when the smallest non-zero one's last mantissa bit still fits a
+  // double that holds the total, every partial sum of ANY order is exact, so the tree sum has
+  // the very same bits and the E dependent additions are only needed otherwise.
   double se = 0;
-  if (lane == 0)
-    for (int i = 0; i < E; i++) se += (double)sp[i];  // index order, as the reference sums
-  se = shfl_double(se, 0);
+  float mn = 2.f;
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (j * 32 + lane < E) {
+      se += (double)v[j];
+      if (v[j] > 0.f) mn = fminf(mn, v[j]);
+    }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    se += __hiloint2double(__shfl_xor_sync(0xffffffffu, __double2hiint(se), o),
+                           __shfl_xor_sync(0xffffffffu, __double2loint(se), o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  se = shfl_double(se, 0);  // (inexact sums may differ between lanes in the last bit: take one)
+  {
+    const int e_min = (int)((__float_as_uint(mn) >> 23) & 0xFF) - 127;
+    const int bits_total = (int)((__double2hiint(se) >> 20) & 0x7FF) - 1023 + 2;  // generous by one bit
+    const bool exact = mn >= 1.17549435e-38f && bits_total - (e_min - 23) <= 53;
+    if (!exact) {  // warp-uniform: mn and se are the same in every lane
+      se = 0;
+      if (lane == 0)
+        for (int i = 0; i < E; i++) se += (double)sp[i];  // index order, as the reference sums
+      se = shfl_double(se, 0);
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 16; j++) {
     int e = j * 32 + lane;
@@ -444,8 +470,21 @@ k_route_scan(int32_t* __restrict__ blockcnt, int nblk, int E, int pairs, int T, 
   const int e = threadIdx.x;
   int cnt = 0;
   if (e < E) {
-    for (int b = 0; b < nblk; b++) {
-      int c = blockcnt[(size_t)b * E + e];
+    // exclusive prefix down this expert's column of the chunk counts; the loads of eight
+    // rows are issued together so that the walk does not pay one memory latency per chunk
+    int b = 0;
+    for (; b + 8 <= nblk; b += 8) {
+      int c[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) c[i] = blockcnt[(size_t)(b + i) * E + e];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        blockcnt[(size_t)(b + i) * E + e] = cnt;
+        cnt += c[i];
+      }
+    }
+    for (; b < nblk; b++) {
+      const int c = blockcnt[(size_t)b * E + e];
       blockcnt[(size_t)b * E + e] = cnt;
       cnt += c;
     }
