@@ -41,6 +41,9 @@ SYMBOLS = {
     "b200moe_forward_routed": (_I, [_P, _I, _P, _I, _P, _P, _I, _P, _P]),
     "b200moe_forward_host": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
+    "b200moe_load_router": (_I, [_P, _I, _P]),
+    "b200moe_router_logits": (_I, [_P, _I, _P, _I, _P, _P]),
+    "b200moe_forward_hidden": (_I, [_P, _I, _P, _I, _P, _P]),
     "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
     "b200moe_route_static": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_ep_set_placement": (_I, [_P, _P]),
@@ -150,6 +153,19 @@ class MoeOperator:
     def load_gguf(self, layer, gate, up, down, type_gu=GGML_Q4_K, type_dn=GGML_Q5_1):
         self._check(lib().b200moe_load_gguf(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),
                                             type_gu, type_dn))
+
+    def load_router(self, layer, gate_weight_bf16):
+        """layers.L.mlp.gate.weight, bf16 [experts][d_model] (tensor or numpy uint16 bits)."""
+        self._check(lib().b200moe_load_router(self._h, layer, _ptr(gate_weight_bf16)))
+
+    def router_logits(self, layer, x, logits, T=None, stream=None):
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_router_logits(self._h, layer, _ptr(x), T, _ptr(logits), _stream(stream)))
+
+    def moe_hidden(self, layer, x, out, T=None, stream=None):
+        """out[T][d] (bf16) = MoE(x) with the router logits computed from x; asynchronous."""
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_forward_hidden(self._h, layer, _ptr(x), T, _ptr(out), _stream(stream)))
 
     def load_shared_q4cp(self, layer, gate, up, down, gate_w_bf16):
         self._check(lib().b200moe_load_shared_q4cp(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),

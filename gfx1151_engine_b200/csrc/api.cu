@@ -22,6 +22,7 @@ constexpr int kProfRing = 64, kProfEvents = 6;
 struct LayerWeights {
   Image gu, dn, sh_gu, sh_dn;
   uint16_t* sh_gate_w = nullptr;
+  uint16_t* router_w = nullptr;  // bf16 [E][d], null until b200moe_load_router
   bool loaded = false, shared_loaded = false;
   bool borrowed = false;  // images belong to another handle
 };
@@ -39,6 +40,10 @@ struct b200moe_ctx {
   void* pairs = nullptr;    // [rows][d]   fp32 or fp16
   __half* x_sorted = nullptr;
   int dec_rows = 0;
+  RouterPlan* rplan = nullptr;     // router logits from hidden states
+  float* router_logits = nullptr;  // [max_tokens][E]
+  int32_t* flag_list = nullptr;    // (token * E + expert) pairs whose logits are recomputed exactly
+  int32_t* flag_count = nullptr;
   void *x_stage = nullptr, *out_stage = nullptr;
   float* logits_stage = nullptr;
   int32_t* status_dev = nullptr;
@@ -241,6 +246,9 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   A((uint8_t**)&h->pairs, pair_bytes);
   if (!simt_all) A(&h->x_sorted, rows * d);
   h->dec_rows = (int)dec_rows;
+  A(&h->router_logits, (size_t)Tm * E);
+  A(&h->flag_list, (size_t)Tm * 16);
+  A(&h->flag_count, 1);
   A((uint8_t**)&h->x_stage, (size_t)Tm * d * 2);
   A((uint8_t**)&h->out_stage, (size_t)Tm * d * 2);
   A(&h->logits_stage, (size_t)Tm * E);
@@ -249,6 +257,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->status_host, 16);
   if (e == cudaSuccess && !simt_all)
     e = tc_create(&h->tc, h->x_sorted, (__half*)h->hid, (long long)rows, d, mid);
+  if (e == cudaSuccess && !simt_all) e = router_plan_create(&h->rplan);
   if (e != cudaSuccess) {
     std::string msg = std::string("b200moe_create: ") + cudaGetErrorString(e);
     cudaGetLastError();
@@ -271,6 +280,7 @@ int b200moe_destroy(b200moe_handle h) {
     free_image(L.sh_gu);
     free_image(L.sh_dn);
     if (L.sh_gate_w) cudaFree(L.sh_gate_w);
+    if (L.router_w) cudaFree(L.router_w);
   }
   free_all(h->allocs);
   if (h->place_dev && !h->place_borrowed) cudaFree(h->place_dev);
@@ -290,6 +300,7 @@ int b200moe_destroy(b200moe_handle h) {
   if (h->ev_start) cudaEventDestroy(h->ev_start);
   if (h->status_host) cudaFreeHost(h->status_host);
   if (h->tc) tc_destroy(h->tc);
+  if (h->rplan) router_plan_destroy(h->rplan);
   cudaGetLastError();
   delete h;
   return B200MOE_OK;
@@ -606,6 +617,54 @@ int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
   if (h->prof) CU_TRY(h, cudaEventRecord(h->prof_ev[(size_t)h->prof_head * kProfEvents], st));
   return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st,
                       h->prof, logits_dev);
+}
+
+int b200moe_load_router(b200moe_handle h, int layer, const void* gate_weight_bf16) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!gate_weight_bf16) return fail(h, B200MOE_ERR_BAD_ARG, "load_router: null pointer");
+  if (h->cfg.experts > 512 || h->cfg.d_model % 64 != 0)
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "load_router: needs experts <= 512 and d_model % 64 == 0");
+  LayerWeights& L = h->layers[layer];
+  if (L.borrowed) return fail(h, B200MOE_ERR_BAD_ARG, "load_router: this handle borrows its weights");
+  const size_t bytes = (size_t)h->cfg.experts * h->cfg.d_model * 2;
+  if (!L.router_w) CU_TRY(h, cudaMalloc((void**)&L.router_w, bytes));
+  CU_TRY(h, cudaMemcpy(L.router_w, gate_weight_bf16, bytes, cudaMemcpyDefault));
+  return B200MOE_OK;
+}
+
+int b200moe_router_logits(b200moe_handle h, int layer, const void* x_bf16_dev, int T, float* logits_dev,
+                          void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_dev || !logits_dev || T < 0 || T > h->cfg.max_tokens)
+    return fail(h, B200MOE_ERR_BAD_ARG, "router_logits: bad argument");
+  LayerWeights& L = h->layers[layer];
+  if (!L.router_w) return fail(h, B200MOE_ERR_NOT_LOADED, "router_logits: router weight not loaded");
+  if (T == 0) return B200MOE_OK;
+  const int E = h->cfg.experts, d = h->cfg.d_model;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int cap = h->cfg.max_tokens * 16;
+  if (T <= 16 || !h->rplan) {
+    // few tokens: double sums (1e-9 from the reference), then the reference's arithmetic for
+    // the experts that decide the top-k where two of them are within a few float ulps
+    CU_TRY(h, launch_router_dots(x_bf16_dev, L.router_w, T, E, d, logits_dev, st));
+    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 5e-7f, h->flag_list, h->flag_count, cap, st));
+  } else {
+    CU_TRY(h, launch_router_gemm(h->rplan, x_bf16_dev, L.router_w, T, E, d, logits_dev, h->status_dev, st));
+    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 1e-4f, h->flag_list, h->flag_count, cap, st));
+  }
+  CU_TRY(h, launch_router_pairs(x_bf16_dev, L.router_w, h->flag_list, h->flag_count, cap, E, d, logits_dev, st));
+  h->launches += 3;
+  return B200MOE_OK;
+}
+
+int b200moe_forward_hidden(b200moe_handle h, int layer, const void* x_bf16_dev, int T, void* out_bf16_dev,
+                           void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_dev || !out_bf16_dev || T < 0 || T > h->cfg.max_tokens)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward_hidden: bad argument (null pointer or T out of range)");
+  if (T == 0) return B200MOE_OK;
+  if (int s = b200moe_router_logits(h, layer, x_bf16_dev, T, h->router_logits, stream)) return s;
+  return b200moe_forward(h, layer, x_bf16_dev, T, h->router_logits, out_bf16_dev, stream);
 }
 
 int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, int T,

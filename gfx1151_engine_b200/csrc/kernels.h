@@ -114,6 +114,24 @@ cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half
 // timeout sets status {3, flag index}.
 cudaError_t launch_wait_flags(const int32_t* flags, int n, int32_t expected, int32_t* status, cudaStream_t st);
 
+// ---- router_gemm.cu (router logits from hidden states) ----
+struct RouterPlan;
+cudaError_t router_plan_create(RouterPlan** out);
+void router_plan_destroy(RouterPlan* p);
+// logits[T][E] fp32 = x[T][d] (bf16) . w[E][d]^T (bf16) on the tensor cores (T > 16)
+cudaError_t launch_router_gemm(RouterPlan* p, const void* x_bf16, const void* w_bf16, int T, int E, int d,
+                               float* logits, int32_t* status, cudaStream_t st);
+// few tokens: every logit as a double tree sum of the exact products, rounded to float
+cudaError_t launch_router_dots(const void* x_bf16, const void* w_bf16, int T, int E, int d, float* logits,
+                               cudaStream_t st);
+// pairs/count <- (token * E + expert) of the experts that decide a token's top-k, for tokens
+// where two of them are closer than rel_margin x magnitude (at most cap pairs are stored)
+cudaError_t launch_router_flag(const float* logits, int T, int E, int k, float rel_margin, int32_t* pairs,
+                               int32_t* count, int cap, cudaStream_t st);
+// the listed logits in the reference's arithmetic
+cudaError_t launch_router_pairs(const void* x_bf16, const void* w_bf16, const int32_t* pairs, const int32_t* count,
+                                int cap, int E, int d, float* logits, cudaStream_t st);
+
 // ---- combine.cu ----
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);

@@ -116,6 +116,26 @@ int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, 
 int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, int T,
                          const float* logits_host, void* out_bf16_host, void* stream);
 
+/* Router logits from hidden states. Replaces the engine's router GEMM in front of moe_b
+ * (gemm(gate_weight(l), d_xb, d_routerb, P), src/gpu/parts/40_model.inc:4022-4025) and follows the
+ * CPU reference (matvec over layers.L.mlp.gate.weight, src/ref.cpp:68-77, 565-567: double
+ * products summed in index order, rounded to float once).
+ *   load_router:    bf16 [experts][d_model], host or device pointer, copied into library memory.
+ *   router_logits:  logits_dev[T][experts] fp32. T <= 16: double sums of the exact products
+ *                   (1e-9 from the reference's sum). T > 16: tensor-core GEMM (exact bf16
+ *                   products, fp32 sums, ~1e-5 from the reference). In both cases the experts
+ *                   that decide a token's top-k (its k largest logits and everything within two
+ *                   margins of the k-th) are recomputed in the reference's arithmetic whenever
+ *                   two of them are closer than the margin, so that the top-k ids and their
+ *                   order are the reference's; the remaining logits only enter the softmax
+ *                   denominator, which cancels in the renormalised weights.
+ *   forward_hidden: router_logits into a workspace, then b200moe_forward. */
+int b200moe_load_router(b200moe_handle h, int layer, const void* gate_weight_bf16);
+int b200moe_router_logits(b200moe_handle h, int layer, const void* x_bf16_dev, int T, float* logits_dev,
+                          void* stream);
+int b200moe_forward_hidden(b200moe_handle h, int layer, const void* x_bf16_dev, int T, void* out_bf16_dev,
+                           void* stream);
+
 /* Replaces: router_topk_b / k_router_topk_w32 (src/gpu/parts/40_model.inc:4011-4017,
  * src/gpu/parts/20_kernels_gemv.inc:1495-1562); arithmetic of src/ref.cpp:574-588.
  * Order: descending probability, ties to the lowest expert id. */

@@ -98,6 +98,16 @@ def router_topk(logits, k, stride=16, want_probs=False):
     return (ids, w, probs) if want_probs else (ids, w)
 
 
+def router_logits(router_w_bits, x_f32):
+    """logits[T][E] of the reference's router matvec (bf16 weight bits [E][d], fp32 activations)."""
+    E, d = router_w_bits.shape
+    T = x_f32.shape[0]
+    out = np.zeros((T, E), np.float32)
+    orc().orc_router_logits(_p(np.ascontiguousarray(router_w_bits, np.uint16)),
+                            _p(np.ascontiguousarray(x_f32, np.float32)), T, E, d, _p(out))
+    return out
+
+
 def count_topk_ties(probs, k):
     T, E = probs.shape
     return orc().orc_count_topk_ties(_p(np.ascontiguousarray(probs, np.float32)), T, E, k)

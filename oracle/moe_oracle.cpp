@@ -267,6 +267,21 @@ int orc_tiles(const int32_t* eoff, int E, int cap, int32_t* tiles /* [n][3] */) 
 }
 
 // Whole layer, token by token. x is fp32 [T][d] (callers pass bf16-valued floats).
+// Router logits from hidden states: y = W x with W bf16 [E][d], products and sum in double in
+// index order, rounded to float once (matvec, src/ref.cpp:68-77; called at src/ref.cpp:565-567).
+extern "C" void orc_router_logits(const uint16_t* router_w, const float* x, int T, int E, int d, float* logits) {
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; t++) {
+    const float* xt = x + (size_t)t * d;
+    for (int e = 0; e < E; e++) {
+      const uint16_t* wr = router_w + (size_t)e * d;
+      double a = 0;
+      for (int c = 0; c < d; c++) a += (double)bf16_bits_to_float(wr[c]) * xt[c];
+      logits[(size_t)t * E + e] = (float)a;
+    }
+  }
+}
+
 // logits: fp32 [T][E] or null (then router_w must be set and logits = float(sum_double)).
 // ids_out / w_out (optional) receive the selection, rows of 16 entries.
 int orc_moe_forward(const OrcLayer* L, const float* x, const float* logits, int T, float* y,

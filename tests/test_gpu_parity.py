@@ -303,6 +303,30 @@ def test_host_path_pipelined_ranges(cuda, T):
         assert np.array_equal(bits(synth.bf16_bits_to_f32(out_h)), bits(y))
 
 
+def test_flag_wait_is_bounded(cuda):
+    """The device-side wait of the copy-engine transport: flags that have reached the sequence
+    number let the stream continue at once; a flag that nothing sets makes the wait give up
+    after its limit (2 s) with a status the host reads -- the context stays usable."""
+    import time
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=128, mid=64)
+    op = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, 4)
+    flags = torch.full((32,), 7, dtype=torch.int32, device="cuda")
+    op.ep_wait_flags(flags, 8, 7)
+    op.ep_wait_flags(flags, 8, 5)       # a sender may be ahead
+    op.synchronize()
+    flags[3] = 6                        # source 3 has not arrived
+    t0 = time.time()
+    op.ep_wait_flags(flags, 8, 7)
+    with pytest.raises(pkg.B200MoeError) as e:
+        op.synchronize()
+    assert e.value.status == 5          # B200MOE_ERR_DEVICE_TIMEOUT
+    assert 1.5 < time.time() - t0 < 10.0
+    op.ep_wait_flags(flags, 3, 7)       # the handle and the stream still work
+    op.synchronize()
+    assert int((flags + 1).sum().item()) == 32 * 8 - 1
+
+
 def test_errors_are_status_codes(cuda):
     torch = cuda
     spec = synth.LayerSpec(experts=8, topk=2, d=128, mid=64)
