@@ -458,6 +458,23 @@ def main():
 
     if op_dec is not None:
         result["decode"] = decode_leg(torch, op_dec, peak_hbm, stream)
+    if world == 1 and not gguf:
+        # the step in front of the path: router logits from hidden states (random router weight)
+        gw = torch.Generator(device="cuda")
+        gw.manual_seed(77)
+        op.load_router(0, (torch.randn(E, D, device="cuda", generator=gw) * 0.02).to(torch.bfloat16))
+        lg2 = torch.empty(T, E, dtype=torch.float32, device="cuda")
+        for _ in range(3):
+            op.router_logits(0, x, lg2, stream=stream)
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record(stream)
+        for _ in range(10):
+            op.router_logits(0, x, lg2, stream=stream)
+        r1.record(stream)
+        op.synchronize(stream)
+        rms = r0.elapsed_time(r1) / 10
+        result["router_from_hidden"] = {"ms": rms, "tflops": 2.0 * T * E * D / (rms * 1e-3) / 1e12,
+                                        "what": "b200moe_router_logits: bf16 tcgen05 GEMM + near-tie recomputation in the reference's arithmetic; not part of `value`"}
     if want_cpu:
         cores = os.cpu_count() or 1
         n_tok = max(cores, 8) * 4
