@@ -42,6 +42,9 @@ SYMBOLS = {
     "b200moe_forward_host": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
     "b200moe_load_router": (_I, [_P, _I, _P]),
+    "b200moe_get_config": (_I, [_P, _P]),
+    "b200moe_load_hgn_file": (_I, [_P, _I, ctypes.c_char_p, _I]),
+    "b200moe_load_gguf_file": (_I, [_P, _I, ctypes.c_char_p, _I]),
     "b200moe_router_logits": (_I, [_P, _I, _P, _I, _P, _P]),
     "b200moe_forward_hidden": (_I, [_P, _I, _P, _I, _P, _P]),
     "b200moe_route": (_I, [_P, _P, _P, _I, _I, _P]),
@@ -153,6 +156,14 @@ class MoeOperator:
     def load_gguf(self, layer, gate, up, down, type_gu=GGML_Q4_K, type_dn=GGML_Q5_1):
         self._check(lib().b200moe_load_gguf(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),
                                             type_gu, type_dn))
+
+    def load_hgn_file(self, layer, path, model_layer=0):
+        """Expert (+ shared expert, router) tensors of layers.<model_layer> from an .hgn file."""
+        self._check(lib().b200moe_load_hgn_file(self._h, layer, os.fsencode(path), model_layer))
+
+    def load_gguf_file(self, layer, path, model_layer=0):
+        """blk.<model_layer>.ffn_{gate,up,down}_exps.weight from a GGUF file or shard set."""
+        self._check(lib().b200moe_load_gguf_file(self._h, layer, os.fsencode(path), model_layer))
 
     def load_router(self, layer, gate_weight_bf16):
         """layers.L.mlp.gate.weight, bf16 [experts][d_model] (tensor or numpy uint16 bits)."""

@@ -619,6 +619,12 @@ int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
                       h->prof, logits_dev);
 }
 
+int b200moe_get_config(b200moe_handle h, b200moe_config* out) {
+  if (!h || !out) return B200MOE_ERR_BAD_ARG;
+  *out = h->cfg;
+  return B200MOE_OK;
+}
+
 int b200moe_load_router(b200moe_handle h, int layer, const void* gate_weight_bf16) {
   if (int s = check_layer(h, layer)) return s;
   if (!gate_weight_bf16) return fail(h, B200MOE_ERR_BAD_ARG, "load_router: null pointer");

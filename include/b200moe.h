@@ -116,6 +116,23 @@ int b200moe_forward_routed(b200moe_handle h, int layer, const void* x_bf16_dev, 
 int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, int T,
                          const float* logits_host, void* out_bf16_host, void* stream);
 
+/* The configuration the handle was created with. */
+int b200moe_get_config(b200moe_handle h, b200moe_config* out);
+
+/* Expert tensors of one layer straight from a model file (mapped read-only for the duration of
+ * the call). `model_layer` is the layer number inside the file; `layer` the handle's slot.
+ *   load_hgn_file:  the engine's own container (Checkpoint::map_file, src/hgn.h:48-62, 295-363):
+ *                   layers.L.mlp.experts.{gate_up_proj,down_proj}.weight (dtype 5, q4cp), with
+ *                   has_shared also layers.L.mlp.shared_expert.* and shared_expert_gate.weight,
+ *                   and the router weight layers.L.mlp.gate.weight when present (src/ref.cpp:566-633).
+ *   load_gguf_file: GGUF v2/v3 (src/gguf.h:1-11, 136-314), sharded or not (pass any shard of
+ *                   NAME-0000i-of-0000n.gguf): blk.L.ffn_{gate,up,down}_exps.weight, ne = [K, N, E]
+ *                   (src/gpu/parts/30_host_util.inc:384-412), Q4_K gate/up and Q5_1 down.
+ * B200MOE_ERR_BAD_ARG: file missing, malformed or without the tensors; B200MOE_ERR_UNSUPPORTED:
+ * shapes or types that do not match the handle. */
+int b200moe_load_hgn_file(b200moe_handle h, int layer, const char* path, int model_layer);
+int b200moe_load_gguf_file(b200moe_handle h, int layer, const char* path, int model_layer);
+
 /* Router logits from hidden states. Replaces the engine's router GEMM in front of moe_b
  * (gemm(gate_weight(l), d_xb, d_routerb, P), src/gpu/parts/40_model.inc:4022-4025) and follows the
  * CPU reference (matvec over layers.L.mlp.gate.weight, src/ref.cpp:68-77, 565-567: double

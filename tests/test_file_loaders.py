@@ -1,0 +1,120 @@
+"""Loading the expert tensors from model files: synthetic .hgn and (sharded) GGUF files written
+here in the layouts the reference reads (src/hgn.h:48-62, 295-363; src/gguf.h:1-11, 136-314)
+give the same bytes out as loading the same tensors from memory."""
+import struct
+
+import numpy as np
+import pytest
+
+import gfx1151_engine_b200 as pkg
+from gfx1151_engine_b200 import synth
+
+from test_gpu_parity import bf16_out_to_f32, bits, make_op, run_layer
+
+
+def write_hgn(path, tensors):
+    """tensors: list of (name, dtype, dims, bytes)."""
+    hdr, rec = 104, 160
+    data_off = hdr + rec * len(tensors)
+    blobs, records, off = [], [], data_off
+    for name, dtype, dims, raw in tensors:
+        raw = bytes(raw)
+        pad = (-off) % 64
+        off += pad
+        blobs.append(b"\0" * pad + raw)
+        d4 = list(dims) + [0] * (4 - len(dims))
+        records.append(struct.pack("<96sII4QQQQ", name.encode(), dtype, len(dims), *d4, off, len(raw), 0))
+        off += len(raw)
+    header = struct.pack("<4sIIIQQQ64s", b"HGN1", 1, len(tensors), 0, hdr, data_off, off, b"synthetic")
+    with open(path, "wb") as f:
+        f.write(header + b"".join(records) + b"".join(blobs))
+
+
+def gguf_str(s):
+    return struct.pack("<Q", len(s)) + s.encode()
+
+
+def write_gguf(path, tensors, alignment=32, extra_kv=True):
+    """tensors: list of (name, ne, ggml_type, bytes)."""
+    kv = [gguf_str("general.architecture") + struct.pack("<I", 8) + gguf_str("synthetic"),
+          gguf_str("general.alignment") + struct.pack("<II", 4, alignment)]
+    if extra_kv:   # an array of strings and an array of floats in front of the tensor infos
+        kv.append(gguf_str("tokenizer.tokens") + struct.pack("<IIQ", 9, 8, 3) + b"".join(gguf_str(t) for t in ("a", "bc", "")))
+        kv.append(gguf_str("x.scores") + struct.pack("<IIQ", 9, 6, 2) + struct.pack("<2f", 1.0, 2.0))
+    infos, blobs, off = [], [], 0
+    for name, ne, typ, raw in tensors:
+        raw = bytes(raw)
+        pad = (-off) % alignment
+        off += pad
+        blobs.append(b"\0" * pad + raw)
+        infos.append(gguf_str(name) + struct.pack("<I", len(ne)) + struct.pack("<%dQ" % len(ne), *ne) + struct.pack("<IQ", typ, off))
+        off += len(raw)
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(kv)) + b"".join(kv) + b"".join(infos)
+    head += b"\0" * ((-len(head)) % alignment)
+    with open(path, "wb") as f:
+        f.write(head + b"".join(blobs))
+
+
+@pytest.mark.gpu
+def test_hgn_file_with_shared_expert_and_router(cuda, tmp_path):
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=64, shared=True, router=True, book="random")
+    layer = synth.make_layer(spec, seed=21)
+    E, d, mid = spec.experts, spec.d, spec.mid
+    path = str(tmp_path / "model.hgn")
+    write_hgn(path, [
+        ("tok_embeddings.weight", 0, (4, d), np.zeros(4 * d, np.uint16).tobytes()),
+        ("layers.3.mlp.gate.weight", 0, (E, d), layer["router_w"].tobytes()),
+        ("layers.3.mlp.experts.gate_up_proj.weight", 5, (E * 2 * mid, d), layer["gate_up"].tobytes()),
+        ("layers.3.mlp.experts.down_proj.weight", 5, (E * d, mid), layer["down"].tobytes()),
+        ("layers.3.mlp.shared_expert.gate_proj.weight", 5, (mid, d), layer["sh_gate"].tobytes()),
+        ("layers.3.mlp.shared_expert.up_proj.weight", 5, (mid, d), layer["sh_up"].tobytes()),
+        ("layers.3.mlp.shared_expert.down_proj.weight", 5, (d, mid), layer["sh_down"].tobytes()),
+        ("layers.3.mlp.shared_expert_gate.weight", 0, (1, d), layer["sh_gate_w"].tobytes()),
+    ])
+    T = 40
+    xb = synth.make_x(synth.rng_for(21, 9), T, d)
+    logits = synth.make_logits(synth.rng_for(21, 1), T, E)
+    y_mem = run_layer(torch, make_op(torch, spec, T, layer=layer), spec, xb, logits)
+    op = make_op(torch, spec, T)
+    op.load_hgn_file(0, path, model_layer=3)
+    assert np.array_equal(bits(run_layer(torch, op, spec, xb, logits)), bits(y_mem))
+    # the router weight came along: forward from hidden states works
+    x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16).reshape(T, d)
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    op.moe_hidden(0, x, out)
+    op.synchronize()
+    assert np.isfinite(bf16_out_to_f32(torch, out)).all()
+    with pytest.raises(pkg.B200MoeError):
+        op.load_hgn_file(0, path, model_layer=4)            # no such layer in the file
+    with pytest.raises(pkg.B200MoeError):
+        op.load_hgn_file(0, str(tmp_path / "missing.hgn"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sharded", [False, True])
+def test_gguf_file(cuda, tmp_path, sharded):
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=128, fmt="gguf")
+    layer = synth.make_layer(spec, seed=22)
+    E, d, mid = spec.experts, spec.d, spec.mid
+    t_gate = ("blk.1.ffn_gate_exps.weight", (d, mid, E), 12, layer["gate"].tobytes())
+    t_up = ("blk.1.ffn_up_exps.weight", (d, mid, E), 12, layer["up"].tobytes())
+    t_down = ("blk.1.ffn_down_exps.weight", (mid, d, E), 7, layer["down"].tobytes())
+    t_other = ("blk.1.attn_norm.weight", (d,), 0, np.ones(d, np.float32).tobytes())
+    if sharded:
+        write_gguf(str(tmp_path / "m-00001-of-00002.gguf"), [t_other, t_gate])
+        write_gguf(str(tmp_path / "m-00002-of-00002.gguf"), [t_down, t_up], alignment=64, extra_kv=False)
+        path = str(tmp_path / "m-00002-of-00002.gguf")
+    else:
+        write_gguf(str(tmp_path / "m.gguf"), [t_other, t_gate, t_up, t_down])
+        path = str(tmp_path / "m.gguf")
+    T = 40
+    xb = synth.make_x(synth.rng_for(22, 9), T, d)
+    logits = synth.make_logits(synth.rng_for(22, 1), T, E)
+    y_mem = run_layer(torch, make_op(torch, spec, T, layer=layer), spec, xb, logits)
+    op = make_op(torch, spec, T)
+    op.load_gguf_file(0, path, model_layer=1)
+    assert np.array_equal(bits(run_layer(torch, op, spec, xb, logits)), bits(y_mem))
+    with pytest.raises(pkg.B200MoeError):
+        op.load_gguf_file(0, path, model_layer=0)
