@@ -453,7 +453,7 @@ def main():
                      "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                      "peak_kind": peak_kind + " dense 16-bit burst",
                      "traffic": 4.98e9 if (world == 1 and (E, T) == (512, T_CHUNK)) else None,
-                     "traffic_note": "bytes per gate/up launch, scaled from an ncu capture of a reduced case by algorithmic bytes (see DESIGN.md)"},
+                     "traffic_note": "bytes per gate/up launch, scaled from an ncu capture of a reduced case by algorithmic bytes"},
     }
 
     if op_dec is not None:

@@ -1,7 +1,7 @@
 """Generates the golden vectors in this directory from the REFERENCE'S OWN CPU code.
 
 Run in a container where the reference tree is mounted:
-    make -C oracle REF_DIR=/root/reference && python tests/golden/make_golden.py
+    make -C oracle REF_DIR=<checkout of the reference> && python tests/golden/make_golden.py
 It calls oracle/_ref/libref.so, i.e. the unmodified Model::moe (src/ref.cpp:563-637),
 Checkpoint::q4cp_row (src/hgn.h:249-261) and gguf::dequant_row (src/gguf.h:339-443) of
 the reference, on seeded synthetic inputs, and stores the outputs together with CRC32
