@@ -57,6 +57,24 @@ def exchange_splits(eoff_all, rank, world):
     return send.tolist(), recv.tolist()
 
 
+def p2p_plan(eoff_all, rank, world):
+    """Copy lists of the copy-engine transport from every rank's expert offset table.
+
+    Returns (dispatch, back, recv_rows): dispatch = [(peer, src_row, dst_row, n)] copies of this
+    rank's send rows into the peers' receive buffers (a receive buffer holds the sources' rows in
+    rank order, exactly as all_to_all_single would leave them); back = [(peer, src_row, dst_row,
+    n)] copies of this rank's result rows into the peers' result buffers (which are in the
+    peers' own send order); recv_rows = rows this rank receives."""
+    eo = np.asarray(eoff_all).reshape(world, -1)
+    per = (eo.shape[1] - 1) // world
+    bd = eo[:, ::per].astype(np.int64)          # [source][dest] row offsets in the source's send buffer
+    cnt = bd[:, 1:] - bd[:, :-1]                # rows source s sends to dest p
+    order = [(rank + i) % world for i in range(1, world + 1)]   # peers first, myself last
+    dispatch = [(p, int(bd[rank, p]), int(cnt[:rank, p].sum()), int(cnt[rank, p])) for p in order]
+    back = [(s, int(cnt[:s, rank].sum()), int(bd[s, rank]), int(cnt[s, rank])) for s in order]
+    return dispatch, back, int(cnt[:, rank].sum())
+
+
 class ExpertParallelMoe:
     """The MoE layer sharded by expert over the ranks of a torch.distributed group.
 
@@ -144,7 +162,6 @@ class ExpertParallelMoe:
         main = torch.cuda.current_stream()
         C = min(self.chunks, (T + self.tc - 1) // self.tc)
         span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
-        per = self.E // self.world
         self.seq += 1
         if self.seq >= (1 << 16):
             raise RuntimeError("sequence numbers of the copy-engine transport exhausted")
@@ -155,36 +172,28 @@ class ExpertParallelMoe:
             dist.all_gather_into_tensor(B["eoff_all"], B["eoff"], group=self.group)
         routed = torch.cuda.Event()
         routed.record(main)
-        bounds, rows = [], 0
+        plans, rows = [], 0
         for c in range(C):
-            eo = self.buf[c]["eoff_all"].cpu().numpy().reshape(self.world, -1)
-            bd = eo[:, ::per].astype(np.int64)           # [source rank][dest rank] row offsets in the source's send buffer
-            cnt = bd[:, 1:] - bd[:, :-1]                 # rows source s sends to dest p
-            if cnt[:, self.rank].sum() > self.buf[c]["cap"]:
+            plan = p2p_plan(self.buf[c]["eoff_all"].cpu().numpy(), self.rank, self.world)
+            if plan[2] > self.buf[c]["cap"]:
                 raise RuntimeError("expert-parallel receive buffer too small: %d rows > capacity %d"
-                                   % (cnt[:, self.rank].sum(), self.buf[c]["cap"]))
-            bounds.append((bd, cnt))
-            rows += int(cnt[:, self.rank].sum())
+                                   % (plan[2], self.buf[c]["cap"]))
+            plans.append(plan)
+            rows += plan[2]
         self.last_recv_rows = rows
-        order = [(self.rank + i) % self.world for i in range(1, self.world + 1)]   # peers first, myself last
         # 1. dispatch: my rows for rank p go behind the rows of the ranks before me in p's buffer.
         #    (p has finished reading that buffer: I waited for p's results of the previous
         #    forward, which p sent after its GEMMs.)
         self.comm.wait_event(routed)
         with torch.cuda.stream(self.comm):
             for c in range(C):
-                bd, cnt = bounds[c]
                 B = self.buf[c]
-                for p in order:
-                    n = int(cnt[self.rank, p])
+                for p, src0, dst0, n in plans[c][0]:
                     if n:
-                        dst0 = int(cnt[:self.rank, p].sum())
-                        src0 = int(bd[self.rank, p])
                         B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
                     B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
         # 2. experts per chunk once its rows have arrived; results go straight back to their owners
         for c in range(C):
-            bd, cnt = bounds[c]
             B = self.buf[c]
             self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
             self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
@@ -192,11 +201,8 @@ class ExpertParallelMoe:
             done.record(main)
             self.comm2.wait_event(done)
             with torch.cuda.stream(self.comm2):
-                for s in order:
-                    n = int(cnt[s, self.rank])
+                for s, src0, dst0, n in plans[c][1]:
                     if n:
-                        src0 = int(cnt[:s, self.rank].sum())
-                        dst0 = int(bd[s, self.rank])
                         B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
                     B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
         # 3. combine

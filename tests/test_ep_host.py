@@ -59,3 +59,43 @@ def test_gloo_two_ranks_exchange_round_trip():
     outs = [p.communicate(timeout=180)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and "EXCHANGE OK" in o, "rank %d failed:\n%s" % (r, o)
+
+
+def test_p2p_plan_moves_every_row_there_and_back():
+    """The copy lists of the copy-engine transport: applying every rank's dispatch copies leaves
+    each receive buffer exactly as the all-to-all would (sources in rank order, experts ascending
+    inside a source), and the return copies bring every row back to where it started."""
+    world, E, k = 3, 12, 2
+    rng = np.random.default_rng(5)
+    eoffs, sends = [], []
+    for r in range(world):
+        counts = rng.integers(0, 6, size=E)
+        counts[rng.integers(0, E)] = 0
+        eoff = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+        eoffs.append(eoff)
+        # a send row is labelled (source rank, row index, expert)
+        experts = np.repeat(np.arange(E), counts)
+        sends.append(np.stack([np.full(eoff[-1], r), np.arange(eoff[-1]), experts], axis=1))
+    eoff_all = np.stack(eoffs)
+    plans = [ep.p2p_plan(eoff_all, r, world) for r in range(world)]
+    recv = [np.full((plans[r][2], 3), -1) for r in range(world)]
+    for r in range(world):
+        assert sorted(p for p, _, _, _ in plans[r][0]) == list(range(world))
+        for p, src0, dst0, n in plans[r][0]:
+            recv[p][dst0:dst0 + n] = sends[r][src0:src0 + n]
+    per = E // world
+    for r in range(world):
+        send_splits, recv_splits = ep.exchange_splits(eoff_all, r, world)
+        assert sum(recv_splits) == plans[r][2] and (recv[r] >= 0).all()
+        # sources in rank order, every row an expert of this rank, experts ascending per source
+        assert np.array_equal(recv[r][:, 0], np.repeat(np.arange(world), recv_splits))
+        assert ((recv[r][:, 2] // per) == r).all()
+        for s in range(world):
+            seg = recv[r][recv[r][:, 0] == s]
+            assert (np.diff(seg[:, 2]) >= 0).all() and (np.diff(seg[:, 1]) == 1).all()
+    back = [np.full((len(sends[r]), 3), -1) for r in range(world)]
+    for r in range(world):
+        for s, src0, dst0, n in plans[r][1]:
+            back[s][dst0:dst0 + n] = recv[r][src0:src0 + n]
+    for r in range(world):
+        assert np.array_equal(back[r], sends[r])
