@@ -108,25 +108,37 @@ k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
 
 // x_sorted[row][:] = fp16(x[tokidx[row]][:]); bf16 -> fp16 is exact for 2^-14 <= |v| < 65520,
 // larger magnitudes saturate to the largest finite half.
+// One warp per row: the token index is read once, a lane keeps four 16-byte loads in flight.
 __global__ void __launch_bounds__(256)
 k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx, int rows, int d,
              __half* __restrict__ xs) {
-  const int per_row = d / 8;
-  const long long total = (long long)rows * per_row;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / per_row), c = (int)(i % per_row) * 8;
-    const uint4 u = *(const uint4*)(x + (size_t)tokidx[row] * d + c);
-    const uint16_t* b = (const uint16_t*)&u;
-    uint4 o;
-    __half2* oh = (__half2*)&o;
+  const int lane = threadIdx.x & 31;
+  const int n_warps = gridDim.x * (blockDim.x >> 5);
+  const int per_row = d / 8;  // 16-byte pieces
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += n_warps) {
+    const uint4* src = (const uint4*)(x + (size_t)tokidx[row] * d);
+    uint4* dst = (uint4*)(xs + (size_t)row * d);
+    for (int v0 = lane; v0 < per_row; v0 += 128) {
+      uint4 u[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      float f0 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j]), -65504.f), 65504.f);
-      float f1 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j + 1]), -65504.f), 65504.f);
-      oh[j] = __floats2half2_rn(f0, f1);
+      for (int i = 0; i < 4; i++)
+        if (v0 + 32 * i < per_row) u[i] = src[v0 + 32 * i];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        if (v0 + 32 * i < per_row) {
+          const uint16_t* b = (const uint16_t*)&u[i];
+          uint4 o;
+          __half2* oh = (__half2*)&o;
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const float f0 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j]), -65504.f), 65504.f);
+            const float f1 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j + 1]), -65504.f), 65504.f);
+            oh[j] = __floats2half2_rn(f0, f1);
+          }
+          dst[v0 + 32 * i] = o;
+        }
+      }
     }
-    *(uint4*)(xs + (size_t)row * d + c) = o;
   }
 }
 
@@ -151,9 +163,8 @@ cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32
 
 cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
                               __half* x_sorted, cudaStream_t st) {
-  long long total = (long long)rows * (d / 8);
-  int blocks = (int)((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  int blocks = (rows + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   k_gather_f16<<<blocks, 256, 0, st>>>((const uint16_t*)x_bf16, tokidx, rows, d, x_sorted);
   return cudaGetLastError();
