@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200moe.so")
 
 GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
-GGML_Q5_1, GGML_Q4_K = 7, 12
+GGML_Q5_1, GGML_Q4_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 20, 23
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
           5: "device timeout", 6: "NCCL error", 7: "out of memory", 8: "too large for the static scratch"}

@@ -355,53 +355,77 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
   return B200MOE_OK;
 }
 
+// Image format, bytes per row of K elements and K granule of a GGUF block type; fmt < 0: not read.
+static void gguf_type_info(int type, bool down, size_t K, int* fmt, size_t* row_bytes, size_t* granule) {
+  *fmt = -1;
+  *row_bytes = 0;
+  *granule = 256;
+  if (type == B200MOE_GGML_Q4_K && !down) *fmt = kQ4K, *row_bytes = K / 256 * 144;
+  else if (type == B200MOE_GGML_Q5_1 && down) *fmt = kQ51, *row_bytes = K / 32 * 24, *granule = 32;
+  else if (type == B200MOE_GGML_IQ4_NL) *fmt = kQ4CP, *row_bytes = K / 32 * 18, *granule = 32;
+  else if (type == B200MOE_GGML_IQ4_XS) *fmt = kQ4CP, *row_bytes = K / 256 * 136;
+}
+
+// Code book of an image made from GGUF blocks: IQ4 = the non-linear grid / 256 (the image's
+// scales carry the factor 256), Q4_K / Q5_1 = the code itself (scale and offset applied after).
+static void gguf_book(int type, float* book32) {
+  static const int8_t grid[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+  const bool iq = type == B200MOE_GGML_IQ4_NL || type == B200MOE_GGML_IQ4_XS;
+  for (int i = 0; i < 32; i++) book32[i] = iq ? (float)grid[i & 15] * (1.f / 256.f) : (float)(i & 15);
+}
+
 int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
                       const void* down_src, int type_gu, int type_dn) {
   if (int s = check_layer(h, layer)) return s;
   if (!gate_src || !up_src || !down_src) return fail(h, B200MOE_ERR_BAD_ARG, "null weight pointer");
-  if (type_gu != B200MOE_GGML_Q4_K || type_dn != B200MOE_GGML_Q5_1)
-    return fail(h, B200MOE_ERR_UNSUPPORTED, "GGUF experts: gate/up must be Q4_K and down Q5_1");
   const b200moe_config& c = h->cfg;
   const size_t E = c.experts, d = c.d_model, mid = c.d_mid;
-  if (d % 256 != 0) return fail(h, B200MOE_ERR_UNSUPPORTED, "Q4_K needs d_model % 256 == 0");
+  int fmt_gu, fmt_dn;
+  size_t rb_gu, rb_dn, gr_gu, gr_dn;
+  gguf_type_info(type_gu, false, d, &fmt_gu, &rb_gu, &gr_gu);
+  gguf_type_info(type_dn, true, mid, &fmt_dn, &rb_dn, &gr_dn);
+  if (fmt_gu < 0 || fmt_dn < 0)
+    return fail(h, B200MOE_ERR_UNSUPPORTED,
+                "GGUF experts: gate/up must be Q4_K, IQ4_NL or IQ4_XS and down Q5_1, IQ4_NL or IQ4_XS");
+  if (d % gr_gu != 0 || mid % gr_dn != 0)
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "GGUF experts: row length is not a whole number of blocks");
   CU_TRY(h, cudaSetDevice(c.device));
   LayerWeights& L = h->layers[layer];
   free_image(L.gu);
   free_image(L.dn);
   L.loaded = false;
-  const size_t gu_bytes = E * mid * (d / 256 * 144), dn_bytes = E * d * (mid / 32 * 24);
+  const size_t gu_bytes = E * mid * rb_gu, dn_bytes = E * d * rb_dn;
   std::vector<void*> tmp;
   const uint8_t *g = nullptr, *u = nullptr, *dn = nullptr;
   const int nl = local_experts(c), e0 = first_expert(c);
   cudaError_t e = stage(gate_src, gu_bytes, &g, tmp);
   if (e == cudaSuccess) e = stage(up_src, gu_bytes, &u, tmp);
-  if (e == cudaSuccess) e = alloc_image(L.gu, kQ4K, nl, (int)mid, (int)d, 1);
+  if (e == cudaSuccess) e = alloc_image(L.gu, fmt_gu, nl, (int)mid, (int)d, 1);
   if (e == cudaSuccess) {
     SrcTensor sg, su;
     sg.codes = g;
     sg.rows_per_expert = mid;
     su.codes = u;
     su.rows_per_expert = mid;
-    e = launch_repack(L.gu, sg, su, (int)d, e0, 0);
+    e = launch_repack(L.gu, sg, su, (int)d, e0, 0, h->source_of_placed_dev, type_gu);
     h->launches++;
   }
-  // the tensor-core path decodes a code byte through the same pair table as q4cp: for the
-  // GGUF formats the "book" is the code itself (0..15), scale and offset are applied after
-  float ident[32];
-  for (int i = 0; i < 32; i++) ident[i] = (float)(i & 15);
-  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, ident, sizeof ident, cudaMemcpyHostToDevice);
+  float book[32];
+  gguf_book(type_gu, book);
+  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, book, sizeof book, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   free_all(tmp);
   if (e == cudaSuccess) e = stage(down_src, dn_bytes, &dn, tmp);
-  if (e == cudaSuccess) e = alloc_image(L.dn, kQ51, nl, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) e = alloc_image(L.dn, fmt_dn, nl, (int)d, (int)mid, 0);
   if (e == cudaSuccess) {
     SrcTensor a;
     a.codes = dn;
     a.rows_per_expert = d;
-    e = launch_repack(L.dn, a, a, (int)mid, e0, 0);
+    e = launch_repack(L.dn, a, a, (int)mid, e0, 0, h->source_of_placed_dev, type_dn);
     h->launches++;
   }
-  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, ident, sizeof ident, cudaMemcpyHostToDevice);
+  gguf_book(type_dn, book);
+  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, book, sizeof book, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   free_all(tmp);
   if (e != cudaSuccess) {

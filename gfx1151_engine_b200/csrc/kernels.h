@@ -49,9 +49,11 @@ struct SrcTensor {
 
 // ---- repack.cu ----
 // expert_map (device, may be null): source expert of image expert i is expert_map[first_expert + i]
-// (placement for expert parallelism), else first_expert + i.
+// (placement for expert parallelism), else first_expert + i. gguf_type 20 / 23: the source is
+// GGUF IQ4_NL / IQ4_XS blocks and the image is q4cp (scale = fp16(256 * block scale)).
 cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
-                          int first_expert, cudaStream_t st, const int32_t* expert_map = nullptr);
+                          int first_expert, cudaStream_t st, const int32_t* expert_map = nullptr,
+                          int gguf_type = 0);
 cudaError_t launch_dequant_rows(const Image& img, int expert, int row0, int nrows, int mid_rows,
                                 float* out, cudaStream_t st);
 

@@ -1,5 +1,5 @@
 // repack.cu -- one-time conversion of the reference's expert tensor layouts (hgn q4cp,
-// GGUF Q4_K, GGUF Q5_1) into the tiled image described in common.cuh, and the inverse
+// GGUF Q4_K, Q5_1, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
 // check: dequantising rows of the image bit-identically to the reference's row
 // dequantisers (q4cp_row, src/hgn.h:249-261; dequant_row, src/gguf.h:360-374, 408-441).
 #include "kernels.h"
@@ -137,6 +137,58 @@ __global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int fir
   }
 }
 
+// GGUF IQ4_NL / IQ4_XS -> the q4cp image: one thread per (tile, row, half). Both formats are
+// "grid value x one scale per 32 elements" (src/gguf.h:375-406), which is what a q4cp tile
+// holds; element j of a block is the low nibble of qs[j], element j+16 the high nibble. The
+// image carries fp16(d * 256 [* (ls - 32)]) as the group's scale and the handle's code book is
+// grid / 256 -- the reference's GPU kernel makes the same exact rescale to keep the scales out
+// of the fp16 subnormal range (src/gpu/parts/27_kernels_moe_lut.inc:312-326).
+template <bool XS>
+__global__ void k_repack_iq4(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                             const int32_t* __restrict__ emap) {
+  const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 256;
+  const long long row_bytes = XS ? (long long)K / 256 * 136 : (long long)K / 32 * 18;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    int r = (int)(i & 127);
+    int h = (int)((i >> 7) & 1);
+    long long t = i >> 8;
+    int kb = (int)(t % img.n_kblocks);
+    long long t2 = t / img.n_kblocks;
+    int mt = (int)(t2 % img.n_mtiles);
+    int e = (int)(t2 / img.n_mtiles);
+    uint8_t* dst = const_cast<uint8_t*>(img.tile(e, mt, kb));
+    const SrcTensor* s;
+    long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
+    const int blk32 = kb * 2 + h;  // 32-element block of the row
+    const uint8_t* blk;
+    const uint8_t* qs;
+    float scale;
+    if (XS) {
+      blk = s->codes + row * row_bytes + (long long)(blk32 >> 3) * 136;
+      const int ib = blk32 & 7;
+      const uint32_t sh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8);
+      const int ls = (int)((blk[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15) | (int)(((sh >> (2 * ib)) & 3u) << 4);
+      scale = (float)(ls - 32);
+      qs = blk + 8 + 16 * ib;
+    } else {
+      blk = s->codes + row * row_bytes + (long long)blk32 * 18;
+      scale = 1.f;
+      qs = blk + 2;
+    }
+    const float d = half_bits_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    scale = __fmul_rn(__fmul_rn(d, 256.f), scale);
+    uint8_t out[16];
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      out[q] = (uint8_t)((qs[2 * q] & 15) | ((qs[2 * q + 1] & 15) << 4));
+      out[q + 8] = (uint8_t)((qs[2 * q] >> 4) | ((qs[2 * q + 1] >> 4) << 4));
+    }
+    *(uint4*)(dst + h * 2048 + r * 16) = *(uint4*)out;
+    ((__half*)(dst + kCodeBytes))[r * 2 + h] = __float2half_rn(scale);
+  }
+}
+
 // Rows of an expert, dequantised from the image with the reference's exact operation
 // order (single fp32 multiply for q4cp; multiply then add/subtract, never fused, for GGUF).
 __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int mid_rows,
@@ -191,10 +243,12 @@ __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int m
 }  // namespace
 
 cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
-                          int first_expert, cudaStream_t st, const int32_t* expert_map) {
+                          int first_expert, cudaStream_t st, const int32_t* expert_map, int gguf_type) {
   const int threads = 256;
   const int blocks = 148 * 8;
-  if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  if (img.fmt == kQ4CP && gguf_type == 20) k_repack_iq4<false><<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else if (img.fmt == kQ4CP && gguf_type == 23) k_repack_iq4<true><<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else if (img.fmt == kQ4K) k_repack_q4k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else k_repack_q51<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   return cudaGetLastError();

@@ -4,7 +4,7 @@ Stand-ins for real checkpoints, with the shapes and value distributions of the
 benchmark configurations:
   * hgn q4cp tensors (layout: src/hgn.h:5-9 of the reference): 16 x f32 code book, 4-bit
     codes uniform in [0,15], fp16 scales |N(0, 0.02)| per (row, 32 columns);
-  * GGUF Q4_K / Q5_1 blocks (layout: src/gguf.h:360-374, 408-441) with uniform codes and
+  * GGUF Q4_K / Q5_1 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
     block scales normalised so that dequantised magnitudes match the q4cp case;
   * bf16 activations ~ N(0,1), router logits ~ N(0,1) with an optional per-expert
     Zipf(1.1) bias under a seeded permutation of the expert ids.
@@ -100,6 +100,38 @@ def make_logits(rng, T, experts, zipf=False, zipf_rng=None, strength=1.0):
 def make_x(rng, T, d):
     """bf16 activations ~ N(0,1) as uint16 bit patterns."""
     return f32_to_bf16_bits(rng.normal(0.0, 1.0, size=(T, d)).astype(np.float32))
+def make_iq4nl(rng, nrows, k, sigma=0.02):
+    """nrows rows of GGUF IQ4_NL blocks (18 bytes per 32 elements: fp16 d, 16 code bytes;
+    src/gguf.h:375-387). |w| <= a with a = |N(0, sigma)| per block, as for the other formats."""
+    nb = nrows * (k // 32)
+    a = np.abs(rng.normal(0.0, sigma, size=nb))
+    blk = np.zeros((nb, 18), dtype=np.uint8)
+    blk[:, 0:2] = (a / 127.0).astype("<f2").view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(0, 256, size=(nb, 16), dtype=np.uint8)
+    return blk.reshape(-1)
+
+
+def make_iq4xs(rng, nrows, k, sigma=0.02):
+    """nrows rows of GGUF IQ4_XS blocks (136 bytes per 256 elements: fp16 d, u16 + 4 bytes of 6-bit
+    sub-block scales, 128 code bytes; src/gguf.h:388-406). d = a / (32 * 127) lands in the fp16
+    subnormal range, as in real files."""
+    nb = nrows * (k // 256)
+    a = np.abs(rng.normal(0.0, sigma, size=nb))
+    blk = np.zeros((nb, 136), dtype=np.uint8)
+    blk[:, 0:2] = (a / (32.0 * 127.0)).astype("<f2").view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(0, 256, size=(nb, 134), dtype=np.uint8)
+    return blk.reshape(-1)
+
+
+GGML_Q5_1, GGML_Q4_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 20, 23
+_GG_MAKERS = {GGML_Q5_1: make_q51, GGML_Q4_K: make_q4k, GGML_IQ4_NL: make_iq4nl, GGML_IQ4_XS: make_iq4xs}
+
+
+def gg_row_bytes(gtype, k):
+    """Bytes of one row of k elements in GGUF block type `gtype` (src/gguf.h:49-62)."""
+    per, nbytes = {GGML_Q5_1: (32, 24), GGML_Q4_K: (256, 144), GGML_IQ4_NL: (32, 18), GGML_IQ4_XS: (256, 136)}[gtype]
+    assert k % per == 0
+    return k // per * nbytes
 
 
 @dataclass
@@ -112,6 +144,8 @@ class LayerSpec:
     fmt: str = "q4cp"      # "q4cp" or "gguf"
     book: str = "linear"   # "linear" or "random" (q4cp only)
     router: bool = False   # also make a bf16 router weight [E][d]
+    gg_gu: int = 12        # GGUF block type of gate/up (fmt "gguf"): Q4_K 12, IQ4_NL 20, IQ4_XS 23
+    gg_dn: int = 7         # GGUF block type of down: Q5_1 7, IQ4_NL 20, IQ4_XS 23
 
 
 # The benchmark configurations (shapes only; see BASELINE.json `configs`).
@@ -129,9 +163,9 @@ def make_layer(spec, seed=0):
         out["gate_up"] = make_q4cp(rng_for(seed, 1), E * 2 * mid, d, spec.book)
         out["down"] = make_q4cp(rng_for(seed, 2), E * d, mid, spec.book)
     else:
-        out["gate"] = make_q4k(rng_for(seed, 1), E * mid, d)
-        out["up"] = make_q4k(rng_for(seed, 3), E * mid, d)
-        out["down"] = make_q51(rng_for(seed, 2), E * d, mid)
+        out["gate"] = _GG_MAKERS[spec.gg_gu](rng_for(seed, 1), E * mid, d)
+        out["up"] = _GG_MAKERS[spec.gg_gu](rng_for(seed, 3), E * mid, d)
+        out["down"] = _GG_MAKERS[spec.gg_dn](rng_for(seed, 2), E * d, mid)
     if spec.shared:
         out["sh_gate"] = make_q4cp(rng_for(seed, 4), mid, d, spec.book)
         out["sh_up"] = make_q4cp(rng_for(seed, 5), mid, d, spec.book)

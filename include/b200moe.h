@@ -41,7 +41,7 @@ enum {
 };
 
 /* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
-enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12 };
+enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12, B200MOE_GGML_IQ4_NL = 20, B200MOE_GGML_IQ4_XS = 23 };
 
 /* Which expert GEMM implementation forward uses for T > decode_max_tokens. */
 enum {
@@ -88,7 +88,11 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
 
 /* Replaces: gguf_experts_open / GgExperts (src/gpu/parts/30_host_util.inc:348-452): raw GGUF
  * blocks of blk.L.ffn_{gate,up,down}_exps.weight, expert e's rows at e*rows*row_bytes
- * (src/gguf.h:3-11). type_gu must be Q4_K and type_dn Q5_1. */
+ * (src/gguf.h:3-11). type_gu: Q4_K, IQ4_NL or IQ4_XS; type_dn: Q5_1, IQ4_NL or IQ4_XS (the
+ * types of moe_gg_up / moe_gg_down and of the table-decoded kernels,
+ * src/gpu/parts/27_kernels_moe_lut.inc:4-19, 659-671). The IQ4 types become the q4cp tile image:
+ * code book = grid / 256, group scale = fp16(256 * d [* (ls - 32)]), the exact rescale of
+ * 27_kernels_moe_lut.inc:312-326. */
 int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
                       const void* down_src, int type_gu, int type_dn);
 

@@ -136,7 +136,7 @@ def moe_forward(spec, layer, x_f32, logits=None, threads=0):
     L = OrcLayer()
     L.experts, L.topk, L.d, L.mid = spec.experts, spec.topk, spec.d, spec.mid
     L.format = 0 if spec.fmt == "q4cp" else 1
-    L.gg_type_gu, L.gg_type_dn = 12, 7
+    L.gg_type_gu, L.gg_type_dn = getattr(spec, "gg_gu", 12), getattr(spec, "gg_dn", 7)
     L.has_shared = int(spec.shared)
     keep = []
 

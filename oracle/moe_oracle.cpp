@@ -12,7 +12,8 @@
 // What each function follows in the reference (paths relative to the reference
 // project root):
 //   orc_q4cp_rows        src/hgn.h:219-261   (q4cp_parse / q4cp_row)
-//   orc_gguf_rows        src/gguf.h:328-336, 360-374, 408-441 (scale_min_k4, Q5_1, Q4_K)
+//   orc_gguf_rows        src/gguf.h:328-336, 360-374, 375-406, 408-441 (scale_min_k4, Q5_1,
+//                        IQ4_NL, IQ4_XS, Q4_K)
 //   orc_router_topk      src/ref.cpp:574-588 (softmax in double, partial_sort on probs)
 //   orc_route            src/gpu/parts/40_model.inc:4171-4193 (host bucketing) and
 //                        src/gpu/parts/10_ple_io.inc:790-811 (pairids rank rule)
@@ -82,11 +83,15 @@ inline void q4_row(const Q4View& v, uint64_t row, float* out) {
   }
 }
 
-enum { GG_Q5_1 = 7, GG_Q4_K = 12 };
+enum { GG_Q5_1 = 7, GG_Q4_K = 12, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
+
+inline bool gg_known(uint32_t t) { return t == GG_Q5_1 || t == GG_Q4_K || t == GG_IQ4_NL || t == GG_IQ4_XS; }
 
 inline uint64_t gg_row_bytes(uint32_t type, uint64_t k) {
   if (type == GG_Q4_K) return k / 256 * 144;
   if (type == GG_Q5_1) return k / 32 * 24;
+  if (type == GG_IQ4_NL) return k / 32 * 18;
+  if (type == GG_IQ4_XS) return k / 256 * 136;
   return 0;
 }
 
@@ -115,6 +120,40 @@ inline void gg_row(uint32_t type, const uint8_t* src, float* y, uint64_t k) {
         int c = (q[j] >> 4) | (int)(((hi >> (j + 16)) & 1u) << 4);
         y[b * 32 + j] = a * d + m;
         y[b * 32 + j + 16] = c * d + m;
+      }
+    }
+    return;
+  }
+  if (type == GG_IQ4_NL || type == GG_IQ4_XS) {
+    // the non-linear 4-bit grid shared by both formats (src/gguf.h:376-377, 389-390)
+    static const int8_t grid[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+    if (type == GG_IQ4_NL) {  // 18 bytes per 32: fp16 d, 16 code bytes (src/gguf.h:375-387)
+      for (uint64_t b = 0; b < k / 32; b++, src += 18) {
+        uint16_t dh;
+        memcpy(&dh, src, 2);
+        const float d = half_bits_to_float(dh);
+        for (int j = 0; j < 16; j++) {
+          y[b * 32 + j] = d * grid[src[2 + j] & 15];
+          y[b * 32 + j + 16] = d * grid[src[2 + j] >> 4];
+        }
+      }
+      return;
+    }
+    // IQ4_XS, 136 bytes per 256: fp16 d, u16 high scale bits, 4 bytes of low scale nibbles,
+    // 128 code bytes; sub-block scale = d * (6-bit value - 32) (src/gguf.h:388-406)
+    for (uint64_t b = 0; b < k / 256; b++, src += 136) {
+      uint16_t dh, sh;
+      memcpy(&dh, src, 2);
+      memcpy(&sh, src + 2, 2);
+      const float d = half_bits_to_float(dh);
+      for (int ib = 0; ib < 8; ib++) {
+        const int ls = ((src[4 + ib / 2] >> (4 * (ib % 2))) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+        const float dl = d * (float)(ls - 32);
+        const uint8_t* q = src + 8 + 16 * ib;
+        for (int j = 0; j < 16; j++) {
+          y[b * 256 + ib * 32 + j] = dl * grid[q[j] & 15];
+          y[b * 256 + ib * 32 + j + 16] = dl * grid[q[j] >> 4];
+        }
       }
     }
     return;
@@ -155,7 +194,7 @@ extern "C" {
 // Layer description handed over from Python (ctypes mirrors this struct field by field).
 struct OrcLayer {
   int32_t experts, topk, d, mid;
-  int32_t format;              // 0 = hgn q4cp, 1 = GGUF (Q4_K gate/up, Q5_1 down)
+  int32_t format;              // 0 = hgn q4cp, 1 = GGUF (block types in gg_type_gu / gg_type_dn)
   int32_t gg_type_gu, gg_type_dn;
   int32_t has_shared;
   const uint8_t* gate_up;      // q4cp: fused [E*2*mid, d] blob; GGUF: unused
@@ -176,7 +215,7 @@ void orc_q4cp_rows(const uint8_t* blob, uint64_t rows, uint64_t cols, uint64_t r
 }
 
 int orc_gguf_rows(uint32_t type, const uint8_t* src, uint64_t k, uint64_t n, float* out) {
-  if (type != GG_Q4_K && type != GG_Q5_1) return -1;
+  if (!gg_known(type) || gg_row_bytes(type, k) == 0) return -1;
   uint64_t rb = gg_row_bytes(type, k);
   for (uint64_t r = 0; r < n; r++) gg_row(type, src + r * rb, out + r * k, k);
   return 0;
@@ -288,7 +327,7 @@ int orc_moe_forward(const OrcLayer* L, const float* x, const float* logits, int 
                     int32_t* ids_out, float* w_out, int threads) {
   const int E = L->experts, k = L->topk, d = L->d, mid = L->mid;
   if (!logits && !L->router_w) return -1;
-  if (L->format == 1 && (L->gg_type_gu != GG_Q4_K || L->gg_type_dn != GG_Q5_1)) return -2;
+  if (L->format == 1 && (!gg_known((uint32_t)L->gg_type_gu) || !gg_known((uint32_t)L->gg_type_dn))) return -2;
 #ifdef _OPENMP
   if (threads > 0) omp_set_num_threads(threads);
 #endif

@@ -34,6 +34,14 @@ def layer_crc(layer):
     return crc(*[layer[k] for k in sorted(layer)])
 
 
+def gguf_iq4():
+    """GGUF IQ4_NL / IQ4_XS rows through the reference's dequant_row (src/gguf.h:375-406)."""
+    nl = synth.make_iq4nl(synth.rng_for(12, 3), 3, 256)
+    xs = synth.make_iq4xs(synth.rng_for(12, 4), 3, 512)
+    np.savez_compressed(os.path.join(OUT, "gguf_iq4_rows.npz"), iq4nl=nl, iq4nl_rows=oracle.gguf_rows(20, nl, 256, 3, use_ref=True),
+                        iq4xs=xs, iq4xs_rows=oracle.gguf_rows(23, xs, 512, 3, use_ref=True))
+
+
 def main():
     assert oracle.have_ref(), "build oracle/_ref/libref.so first (needs the reference tree)"
     # 1. q4cp rows, including a width whose scale record is padded (640 -> 40 B -> 48 B)
@@ -46,6 +54,7 @@ def main():
     q51 = synth.make_q51(synth.rng_for(12, 2), 3, 256)
     np.savez_compressed(os.path.join(OUT, "gguf_rows.npz"), q4k=q4k, q4k_rows=oracle.gguf_rows(12, q4k, 512, 3, use_ref=True),
                         q51=q51, q51_rows=oracle.gguf_rows(7, q51, 256, 3, use_ref=True))
+    gguf_iq4()
     # 3. tiny layer with shared expert and a random non-uniform code book
     spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=64, shared=True, router=True, book="random")
     layer = synth.make_layer(spec, seed=3)

@@ -92,15 +92,15 @@ def test_hgn_file_with_shared_expert_and_router(cuda, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("sharded", [False, True])
-def test_gguf_file(cuda, tmp_path, sharded):
+@pytest.mark.parametrize("sharded,gu,dn", [(False, 12, 7), (True, 12, 7), (False, 20, 23), (True, 23, 20)])
+def test_gguf_file(cuda, tmp_path, sharded, gu, dn):
     torch = cuda
-    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=128, fmt="gguf")
+    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=256, fmt="gguf", gg_gu=gu, gg_dn=dn)
     layer = synth.make_layer(spec, seed=22)
     E, d, mid = spec.experts, spec.d, spec.mid
-    t_gate = ("blk.1.ffn_gate_exps.weight", (d, mid, E), 12, layer["gate"].tobytes())
-    t_up = ("blk.1.ffn_up_exps.weight", (d, mid, E), 12, layer["up"].tobytes())
-    t_down = ("blk.1.ffn_down_exps.weight", (mid, d, E), 7, layer["down"].tobytes())
+    t_gate = ("blk.1.ffn_gate_exps.weight", (d, mid, E), gu, layer["gate"].tobytes())
+    t_up = ("blk.1.ffn_up_exps.weight", (d, mid, E), gu, layer["up"].tobytes())
+    t_down = ("blk.1.ffn_down_exps.weight", (mid, d, E), dn, layer["down"].tobytes())
     t_other = ("blk.1.attn_norm.weight", (d,), 0, np.ones(d, np.float32).tobytes())
     if sharded:
         write_gguf(str(tmp_path / "m-00001-of-00002.gguf"), [t_other, t_gate])

@@ -27,7 +27,7 @@ def make_op(torch, spec, max_tokens, impl=pkg.GEMM_AUTO, layer=None, **kw):
             op.load_q4cp(0, dev_bytes(torch, layer["gate_up"]), dev_bytes(torch, layer["down"]))
         else:
             op.load_gguf(0, dev_bytes(torch, layer["gate"]), dev_bytes(torch, layer["up"]),
-                         dev_bytes(torch, layer["down"]))
+                         dev_bytes(torch, layer["down"]), type_gu=spec.gg_gu, type_dn=spec.gg_dn)
         if spec.shared:
             op.load_shared_q4cp(0, dev_bytes(torch, layer["sh_gate"]), dev_bytes(torch, layer["sh_up"]),
                                 dev_bytes(torch, layer["sh_down"]), dev_bytes(torch, layer["sh_gate_w"]))
@@ -89,6 +89,37 @@ def test_dequant_gguf_bit_exact(cuda):
         rb = spec.mid // 32 * 24
         dn = oracle.gguf_rows(7, layer["down"][e * spec.d * rb:(e + 1) * spec.d * rb], spec.mid, spec.d)
         assert np.array_equal(bits(out.cpu().numpy()), bits(dn))
+
+
+@pytest.mark.parametrize("gtype", [synth.GGML_IQ4_NL, synth.GGML_IQ4_XS])
+def test_dequant_iq4(cuda, gtype):
+    """IQ4_NL / IQ4_XS experts are stored as the q4cp image (grid / 256, fp16(256 * block scale)).
+    IQ4_NL: the image dequantises bit-exactly to the reference's rows. IQ4_XS: the sub-block
+    scale d * (ls - 32) is rounded to fp16 as in the reference's GPU kernel, so rows agree to
+    2^-11 relative, and exactly wherever that product fits 11 bits."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=2, topk=1, d=512, mid=256, fmt="gguf", gg_gu=gtype, gg_dn=gtype)
+    layer = synth.make_layer(spec, seed=33)
+    op = make_op(torch, spec, 4, impl=pkg.GEMM_SIMT, layer=layer)
+    exact = 0
+    for e in range(spec.experts):
+        out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 0, e, 0, 2 * spec.mid, out)
+        rb = synth.gg_row_bytes(gtype, spec.d)
+        g = oracle.gguf_rows(gtype, layer["gate"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        u = oracle.gguf_rows(gtype, layer["up"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        out2 = torch.empty((spec.d, spec.mid), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 1, e, 0, spec.d, out2)
+        rb = synth.gg_row_bytes(gtype, spec.mid)
+        dn = oracle.gguf_rows(gtype, layer["down"][e * spec.d * rb:(e + 1) * spec.d * rb], spec.mid, spec.d)
+        for got, want in ((out.cpu().numpy(), np.concatenate([g, u])), (out2.cpu().numpy(), dn)):
+            if gtype == synth.GGML_IQ4_NL:
+                assert np.array_equal(bits(got), bits(want))
+            else:
+                assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -11)
+                exact += int(np.count_nonzero(bits(got) == bits(want)))
+    if gtype == synth.GGML_IQ4_XS:
+        assert exact > 0
 
 
 # ---------------------------------------------------------------- routing ----------------
@@ -261,6 +292,25 @@ def test_gguf_layer(cuda, impl):
         y = run_layer(torch, op, spec, xb, logits)
         max_abs, mean_rel = assert_output_close(y, y_o, "gguf T=%d impl %d" % (T, impl))
         print("gguf T=%d impl=%d max-abs %.2e mean-rel %.2e" % (T, impl, max_abs, mean_rel))
+
+
+@pytest.mark.parametrize("gu,dn,impl", [(20, 20, pkg.GEMM_AUTO), (23, 23, pkg.GEMM_AUTO), (12, 23, pkg.GEMM_AUTO),
+                                        (20, 7, pkg.GEMM_AUTO), (23, 20, pkg.GEMM_SIMT)])
+def test_iq4_layer(cuda, gu, dn, impl):
+    """GGUF experts in IQ4_NL (20) / IQ4_XS (23), alone and mixed with Q4_K (12) / Q5_1 (7): GEMV
+    (T=3), tensor-core (T=40, 300) and fp32 paths against the oracle, which dequantises the raw
+    blocks as the reference's dequant_row does."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=256, fmt="gguf", gg_gu=gu, gg_dn=dn)
+    layer = synth.make_layer(spec, seed=81)
+    for T in (3, 40, 300):
+        logits = synth.make_logits(synth.rng_for(81, T), T, spec.experts, zipf=T > 40)
+        xb = synth.make_x(synth.rng_for(81, 9), T, spec.d)
+        y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+        op = make_op(torch, spec, T, impl=impl, layer=layer)
+        y = run_layer(torch, op, spec, xb, logits)
+        max_abs, mean_rel = assert_output_close(y, y_o, "iq4 %d/%d T=%d impl %d" % (gu, dn, T, impl))
+        print("iq4 gu=%d dn=%d T=%d impl=%d max-abs %.2e mean-rel %.2e" % (gu, dn, T, impl, max_abs, mean_rel))
 
 
 def test_forward_routed_and_host_paths(cuda):

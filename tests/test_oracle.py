@@ -30,6 +30,16 @@ def test_gguf_rows_golden(golden_dir):
     assert np.array_equal(bits(oracle.gguf_rows(7, g["q51"], 256, 3)), bits(g["q51_rows"]))
 
 
+def test_gguf_iq4_rows_golden(golden_dir):
+    """IQ4_NL / IQ4_XS rows against the reference's dequant_row (src/gguf.h:375-406)."""
+    g = np.load(os.path.join(golden_dir, "gguf_iq4_rows.npz"))
+    assert np.array_equal(bits(oracle.gguf_rows(20, g["iq4nl"], 256, 3)), bits(g["iq4nl_rows"]))
+    assert np.array_equal(bits(oracle.gguf_rows(23, g["iq4xs"], 512, 3)), bits(g["iq4xs_rows"]))
+    assert np.array_equal(synth.make_iq4nl(synth.rng_for(12, 3), 3, 256), g["iq4nl"])
+    assert np.array_equal(synth.make_iq4xs(synth.rng_for(12, 4), 3, 512), g["iq4xs"])
+    assert float(np.abs(g["iq4xs_rows"]).max()) > 0 and np.isfinite(g["iq4xs_rows"]).all()
+
+
 def test_generators_reproduce_golden_inputs(golden_dir):
     """The synthetic generator must give the bytes the golden outputs were made from."""
     g = np.load(os.path.join(golden_dir, "moe_tiny.npz"))
