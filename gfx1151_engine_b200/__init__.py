@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200moe.so")
 
 GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
-GGML_Q5_1, GGML_Q4_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 20, 23
+GGML_Q5_1, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 13, 20, 23
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
           5: "device timeout", 6: "NCCL error", 7: "out of memory", 8: "too large for the static scratch"}
@@ -38,6 +38,7 @@ SYMBOLS = {
     "b200moe_load_gguf": (_I, [_P, _I, _P, _P, _P, _I, _I]),
     "b200moe_load_shared_q4cp": (_I, [_P, _I, _P, _P, _P, _P]),
     "b200moe_forward": (_I, [_P, _I, _P, _I, _P, _P, _P]),
+    "b200moe_forward_hc": (_I, [_P, _I, _P, _I, _P, _P, _P, _P]),
     "b200moe_forward_routed": (_I, [_P, _I, _P, _I, _P, _P, _I, _P, _P]),
     "b200moe_forward_host": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_router_topk": (_I, [_P, _P, _I, _P, _P, _I, _P]),
@@ -188,6 +189,13 @@ class MoeOperator:
         T = x.shape[0] if T is None else T
         self._check(lib().b200moe_forward(self._h, layer, _ptr(x), T, _ptr(logits), _ptr(out),
                                           _stream(stream)))
+
+    def moe_b_hc(self, layer, x, logits, inject_w4, state, T=None, stream=None):
+        """As moe_b, but the result is added into the bf16 residual state [T][4][d] with the gates
+        2*sigmoid(inject_w4[t][b] / 4) (k_moe_reduce_pw_sg_hc of the reference) instead of stored."""
+        T = x.shape[0] if T is None else T
+        self._check(lib().b200moe_forward_hc(self._h, layer, _ptr(x), T, _ptr(logits), _ptr(inject_w4),
+                                             _ptr(state), _stream(stream)))
 
     moe = moe_b  # the single-token entry point of the reference is the same call with T = 1
 

@@ -41,6 +41,8 @@ struct b200moe_ctx {
   __half* x_sorted = nullptr;
   int dec_rows = 0;
   RouterPlan* rplan = nullptr;     // router logits from hidden states
+  const float* hc_w4 = nullptr;    // set for the duration of b200moe_forward_hc: the combine
+  void* hc_state = nullptr;        // adds into the residual state instead of storing `out`
   float* router_logits = nullptr;  // [max_tokens][E]
   int32_t* flag_list = nullptr;    // (token * E + expert) pairs whose logits are recomputed exactly
   int32_t* flag_count = nullptr;
@@ -361,6 +363,7 @@ static void gguf_type_info(int type, bool down, size_t K, int* fmt, size_t* row_
   *row_bytes = 0;
   *granule = 256;
   if (type == B200MOE_GGML_Q4_K && !down) *fmt = kQ4K, *row_bytes = K / 256 * 144;
+  else if (type == B200MOE_GGML_Q5_K && !down) *fmt = kQ51, *row_bytes = K / 256 * 176;
   else if (type == B200MOE_GGML_Q5_1 && down) *fmt = kQ51, *row_bytes = K / 32 * 24, *granule = 32;
   else if (type == B200MOE_GGML_IQ4_NL) *fmt = kQ4CP, *row_bytes = K / 32 * 18, *granule = 32;
   else if (type == B200MOE_GGML_IQ4_XS) *fmt = kQ4CP, *row_bytes = K / 256 * 136;
@@ -386,7 +389,7 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
   gguf_type_info(type_dn, true, mid, &fmt_dn, &rb_dn, &gr_dn);
   if (fmt_gu < 0 || fmt_dn < 0)
     return fail(h, B200MOE_ERR_UNSUPPORTED,
-                "GGUF experts: gate/up must be Q4_K, IQ4_NL or IQ4_XS and down Q5_1, IQ4_NL or IQ4_XS");
+                "GGUF experts: gate/up must be Q4_K, Q5_K, IQ4_NL or IQ4_XS and down Q5_1, IQ4_NL or IQ4_XS");
   if (d % gr_gu != 0 || mid % gr_dn != 0)
     return fail(h, B200MOE_ERR_UNSUPPORTED, "GGUF experts: row length is not a whole number of blocks");
   CU_TRY(h, cudaSetDevice(c.device));
@@ -568,7 +571,7 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
                                h->rb.runs, h->rb.n_runs, (float*)h->pairs, st));
     if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
-                                 shared ? pairs : -1, out, st));
+                                 shared ? pairs : -1, out, st, h->hc_w4, h->hc_state));
     n += 3;
   } else if (simt) {
     const int max_runs = std::min(E, pairs);
@@ -592,7 +595,7 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     }
     if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f32((const float*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
-                                 shared ? pairs : -1, out, st));
+                                 shared ? pairs : -1, out, st, h->hc_w4, h->hc_state));
     n++;
   } else {
     if (!h->tc) return fail(h, B200MOE_ERR_UNSUPPORTED, "tensor-core path not available on this handle");
@@ -619,7 +622,7 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     }
     if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
     CU_TRY(h, launch_combine_f16((const __half*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d,
-                                 shared ? pairs : -1, out, st));
+                                 shared ? pairs : -1, out, st, h->hc_w4, h->hc_state));
     n++;
   }
   if (ev) {
@@ -641,6 +644,25 @@ int b200moe_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
   if (h->prof) CU_TRY(h, cudaEventRecord(h->prof_ev[(size_t)h->prof_head * kProfEvents], st));
   return forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, out_bf16_dev, st,
                       h->prof, logits_dev);
+}
+
+int b200moe_forward_hc(b200moe_handle h, int layer, const void* x_bf16_dev, int T, const float* logits_dev,
+                       const float* inject_w4_dev, void* state_bf16_dev, void* stream) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!x_bf16_dev || !logits_dev || !inject_w4_dev || !state_bf16_dev || T < 0 || T > h->cfg.max_tokens)
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward_hc: bad argument (null pointer or T out of range)");
+  if (h->cfg.d_model % 8 != 0 || ((uintptr_t)state_bf16_dev & 15))
+    return fail(h, B200MOE_ERR_BAD_ARG, "forward_hc: the state needs d_model % 8 == 0 and 16-byte alignment");
+  if (T == 0) return B200MOE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (h->prof) CU_TRY(h, cudaEventRecord(h->prof_ev[(size_t)h->prof_head * kProfEvents], st));
+  h->hc_w4 = inject_w4_dev;
+  h->hc_state = state_bf16_dev;
+  const int rc = forward_impl(h, layer, x_bf16_dev, T, h->rb.topids, h->rb.topw, kIdStride, nullptr, st, h->prof,
+                              logits_dev);
+  h->hc_w4 = nullptr;
+  h->hc_state = nullptr;
+  return rc;
 }
 
 int b200moe_get_config(b200moe_handle h, b200moe_config* out) {

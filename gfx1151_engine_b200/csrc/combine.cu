@@ -6,6 +6,11 @@
 //   out[t][c] = sum_{s<k} pw[row_s] * pairs[row_s][c]   (+ gate[t] * pairs[shared row][c])
 // with row_s = pairids[t*k + s], i.e. a fixed order (ascending expert id), fp32
 // accumulation, every output element written exactly once -- deterministic, no atomics.
+//
+// With a state pointer the same kernels do the write-back of k_moe_reduce_pw_sg_hc
+// (src/gpu/parts/24_kernels_moe_lt.inc:126-161) instead of storing `out`: the layer result is
+// added into the four branches of the bf16 residual state,
+//   R[t][b][c] = bf16(float(R[t][b][c]) + inj[t][b] * sum),  inj = 2 / (1 + exp(-w4[t][b] / 4)).
 #include "kernels.h"
 
 namespace b200moe {
@@ -28,12 +33,25 @@ __device__ __forceinline__ void load8(const __half* p, float* v) {
   }
 }
 
+struct HcWriteBack {
+  const float* w4;   // [T][4] inject gate pre-activations, or null: store `out`
+  uint16_t* state;   // [T][4][d] bf16
+};
+
+__device__ __forceinline__ float hc_inject(float w) { return 2.f / (1.f + expf(-w * 0.25f)); }
+
+__device__ __forceinline__ uint32_t hc_add2(uint32_t r, float inj, float a, float b) {
+  const float lo = bf16_bits_to_f32((uint16_t)(r & 0xFFFFu)), hi = bf16_bits_to_f32((uint16_t)(r >> 16));
+  const __nv_bfloat162 o = __floats2bfloat162_rn(fmaf(inj, a, lo), fmaf(inj, b, hi));
+  return *(const uint32_t*)&o;
+}
+
 // One block per (token, 2048-column slice); each thread owns 8 consecutive columns.
 template <typename TP>
 __global__ void __launch_bounds__(256)
 k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
           const int32_t* __restrict__ pairids, int k, int d, int shared_row0,
-          __nv_bfloat16* __restrict__ out) {
+          __nv_bfloat16* __restrict__ out, HcWriteBack hc) {
   const int t = blockIdx.x;
   __shared__ int s_row[kMaxTopK + 1];
   __shared__ float s_w[kMaxTopK + 1];
@@ -60,6 +78,20 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
 #pragma unroll
       for (int i = 0; i < 8; i++) acc[i] = fmaf(w, v[i], acc[i]);
     }
+    if (hc.w4) {
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const float inj = hc_inject(hc.w4[(size_t)t * 4 + b]);
+        uint4* rp = (uint4*)(hc.state + ((size_t)t * 4 + b) * d + c);
+        uint4 r = *rp;
+        r.x = hc_add2(r.x, inj, acc[0], acc[1]);
+        r.y = hc_add2(r.y, inj, acc[2], acc[3]);
+        r.z = hc_add2(r.z, inj, acc[4], acc[5]);
+        r.w = hc_add2(r.w, inj, acc[6], acc[7]);
+        *rp = r;
+      }
+      continue;
+    }
     uint4 o;
     __nv_bfloat162* ob = (__nv_bfloat162*)&o;
 #pragma unroll
@@ -73,7 +105,7 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
 __global__ void __launch_bounds__(128)
 k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
                 const int32_t* __restrict__ pairids, int k, int d, int shared_row0,
-                __nv_bfloat16* __restrict__ out) {
+                __nv_bfloat16* __restrict__ out, HcWriteBack hc) {
   const int t = blockIdx.x;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   pdl_trigger();
@@ -99,6 +131,18 @@ k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
       acc.z = fmaf(w[s], v[s].z, acc.z);
       acc.w = fmaf(w[s], v[s].w, acc.w);
     }
+  }
+  if (hc.w4) {
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const float inj = hc_inject(hc.w4[(size_t)t * 4 + b]);
+      uint2* rp = (uint2*)(hc.state + ((size_t)t * 4 + b) * d + c);
+      uint2 r = *rp;
+      r.x = hc_add2(r.x, inj, acc.x, acc.y);
+      r.y = hc_add2(r.y, inj, acc.z, acc.w);
+      *rp = r;
+    }
+    return;
   }
   uint2 o;
   *(__nv_bfloat162*)&o.x = __floats2bfloat162_rn(acc.x, acc.y);
@@ -145,19 +189,22 @@ k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx,
 }  // namespace
 
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
-                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st,
+                               const float* hc_w4, void* hc_state) {
+  const HcWriteBack hc{hc_w4, (uint16_t*)hc_state};
   if (T <= 64 && d % 4 == 0)
     return launch_pdl(k_combine_small, dim3(T, (d / 4 + 127) / 128), dim3(128), 0, st, pairs, pw, pairids, k, d, shared_row0,
-                      (__nv_bfloat16*)out_bf16);
+                      (__nv_bfloat16*)out_bf16, hc);
   else
-    k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16);
+    k_combine<float><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0, (__nv_bfloat16*)out_bf16, hc);
   return cudaGetLastError();
 }
 
 cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
-                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st) {
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st,
+                               const float* hc_w4, void* hc_state) {
   k_combine<__half><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, shared_row0,
-                                       (__nv_bfloat16*)out_bf16);
+                                       (__nv_bfloat16*)out_bf16, HcWriteBack{hc_w4, (uint16_t*)hc_state});
   return cudaGetLastError();
 }
 

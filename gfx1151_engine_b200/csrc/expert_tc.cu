@@ -770,6 +770,8 @@ cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, cons
                          int max_tiles, __half* hid16, int32_t* status, cudaStream_t st) {
   if (img.fmt == kQ4K)
     return launch<true, false, kQ4K>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
+  if (img.fmt == kQ51)  // Q5_K gate/up in the Q5_1 image form
+    return launch<true, false, kQ51>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);
   if (img.fmt != kQ4CP) return cudaErrorNotSupported;
   if (img.dual_book)
     return launch<true, true, kQ4CP>(plan, plan->x, img, tiles, n_tiles, max_tiles, hid16, img.n_mtiles * 64, status, st);

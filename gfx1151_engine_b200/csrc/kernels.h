@@ -50,7 +50,8 @@ struct SrcTensor {
 // ---- repack.cu ----
 // expert_map (device, may be null): source expert of image expert i is expert_map[first_expert + i]
 // (placement for expert parallelism), else first_expert + i. gguf_type 20 / 23: the source is
-// GGUF IQ4_NL / IQ4_XS blocks and the image is q4cp (scale = fp16(256 * block scale)).
+// GGUF IQ4_NL / IQ4_XS blocks and the image is q4cp (scale = fp16(256 * block scale)); 13: the
+// source is Q5_K and the image has the Q5_1 form.
 cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor& b, int K,
                           int first_expert, cudaStream_t st, const int32_t* expert_map = nullptr,
                           int gguf_type = 0);
@@ -135,10 +136,14 @@ cudaError_t launch_router_pairs(const void* x_bf16, const void* w_bf16, const in
                                 int cap, int E, int d, float* logits, cudaStream_t st);
 
 // ---- combine.cu ----
+// hc_w4 / hc_state non-null: add the result into the four branches of the bf16 state
+// [T][4][d] with gates 2*sigmoid(w4[t][b]/4) instead of storing out_bf16.
 cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_t* pairids, int T,
-                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st,
+                               const float* hc_w4 = nullptr, void* hc_state = nullptr);
 cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
-                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st);
+                               int k, int d, int shared_row0, void* out_bf16, cudaStream_t st,
+                               const float* hc_w4 = nullptr, void* hc_state = nullptr);
 cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
                               __half* x_sorted, cudaStream_t st);
 

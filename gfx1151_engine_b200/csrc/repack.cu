@@ -1,5 +1,5 @@
 // repack.cu -- one-time conversion of the reference's expert tensor layouts (hgn q4cp,
-// GGUF Q4_K, Q5_1, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
+// GGUF Q4_K, Q5_K, Q5_1, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
 // check: dequantising rows of the image bit-identically to the reference's row
 // dequantisers (q4cp_row, src/hgn.h:249-261; dequant_row, src/gguf.h:360-374, 408-441).
 #include "kernels.h"
@@ -137,6 +137,51 @@ __global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int fir
   }
 }
 
+// Q5_K (gate/up) -> the image format of Q5_1, "w = d' * (q + 16 * fifth bit) + m'" per 32
+// elements: d' = fp16(d * sc), m' = fp16(-(dmin * mn)) -- the constants the tensor-core path
+// forms for Q4_K as well -- and the group's 32 fifth bits gathered from bit 2*sub+h of the 32
+// qh bytes (src/gguf.h:408-441). One thread per (tile, row, half).
+__global__ void k_repack_q5k(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                             const int32_t* __restrict__ emap) {
+  const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 256;
+  const long long row_bytes = (long long)K / 256 * 176;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    int r = (int)(i & 127);
+    int h = (int)((i >> 7) & 1);
+    long long t = i >> 8;
+    int kb = (int)(t % img.n_kblocks);
+    long long t2 = t / img.n_kblocks;
+    int mt = (int)(t2 % img.n_mtiles);
+    int e = (int)(t2 / img.n_mtiles);
+    uint8_t* dst = const_cast<uint8_t*>(img.tile(e, mt, kb));
+    const SrcTensor* s;
+    long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
+    const uint8_t* blk = s->codes + row * row_bytes + (long long)(kb >> 2) * 176;
+    const int sub = kb & 3;
+    const uint8_t* ql = blk + 48 + 32 * sub;
+    const uint8_t* qh = blk + 16;
+    uint8_t out[16];
+    uint32_t fifth = 0;
+#pragma unroll
+    for (int q = 0; q < 16; q++) {
+      const uint8_t c0 = ql[2 * q], c1 = ql[2 * q + 1];
+      out[q] = h ? (uint8_t)((c0 >> 4) | ((c1 >> 4) << 4)) : (uint8_t)((c0 & 15) | ((c1 & 15) << 4));
+    }
+#pragma unroll
+    for (int l = 0; l < 32; l++) fifth |= (uint32_t)((qh[l] >> (2 * sub + h)) & 1) << l;
+    *(uint4*)(dst + h * 2048 + r * 16) = *(uint4*)out;
+    uint8_t sc, mn;
+    k4_scale_min(2 * sub + h, blk + 4, sc, mn);
+    const float d = half_bits_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    const float dmin = half_bits_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+    uint8_t* meta = dst + kCodeBytes + r * 16 + h * 8;
+    *(__half*)meta = __float2half_rn(__fmul_rn(d, (float)sc));
+    *(__half*)(meta + 2) = __float2half_rn(-__fmul_rn(dmin, (float)mn));
+    *(uint32_t*)(meta + 4) = fifth;
+  }
+}
+
 // GGUF IQ4_NL / IQ4_XS -> the q4cp image: one thread per (tile, row, half). Both formats are
 // "grid value x one scale per 32 elements" (src/gguf.h:375-406), which is what a q4cp tile
 // holds; element j of a block is the low nibble of qs[j], element j+16 the high nibble. The
@@ -250,6 +295,7 @@ cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor&
   else if (img.fmt == kQ4CP && gguf_type == 23) k_repack_iq4<true><<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else if (img.fmt == kQ4K) k_repack_q4k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else if (gguf_type == 13) k_repack_q5k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else k_repack_q51<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   return cudaGetLastError();
 }

@@ -4,7 +4,7 @@ Stand-ins for real checkpoints, with the shapes and value distributions of the
 benchmark configurations:
   * hgn q4cp tensors (layout: src/hgn.h:5-9 of the reference): 16 x f32 code book, 4-bit
     codes uniform in [0,15], fp16 scales |N(0, 0.02)| per (row, 32 columns);
-  * GGUF Q4_K / Q5_1 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
+  * GGUF Q4_K / Q5_K / Q5_1 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
     block scales normalised so that dequantised magnitudes match the q4cp case;
   * bf16 activations ~ N(0,1), router logits ~ N(0,1) with an optional per-expert
     Zipf(1.1) bias under a seeded permutation of the expert ids.
@@ -100,6 +100,18 @@ def make_logits(rng, T, experts, zipf=False, zipf_rng=None, strength=1.0):
 def make_x(rng, T, d):
     """bf16 activations ~ N(0,1) as uint16 bit patterns."""
     return f32_to_bf16_bits(rng.normal(0.0, 1.0, size=(T, d)).astype(np.float32))
+def make_q5k(rng, nrows, k, sigma=0.02):
+    """nrows rows of GGUF Q5_K blocks (176 bytes per 256 elements: d, dmin, 12 packed scale bytes,
+    32 bytes of fifth bits, 128 nibble bytes; src/gguf.h:408-441)."""
+    nb = nrows * (k // 256)
+    a = np.abs(rng.normal(0.0, sigma, size=nb))
+    blk = np.zeros((nb, 176), dtype=np.uint8)
+    blk[:, 0:2] = (a / (63.0 * 31.0)).astype("<f2").view(np.uint8).reshape(nb, 2)
+    blk[:, 2:4] = (a / (63.0 * 2.0)).astype("<f2").view(np.uint8).reshape(nb, 2)
+    blk[:, 4:] = rng.integers(0, 256, size=(nb, 172), dtype=np.uint8)
+    return blk.reshape(-1)
+
+
 def make_iq4nl(rng, nrows, k, sigma=0.02):
     """nrows rows of GGUF IQ4_NL blocks (18 bytes per 32 elements: fp16 d, 16 code bytes;
     src/gguf.h:375-387). |w| <= a with a = |N(0, sigma)| per block, as for the other formats."""
@@ -123,13 +135,13 @@ def make_iq4xs(rng, nrows, k, sigma=0.02):
     return blk.reshape(-1)
 
 
-GGML_Q5_1, GGML_Q4_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 20, 23
-_GG_MAKERS = {GGML_Q5_1: make_q51, GGML_Q4_K: make_q4k, GGML_IQ4_NL: make_iq4nl, GGML_IQ4_XS: make_iq4xs}
+GGML_Q5_1, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 13, 20, 23
+_GG_MAKERS = {GGML_Q5_1: make_q51, GGML_Q4_K: make_q4k, GGML_Q5_K: make_q5k, GGML_IQ4_NL: make_iq4nl, GGML_IQ4_XS: make_iq4xs}
 
 
 def gg_row_bytes(gtype, k):
     """Bytes of one row of k elements in GGUF block type `gtype` (src/gguf.h:49-62)."""
-    per, nbytes = {GGML_Q5_1: (32, 24), GGML_Q4_K: (256, 144), GGML_IQ4_NL: (32, 18), GGML_IQ4_XS: (256, 136)}[gtype]
+    per, nbytes = {GGML_Q5_1: (32, 24), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_IQ4_NL: (32, 18), GGML_IQ4_XS: (256, 136)}[gtype]
     assert k % per == 0
     return k // per * nbytes
 
@@ -144,7 +156,7 @@ class LayerSpec:
     fmt: str = "q4cp"      # "q4cp" or "gguf"
     book: str = "linear"   # "linear" or "random" (q4cp only)
     router: bool = False   # also make a bf16 router weight [E][d]
-    gg_gu: int = 12        # GGUF block type of gate/up (fmt "gguf"): Q4_K 12, IQ4_NL 20, IQ4_XS 23
+    gg_gu: int = 12        # GGUF block type of gate/up (fmt "gguf"): Q4_K 12, Q5_K 13, IQ4_NL 20, IQ4_XS 23
     gg_dn: int = 7         # GGUF block type of down: Q5_1 7, IQ4_NL 20, IQ4_XS 23
 
 

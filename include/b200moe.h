@@ -41,7 +41,7 @@ enum {
 };
 
 /* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
-enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12, B200MOE_GGML_IQ4_NL = 20, B200MOE_GGML_IQ4_XS = 23 };
+enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12, B200MOE_GGML_Q5_K = 13, B200MOE_GGML_IQ4_NL = 20, B200MOE_GGML_IQ4_XS = 23 };
 
 /* Which expert GEMM implementation forward uses for T > decode_max_tokens. */
 enum {
@@ -88,11 +88,12 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
 
 /* Replaces: gguf_experts_open / GgExperts (src/gpu/parts/30_host_util.inc:348-452): raw GGUF
  * blocks of blk.L.ffn_{gate,up,down}_exps.weight, expert e's rows at e*rows*row_bytes
- * (src/gguf.h:3-11). type_gu: Q4_K, IQ4_NL or IQ4_XS; type_dn: Q5_1, IQ4_NL or IQ4_XS (the
+ * (src/gguf.h:3-11). type_gu: Q4_K, Q5_K, IQ4_NL or IQ4_XS; type_dn: Q5_1, IQ4_NL or IQ4_XS (the
  * types of moe_gg_up / moe_gg_down and of the table-decoded kernels,
  * src/gpu/parts/27_kernels_moe_lut.inc:4-19, 659-671). The IQ4 types become the q4cp tile image:
  * code book = grid / 256, group scale = fp16(256 * d [* (ls - 32)]), the exact rescale of
- * 27_kernels_moe_lut.inc:312-326. */
+ * 27_kernels_moe_lut.inc:312-326; Q5_K becomes the Q5_1 image form (d' = fp16(d*sc),
+ * m' = fp16(-dmin*mn) per 32 elements, fifth bits regrouped). */
 int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
                       const void* down_src, int type_gu, int type_dn);
 
@@ -121,6 +122,14 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
                          const float* logits_host, void* out_bf16_host, void* stream);
 
 /* The configuration the handle was created with. */
+/* Replaces: the layer call followed by k_moe_reduce_pw_sg_hc
+ * (src/gpu/parts/24_kernels_moe_lt.inc:126-161): as b200moe_forward, but the result is not
+ * stored; it is added into the four branches of the bf16 residual state [T][4][d_model],
+ *   state[t][b][c] = bf16(float(state[t][b][c]) + 2*sigmoid(inject_w4[t][b] / 4) * y[t][c]),
+ * with y in fp32 (no bf16 rounding of the layer output in between). inject_w4 is fp32 [T][4]. */
+int b200moe_forward_hc(b200moe_handle h, int layer, const void* x_bf16_dev, int T, const float* logits_dev,
+                       const float* inject_w4_dev, void* state_bf16_dev, void* stream);
+
 int b200moe_get_config(b200moe_handle h, b200moe_config* out);
 
 /* Expert tensors of one layer straight from a model file (mapped read-only for the duration of

@@ -13,7 +13,7 @@
 // project root):
 //   orc_q4cp_rows        src/hgn.h:219-261   (q4cp_parse / q4cp_row)
 //   orc_gguf_rows        src/gguf.h:328-336, 360-374, 375-406, 408-441 (scale_min_k4, Q5_1,
-//                        IQ4_NL, IQ4_XS, Q4_K)
+//                        IQ4_NL, IQ4_XS, Q4_K, Q5_K)
 //   orc_router_topk      src/ref.cpp:574-588 (softmax in double, partial_sort on probs)
 //   orc_route            src/gpu/parts/40_model.inc:4171-4193 (host bucketing) and
 //                        src/gpu/parts/10_ple_io.inc:790-811 (pairids rank rule)
@@ -83,12 +83,13 @@ inline void q4_row(const Q4View& v, uint64_t row, float* out) {
   }
 }
 
-enum { GG_Q5_1 = 7, GG_Q4_K = 12, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
+enum { GG_Q5_1 = 7, GG_Q4_K = 12, GG_Q5_K = 13, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
 
-inline bool gg_known(uint32_t t) { return t == GG_Q5_1 || t == GG_Q4_K || t == GG_IQ4_NL || t == GG_IQ4_XS; }
+inline bool gg_known(uint32_t t) { return t == GG_Q5_1 || t == GG_Q4_K || t == GG_Q5_K || t == GG_IQ4_NL || t == GG_IQ4_XS; }
 
 inline uint64_t gg_row_bytes(uint32_t type, uint64_t k) {
   if (type == GG_Q4_K) return k / 256 * 144;
+  if (type == GG_Q5_K) return k / 256 * 176;
   if (type == GG_Q5_1) return k / 32 * 24;
   if (type == GG_IQ4_NL) return k / 32 * 18;
   if (type == GG_IQ4_XS) return k / 256 * 136;
@@ -158,22 +159,32 @@ inline void gg_row(uint32_t type, const uint8_t* src, float* y, uint64_t k) {
     }
     return;
   }
-  // Q4_K
-  for (uint64_t b = 0; b < k / 256; b++, src += 144) {
+  // Q4_K (144 bytes per 256) and Q5_K (176 bytes: 32 bytes of fifth bits between the packed
+  // scales and the nibbles; bit 2*sub / 2*sub+1 of qh[l] belongs to element l of the low / high
+  // group of the sub-th 64 elements), src/gguf.h:408-441
+  const bool five = type == GG_Q5_K;
+  for (uint64_t b = 0; b < k / 256; b++, src += five ? 176 : 144) {
     uint16_t dh, mh;
     memcpy(&dh, src, 2);
     memcpy(&mh, src + 2, 2);
     const float d = half_bits_to_float(dh), dmin = half_bits_to_float(mh);
     const uint8_t* packed = src + 4;
-    const uint8_t* q = src + 16;
+    const uint8_t* hb = src + 16;
+    const uint8_t* q = src + (five ? 48 : 16);
     float* o = y + b * 256;
     for (int sub = 0; sub < 4; sub++) {
       uint8_t s0, m0, s1, m1;
       k4_scale_min(2 * sub, packed, s0, m0);
       k4_scale_min(2 * sub + 1, packed, s1, m1);
       const float a0 = d * s0, b0 = dmin * m0, a1 = d * s1, b1 = dmin * m1;
-      for (int l = 0; l < 32; l++) o[64 * sub + l] = a0 * (q[32 * sub + l] & 15) - b0;
-      for (int l = 0; l < 32; l++) o[64 * sub + 32 + l] = a1 * (q[32 * sub + l] >> 4) - b1;
+      for (int l = 0; l < 32; l++) {
+        const int lo = (q[32 * sub + l] & 15) + (five && ((hb[l] >> (2 * sub)) & 1) ? 16 : 0);
+        o[64 * sub + l] = a0 * lo - b0;
+      }
+      for (int l = 0; l < 32; l++) {
+        const int hi = (q[32 * sub + l] >> 4) + (five && ((hb[l] >> (2 * sub + 1)) & 1) ? 16 : 0);
+        o[64 * sub + 32 + l] = a1 * hi - b1;
+      }
     }
   }
 }

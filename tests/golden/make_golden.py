@@ -40,6 +40,8 @@ def gguf_iq4():
     xs = synth.make_iq4xs(synth.rng_for(12, 4), 3, 512)
     np.savez_compressed(os.path.join(OUT, "gguf_iq4_rows.npz"), iq4nl=nl, iq4nl_rows=oracle.gguf_rows(20, nl, 256, 3, use_ref=True),
                         iq4xs=xs, iq4xs_rows=oracle.gguf_rows(23, xs, 512, 3, use_ref=True))
+    q5k = synth.make_q5k(synth.rng_for(12, 5), 3, 512)
+    np.savez_compressed(os.path.join(OUT, "gguf_q5k_rows.npz"), q5k=q5k, q5k_rows=oracle.gguf_rows(13, q5k, 512, 3, use_ref=True))
 
 
 def main():

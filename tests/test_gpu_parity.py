@@ -294,10 +294,32 @@ def test_gguf_layer(cuda, impl):
         print("gguf T=%d impl=%d max-abs %.2e mean-rel %.2e" % (T, impl, max_abs, mean_rel))
 
 
+def test_dequant_q5k(cuda):
+    """Q5_K gate/up is stored in the Q5_1 image form with d' = fp16(d*sc), m' = fp16(-dmin*mn):
+    nibbles, fifth bits and sub-block scales must land on the right elements (error far below one
+    code step), the two roundings bound the difference to the reference's rows."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=2, topk=1, d=512, mid=128, fmt="gguf", gg_gu=13, gg_dn=7)
+    layer = synth.make_layer(spec, seed=34)
+    op = make_op(torch, spec, 4, impl=pkg.GEMM_SIMT, layer=layer)
+    for e in range(spec.experts):
+        out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 0, e, 0, 2 * spec.mid, out)
+        rb = synth.gg_row_bytes(13, spec.d)
+        g = oracle.gguf_rows(13, layer["gate"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        u = oracle.gguf_rows(13, layer["up"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        got, want = out.cpu().numpy(), np.concatenate([g, u])
+        # per 256-block: |w| <= a, one code step = a / 31 at the largest sub-scale; rounding error
+        # of d' and m' is below 2^-10 * a, i.e. 3 % of a step
+        a = np.abs(want).reshape(-1, 256).max(axis=1, keepdims=True) + 1e-12
+        assert np.all(np.abs(got - want).reshape(-1, 256) <= a * 2.0 ** -9)
+
+
 @pytest.mark.parametrize("gu,dn,impl", [(20, 20, pkg.GEMM_AUTO), (23, 23, pkg.GEMM_AUTO), (12, 23, pkg.GEMM_AUTO),
-                                        (20, 7, pkg.GEMM_AUTO), (23, 20, pkg.GEMM_SIMT)])
+                                        (20, 7, pkg.GEMM_AUTO), (23, 20, pkg.GEMM_SIMT), (13, 7, pkg.GEMM_AUTO),
+                                        (13, 23, pkg.GEMM_AUTO), (13, 7, pkg.GEMM_SIMT)])
 def test_iq4_layer(cuda, gu, dn, impl):
-    """GGUF experts in IQ4_NL (20) / IQ4_XS (23), alone and mixed with Q4_K (12) / Q5_1 (7): GEMV
+    """GGUF experts in Q5_K (13), IQ4_NL (20) / IQ4_XS (23), alone and mixed with Q4_K (12) / Q5_1 (7): GEMV
     (T=3), tensor-core (T=40, 300) and fp32 paths against the oracle, which dequantises the raw
     blocks as the reference's dequant_row does."""
     torch = cuda
@@ -311,6 +333,40 @@ def test_iq4_layer(cuda, gu, dn, impl):
         y = run_layer(torch, op, spec, xb, logits)
         max_abs, mean_rel = assert_output_close(y, y_o, "iq4 %d/%d T=%d impl %d" % (gu, dn, T, impl))
         print("iq4 gu=%d dn=%d T=%d impl=%d max-abs %.2e mean-rel %.2e" % (gu, dn, T, impl, max_abs, mean_rel))
+
+
+@pytest.mark.parametrize("shared", [False, True])
+def test_hc_write_back(cuda, shared):
+    """b200moe_forward_hc against the reference's k_moe_reduce_pw_sg_hc
+    (src/gpu/parts/24_kernels_moe_lt.inc:126-161) restated in numpy on the oracle's fp32 layer
+    output: state[t][b] = bf16(state[t][b] + 2*sigmoid(w4[t][b]/4) * y[t]). The layer output itself
+    is only within the layer tolerance, so the state is compared with that tolerance scaled by the
+    gate (<= 2) plus one bf16 step, and nearly all elements must be bit-equal."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=128, shared=shared)
+    layer = synth.make_layer(spec, seed=90)
+    for T in (3, 40, 300):   # GEMV + small combine, tensor-core + fp16 combine
+        logits = synth.make_logits(synth.rng_for(90, T), T, spec.experts)
+        xb = synth.make_x(synth.rng_for(90, 9), T, spec.d)
+        y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+        rng = synth.rng_for(90, 100 + T)
+        r0_bits = synth.f32_to_bf16_bits(rng.normal(0.0, 1.0, size=(T, 4, spec.d)).astype(np.float32))
+        w4 = rng.normal(0.0, 2.0, size=(T, 4)).astype(np.float32)
+        inj = (np.float32(2.0) / (np.float32(1.0) + np.exp(-w4 * np.float32(0.25)))).astype(np.float32)
+        want = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(
+            synth.bf16_bits_to_f32(r0_bits) + inj[:, :, None] * y_o[:, None, :]))
+        op = make_op(torch, spec, T, layer=layer)
+        state = bf16_tensor(torch, r0_bits, (T, 4, spec.d))
+        op.moe_b_hc(0, bf16_tensor(torch, xb, (T, spec.d)), torch.from_numpy(np.ascontiguousarray(logits, np.float32)).cuda(),
+                    torch.from_numpy(w4).cuda(), state)
+        op.synchronize()
+        got = bf16_out_to_f32(torch, state.reshape(T * 4, spec.d)).reshape(T, 4, spec.d)
+        assert np.isfinite(got).all()
+        assert np.all(np.abs(got - want) <= 2 * 2e-2 + np.abs(want) * 2.0 ** -7)
+        same = float(np.mean(got == want))
+        print("hc T=%d shared=%d bit-equal %.4f" % (T, shared, same))
+        assert same > 0.95
+        assert not np.array_equal(got, synth.bf16_bits_to_f32(r0_bits))
 
 
 def test_forward_routed_and_host_paths(cuda):

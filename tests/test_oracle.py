@@ -40,6 +40,13 @@ def test_gguf_iq4_rows_golden(golden_dir):
     assert float(np.abs(g["iq4xs_rows"]).max()) > 0 and np.isfinite(g["iq4xs_rows"]).all()
 
 
+def test_gguf_q5k_rows_golden(golden_dir):
+    """Q5_K rows against the reference's dequant_row (src/gguf.h:408-441)."""
+    g = np.load(os.path.join(golden_dir, "gguf_q5k_rows.npz"))
+    assert np.array_equal(bits(oracle.gguf_rows(13, g["q5k"], 512, 3)), bits(g["q5k_rows"]))
+    assert np.array_equal(synth.make_q5k(synth.rng_for(12, 5), 3, 512), g["q5k"])
+
+
 def test_generators_reproduce_golden_inputs(golden_dir):
     """The synthetic generator must give the bytes the golden outputs were made from."""
     g = np.load(os.path.join(golden_dir, "moe_tiny.npz"))
