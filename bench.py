@@ -148,9 +148,12 @@ def gguf_blocks_device(torch, rows, cols, kind, gen):
     return blob.reshape(-1)
 
 
+ZIPF_STRENGTH = 1.0  # --zipf-strength: 1.0 = the benchmark's Zipf(1.1) bias, 0.5 = the milder sensitivity run
+
+
 def zipf_logits(torch, T, gen, seed):
     from gfx1151_engine_b200 import synth
-    bias = synth.zipf_bias(synth.rng_for(seed, 77), E)
+    bias = synth.zipf_bias(synth.rng_for(seed, 77), E, strength=ZIPF_STRENGTH)
     return (torch.randn(T, E, device="cuda", generator=gen) + torch.from_numpy(bias).cuda()[None, :]).contiguous()
 
 
@@ -223,7 +226,7 @@ def reference_arm(args):
 
 # ------------------------------------------------------------------ GPU arm
 def main():
-    global E
+    global E, ZIPF_STRENGTH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
@@ -238,6 +241,8 @@ def main():
     ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
     ap.add_argument("--transport", default="p2p", choices=["nccl", "p2p"],
                     help="N>1: exchanges by NCCL all-to-all or by peer copies (copy engines) through CUDA IPC")
+    ap.add_argument("--zipf-strength", type=float, default=1.0,
+                    help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
@@ -247,6 +252,7 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     E = args.experts
+    ZIPF_STRENGTH = args.zipf_strength
 
     import torch
     import torch.distributed as dist
@@ -325,6 +331,10 @@ def main():
     logits = zipf_logits(torch, T, gen_in, 0)
     out = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
     stream = torch.cuda.current_stream()
+    # realised routing histogram of this rank's chunk (pairs per expert)
+    hist = torch.bincount(torch.topk(logits, K_TOP, dim=1).indices.reshape(-1), minlength=E).cpu().numpy()
+    routing = {"zipf_strength": ZIPF_STRENGTH, "pairs_max": int(hist.max()), "pairs_median": float(np.median(hist)),
+               "experts_below_64_pairs": int((hist < 64).sum()), "experts_unused": int((hist == 0).sum())}
 
     def barrier():
         if world > 1:
@@ -443,8 +453,9 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
         "data": "synthetic",
         "config": {"workload": ("GGUF variant (Q4_K gate/up, Q5_1 down), not the benchmark workload" if gguf else
+                                "sensitivity run with a scaled routing bias (not the benchmark workload)" if ZIPF_STRENGTH != 1.0 else
                                 WORKLOAD if (E, T) == (512, T_CHUNK) else "reduced case for profiling (not the benchmark workload)"), "tokens_per_gpu": T, "experts": E, "topk": K_TOP, "d_model": D,
-                   "d_mid": MID, "parallelism": "expert-parallel x%d" % world if world > 1 else "single GPU",
+                   "d_mid": MID, "routing": routing, "parallelism": "expert-parallel x%d" % world if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: 3.6 GB of expert weights + 168 MB of activations per step"},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "expert_parallel": ep_info,
         "stage_ms": {k: round(v, 4) for k, v in stages.items()},
