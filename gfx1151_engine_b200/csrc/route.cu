@@ -166,13 +166,28 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
     if (tok) {
       const uint4* xv = (const uint4*)(x + (size_t)ts * d);
       const uint4* gv = (const uint4*)gw;
-      for (int c = wq * 32 + lane; c < d / 8; c += W * 32) {
-        const uint4 xa = xv[c], ga = __ldg(gv + c);
-        const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, gq[4] = {ga.x, ga.y, ga.z, ga.w};
+      // eight pieces per lane are loaded before any is used (with one warp per token the loop
+      // would otherwise pay a global-load latency per piece); the additions keep their order
+      for (int c0 = wq * 32 + lane; c0 < d / 8; c0 += W * 32 * 8) {
+        uint4 xa[8], ga[8];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          a += (double)__uint_as_float(gq[q] << 16) * (double)__uint_as_float(xw[q] << 16);
-          a += (double)__uint_as_float(gq[q] & 0xFFFF0000u) * (double)__uint_as_float(xw[q] & 0xFFFF0000u);
+        for (int u = 0; u < 8; u++) {
+          const int c = c0 + u * W * 32;
+          if (c < d / 8) {
+            xa[u] = xv[c];
+            ga[u] = __ldg(gv + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (c0 + u * W * 32 < d / 8) {
+            const uint32_t xw[4] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w}, gq[4] = {ga[u].x, ga[u].y, ga[u].z, ga[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              a += (double)__uint_as_float(gq[q] << 16) * (double)__uint_as_float(xw[q] << 16);
+              a += (double)__uint_as_float(gq[q] & 0xFFFF0000u) * (double)__uint_as_float(xw[q] & 0xFFFF0000u);
+            }
+          }
         }
       }
     }
@@ -385,17 +400,19 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
       for (int i = lane; i < kIdStride; i += 32) {
         const bool valid = i < k && i < 32;
         rb.topids[(size_t)ts * kIdStride + i] = valid ? my_id : 0;
-        rb.topw[(size_t)ts * kIdStride + i] = valid ? (float)((double)my_p / kept) : 0.f;
+        const float wv = valid ? (float)((double)my_p / kept) : 0.f;
+        rb.topw[(size_t)ts * kIdStride + i] = wv;
+        if (valid) {  // the bucketing below takes the selection from shared memory, not back from global
+          s_key[ts * k + i] = my_id;
+          s_w[ts * k + i] = wv;
+        }
       }
     }
-    __syncthreads();
-    ids_in = rb.topids;
-    w_in = rb.topw;
-    stride_in = kIdStride;
-  }
-  for (int p = tid; p < P; p += blockDim.x) {
-    s_key[p] = ids_in[(size_t)(p / k) * stride_in + p % k];
-    s_w[p] = w_in[(size_t)(p / k) * stride_in + p % k];
+  } else {
+    for (int p = tid; p < P; p += blockDim.x) {
+      s_key[p] = ids_in[(size_t)(p / k) * stride_in + p % k];
+      s_w[p] = w_in[(size_t)(p / k) * stride_in + p % k];
+    }
   }
   __syncthreads();
   // pair p -> row = number of pairs ordered before it by (expert, p)
