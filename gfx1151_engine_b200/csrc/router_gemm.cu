@@ -296,6 +296,7 @@ k_router_dots(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, in
 __global__ void __launch_bounds__(256)
 k_router_pairs(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, const int32_t* __restrict__ pairs,
                const int32_t* __restrict__ count, int cap, int E, int d, float* __restrict__ logits) {
+  __shared__ double s_prod[8][256];  // per warp: the products of 256 elements, for the index-order replay
   const int lane = threadIdx.x & 31;
   const int n_warps = gridDim.x * (blockDim.x >> 5);
   const int n = min(*count, cap);
@@ -324,11 +325,32 @@ k_router_pairs(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, c
     }
     acc = __hiloint2double(__shfl_sync(0xffffffffu, __double2hiint(acc), 0), __shfl_sync(0xffffffffu, __double2loint(acc), 0));
     mag = __hiloint2double(__shfl_sync(0xffffffffu, __double2hiint(mag), 0), __shfl_sync(0xffffffffu, __double2loint(mag), 0));
-    const double delta = 4.0 * (double)d * 1.1102230246251565e-16 * mag;
+    // |index-order sum - true sum| <= gamma(d-1) * sum|p|, |this tree sum - true sum| <=
+    // gamma(d/32 + 5) * sum|p| (d/32 additions per lane, five shuffle levels), gamma(n) ~ n * 2^-53;
+    // `mag` is within the same tiny factor of sum|p|: 1 % of slack covers both second-order terms
+    const double delta = 1.01 * (double)(d + d / 32 + 8) * 1.1102230246251565e-16 * mag;
     if ((float)(acc - delta) != (float)(acc + delta)) {  // warp-uniform
+      // replay of the reference's order: the lanes form the (exact) products of 256 elements at a
+      // time, lane 0 adds them in index order -- the chain of dependent additions is all that is
+      // left on one thread
       acc = 0;
-      if (lane == 0)
-        for (int c = 0; c < d; c++) acc += (double)bf16_bits_to_f32(wr[c]) * (double)bf16_bits_to_f32(xr[c]);  // index order
+      double* sp = s_prod[threadIdx.x >> 5];
+      for (int c0 = 0; c0 < d; c0 += 256) {
+        const int c = c0 + lane * 8;
+        if (c < d) {
+          const uint4 xv = *(const uint4*)(xr + c), wv = __ldg((const uint4*)(wr + c));
+          const uint16_t* xb = (const uint16_t*)&xv;
+          const uint16_t* wb = (const uint16_t*)&wv;
+#pragma unroll
+          for (int j = 0; j < 8; j++) sp[lane * 8 + j] = (double)bf16_bits_to_f32(wb[j]) * (double)bf16_bits_to_f32(xb[j]);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          const int n = min(256, d - c0);
+          for (int j = 0; j < n; j++) acc += sp[j];
+        }
+        __syncwarp();
+      }
     }
     if (lane == 0) logits[(size_t)t * E + e] = (float)acc;
   }
