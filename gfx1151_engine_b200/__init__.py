@@ -56,6 +56,7 @@ SYMBOLS = {
     "b200moe_ep_route": (_I, [_P, _I, _P, _I, _P, _P, _P]),
     "b200moe_ep_offsets": (_I, [_P, ctypes.POINTER(_P)]),
     "b200moe_ep_experts": (_I, [_P, _I, _P, _P]),
+    "b200moe_ep_experts_part": (_I, [_P, _I, _P, _I, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _P, _P]),
     "b200moe_ep_wait_flags": (_I, [_P, _P, _I, _I, _P]),
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
@@ -241,8 +242,9 @@ class MoeOperator:
         self._check(lib().b200moe_ep_offsets(self._h, ctypes.byref(p)))
         return p.value
 
-    def ep_experts(self, layer, eoff_all, stream=None):
-        self._check(lib().b200moe_ep_experts(self._h, layer, _ptr(eoff_all), _stream(stream)))
+    def ep_experts(self, layer, eoff_all, stream=None, part=0):
+        """part 0: all received rows; 1: the rows this rank sent to itself; 2: the other ranks' rows."""
+        self._check(lib().b200moe_ep_experts_part(self._h, layer, _ptr(eoff_all), part, _stream(stream)))
 
     def ep_combine(self, out, T, stream=None):
         self._check(lib().b200moe_ep_combine(self._h, T, _ptr(out), _stream(stream)))

@@ -957,15 +957,20 @@ int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev) {
 }
 
 int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream) {
+  return b200moe_ep_experts_part(h, layer, eoff_all_dev, 0, stream);
+}
+
+int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream) {
   if (int s = check_layer(h, layer)) return s;
-  if (!eoff_all_dev || !h->tc_ep) return fail(h, B200MOE_ERR_BAD_ARG, "ep_experts: bad argument or buffers not attached");
+  if (!eoff_all_dev || !h->tc_ep || part < 0 || part > 2)
+    return fail(h, B200MOE_ERR_BAD_ARG, "ep_experts: bad argument or buffers not attached");
   LayerWeights& L = h->layers[layer];
   if (!L.loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "ep_experts: layer weights not loaded");
   const b200moe_config& c = h->cfg;
   cudaStream_t st = (cudaStream_t)stream;
   const int El = local_experts(c);
   CU_TRY(h, launch_ep_tiles(eoff_all_dev, c.ep_size, c.experts, first_expert(c), El, h->tile_cap, h->ep_tiles,
-                            h->ep_counts, h->ep_counts + 1, st));
+                            h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part));
   CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
   CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv,
                            h->status_dev, st));

@@ -659,7 +659,7 @@ __global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, 
 // its position in the buffer, then tiles of at most tile_cap rows (full tiles first, ragged
 // ones by descending size), exactly as the single-GPU tile list is built.
 __global__ void __launch_bounds__(kMaxExperts)
-k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, int tile_cap,
+k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, int tile_cap, int own, int part,
            Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ total_rows) {
   __shared__ int s_a[kMaxExperts], s_c[kMaxExperts];
   const int tid = threadIdx.x;
@@ -674,8 +674,10 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
       const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
       first += e2[e0 + El] - e2[e0];
     }
+    // part 1: only the rows this rank sent to itself; part 2: only the other ranks' rows
+    if ((part == 1 && src != own) || (part == 2 && src == own)) cnt = 0;
   }
-  const int nfull = cnt / tile_cap, part = cnt % tile_cap;
+  const int nfull = cnt / tile_cap, rag = cnt % tile_cap;
   s_c[tid] = nfull;
   __syncthreads();
   for (int o = 1; o < kMaxExperts; o <<= 1) {
@@ -686,15 +688,15 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
   }
   const int total_full = s_c[kMaxExperts - 1], full0 = s_c[tid] - nfull;
   for (int j = 0; j < nfull; j++) tiles[full0 + j] = Tile{e, first + j * tile_cap, tile_cap};
-  s_a[tid] = part;
+  s_a[tid] = rag;
   __syncthreads();
   int rank = 0, nparts = 0;
   for (int o = 0; o < kMaxExperts; o++) {
     const int pp = s_a[o];
     nparts += pp > 0;
-    rank += (pp > part) || (pp == part && o < tid);
+    rank += (pp > rag) || (pp == rag && o < tid);
   }
-  if (part > 0) tiles[total_full + rank] = Tile{e, first + nfull * tile_cap, part};
+  if (rag > 0) tiles[total_full + rank] = Tile{e, first + nfull * tile_cap, rag};
   if (tid == 0) {
     n_tiles[0] = total_full + nparts;
     int rows = 0;
@@ -713,8 +715,8 @@ cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, const
 }
 
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
-                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st) {
-  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, tiles, n_tiles, total_rows);
+                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st, int own, int part) {
+  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, own, part, tiles, n_tiles, total_rows);
   return cudaGetLastError();
 }
 

@@ -84,11 +84,15 @@ class ExpertParallelMoe:
     compute stream, so the NVLink time hides behind the tensor-core time."""
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
-                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl"):
+                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
         self.transport = transport
+        # p2p transport only: GEMMs over the rows a rank sent to itself run apart from those over the
+        # other ranks' rows -- first chunk: own rows first (while the others still arrive), last
+        # chunk: own rows last (while the others' results already travel back)
+        self.split_local = split_local and transport == "p2p"
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
         self.chunks = chunks
         self.tc = (max_tokens + chunks - 1) // chunks            # tokens per chunk
@@ -185,26 +189,58 @@ class ExpertParallelMoe:
         #    (p has finished reading that buffer: I waited for p's results of the previous
         #    forward, which p sent after its GEMMs.)
         self.comm.wait_event(routed)
+        own_in = [torch.cuda.Event() for _ in range(C)]
         with torch.cuda.stream(self.comm):
+            if self.split_local:
+                # the rows that stay on this GPU go first: their GEMMs start without any exchange
+                for c in range(C):
+                    B = self.buf[c]
+                    for p, src0, dst0, n in plans[c][0]:
+                        if p == self.rank:
+                            if n:
+                                B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
+                            B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
+                    own_in[c].record(self.comm)
             for c in range(C):
                 B = self.buf[c]
                 for p, src0, dst0, n in plans[c][0]:
+                    if self.split_local and p == self.rank:
+                        continue
                     if n:
                         B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
                     B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
-        # 2. experts per chunk once its rows have arrived; results go straight back to their owners
-        for c in range(C):
+
+        def send_back(c, which):
+            # which: None = every source, True = only my own rows, False = only the other ranks' rows
             B = self.buf[c]
-            self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
-            self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
             done = torch.cuda.Event()
             done.record(main)
             self.comm2.wait_event(done)
             with torch.cuda.stream(self.comm2):
                 for s, src0, dst0, n in plans[c][1]:
+                    if which is not None and (s == self.rank) != which:
+                        continue
                     if n:
                         B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
                     B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
+
+        # 2. experts per chunk once its rows have arrived; results go straight back to their owners
+        for c in range(C):
+            B = self.buf[c]
+            if not self.split_local:
+                self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
+                self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
+                send_back(c, None)
+                continue
+            own_first = c < C - 1 or C == 1
+            for own in ((True, False) if own_first else (False, True)):
+                if own:
+                    main.wait_event(own_in[c])
+                    self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=1)
+                else:
+                    self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
+                    self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=2)
+                send_back(c, own)
         # 3. combine
         for c, (a, b) in enumerate(span):
             B = self.buf[c]

@@ -219,6 +219,10 @@ int b200moe_ep_route(b200moe_handle h, int layer, const void* x_bf16_dev, int T,
                      void* stream);
 int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev);
 int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream);
+/* The same over a part of the received rows: part 1 = the rows this rank sent to itself (they need
+ * no exchange, so their GEMMs can run while the other ranks' rows are still arriving), part 2 = the
+ * other ranks' rows, 0 = all. Parts 1 and 2 together write what part 0 writes. */
+int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream);
 int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream);
 /* For hosts that move the rows with peer copies (copy engines) instead of a collective: every
  * sender writes its sequence number into the receiver's flag array behind its data (same
