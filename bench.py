@@ -243,8 +243,8 @@ def main():
                     help="N>1: exchanges by NCCL all-to-all or by peer copies (copy engines) through CUDA IPC")
     ap.add_argument("--zipf-strength", type=float, default=1.0,
                     help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
-    ap.add_argument("--ep-split", type=int, default=0,
-                    help="N>1, p2p transport: 1 = GEMMs over a rank's own rows run apart from those over the other ranks' rows")
+    ap.add_argument("--ep-split", type=int, default=1,
+                    help="N>1, p2p transport: 1 (default) = GEMMs over a rank's own rows run apart from those over the other ranks' rows; 0 = one GEMM pass per chunk")
     ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
