@@ -739,7 +739,7 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
   if (T == 0) return B200MOE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int d = h->cfg.d_model, E = h->cfg.experts;
-  // Large chunks are cut into up to four token ranges: the copy of range c+1 to the device
+  // Large chunks are cut into up to four token ranges (of unequal size, see below): the copy of range c+1 to the device
   // and the copy of range c-1 back run on their own streams while range c computes. A
   // token's result does not depend on which other tokens share its call, so the output is
   // the same as for one call. B200MOE_HOST_CHUNKS overrides the number of ranges.
@@ -763,15 +763,33 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
     if (int s = b200moe_forward(h, layer, h->x_stage, T, h->logits_stage, h->out_stage, stream)) return s;
     CU_TRY(h, cudaMemcpyAsync(out_bf16_host, h->out_stage, xb, cudaMemcpyDeviceToHost, st));
   } else {
-    const int per = (T + C - 1) / C;
+    // range boundaries. Four ranges are cut 1/8, 2/8, 4/8, 1/8: a short first range puts the first
+    // GEMMs behind a short copy, every later copy in is about as long as the compute it hides
+    // behind (copying a token in takes about half as long as computing it), and the last range
+    // -- whose copy out nothing hides -- is short again. Otherwise equal ranges.
+    int off[b200moe_ctx::kHostChunks + 1];
+    for (int c = 0; c <= C; c++) off[c] = (int)((long long)T * c / C);
+    if (C == 4 && forced <= 0) {
+      int w[4] = {1, 2, 4, 1};
+      if (const char* sp = getenv("B200MOE_HOST_SPLIT")) {  // tuning aid: four weights that add up to 8
+        int v[4];
+        if (sscanf(sp, "%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3]) == 4 && v[0] > 0 && v[1] > 0 && v[2] > 0 && v[3] > 0 &&
+            v[0] + v[1] + v[2] + v[3] == 8)
+          for (int i = 0; i < 4; i++) w[i] = v[i];
+      }
+      const int eighth = T / 8;
+      off[1] = w[0] * eighth;
+      off[2] = off[1] + w[1] * eighth;
+      off[3] = off[2] + w[2] * eighth;
+    }
     // the copy streams start after whatever the caller's stream has queued (the staging
     // buffers may still be in use by an earlier call)
     CU_TRY(h, cudaEventRecord(h->ev_start, st));
     CU_TRY(h, cudaStreamWaitEvent(h->s_in, h->ev_start, 0));
     CU_TRY(h, cudaStreamWaitEvent(h->s_out, h->ev_start, 0));
     for (int c = 0; c < C; c++) {
-      const int a = c * per, n = std::min(per, T - a);
-      if (n <= 0) break;
+      const int a = off[c], n = off[c + 1] - a;
+      if (n <= 0) continue;
       CU_TRY(h, cudaMemcpyAsync((uint8_t*)h->x_stage + (size_t)a * d * 2, (const uint8_t*)x_bf16_host + (size_t)a * d * 2,
                                 (size_t)n * d * 2, cudaMemcpyHostToDevice, h->s_in));
       CU_TRY(h, cudaMemcpyAsync(h->logits_stage + (size_t)a * E, logits_host + (size_t)a * E, (size_t)n * E * 4,
@@ -779,8 +797,8 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
       CU_TRY(h, cudaEventRecord(h->ev_in[c], h->s_in));
     }
     for (int c = 0; c < C; c++) {
-      const int a = c * per, n = std::min(per, T - a);
-      if (n <= 0) break;
+      const int a = off[c], n = off[c + 1] - a;
+      if (n <= 0) continue;
       CU_TRY(h, cudaStreamWaitEvent(st, h->ev_in[c], 0));
       if (int s = b200moe_forward(h, layer, (uint8_t*)h->x_stage + (size_t)a * d * 2, n, h->logits_stage + (size_t)a * E,
                                   (uint8_t*)h->out_stage + (size_t)a * d * 2, stream))
@@ -793,7 +811,7 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
     }
     // the caller's stream ends after the last copy back (the copies of one stream are ordered)
     for (int c = C - 1; c >= 0; c--)
-      if (c * per < T) {
+      if (off[c + 1] > off[c]) {
         CU_TRY(h, cudaStreamWaitEvent(st, h->ev_out[c], 0));
         break;
       }
