@@ -1,0 +1,99 @@
+"""The expert-parallel phases of the library (b200moe_ep_route / ep_experts(_part) / ep_combine) on ONE
+GPU: the ranks are handles of one process that run one after the other, and the two exchanges are plain
+device copies laid out by ep.p2p_plan -- the copy lists the multi-GPU transport uses. Nothing waits on
+another rank, so no kernel depends on a concurrent one. The result must equal the single-GPU operator on
+the same tokens up to the order of the combine's additions, and the own-rows / other-rows split must
+give the bytes of the single pass."""
+import numpy as np
+import pytest
+
+import gfx1151_engine_b200 as pkg
+from gfx1151_engine_b200 import ep, synth
+from helpers import bf16_out_to_f32, bf16_tensor, dev_bytes, output_errors
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def run_ranks(torch, spec, layer, xs, lgs, world, split, placement=None):
+    T = xs[0].shape[0]
+    pairs = T * spec.topk
+    cap = world * pairs
+    ops, bufs = [], []
+    for r in range(world):
+        op = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, T, ep_rank=r, ep_size=world)
+        if placement is not None:
+            op.ep_set_placement(np.ascontiguousarray(placement, dtype=np.int32))
+        op.load_q4cp(0, dev_bytes(torch, layer["gate_up"]), dev_bytes(torch, layer["down"]))
+        b = {"x_send": torch.zeros(pairs, spec.d, dtype=torch.float16, device="cuda"),
+             "x_recv": torch.zeros(cap, spec.d, dtype=torch.float16, device="cuda"),
+             "pairs_recv": torch.zeros(cap, spec.d, dtype=torch.float16, device="cuda"),
+             "pairs_back": torch.zeros(pairs, spec.d, dtype=torch.float16, device="cuda"),
+             "eoff": torch.zeros(spec.experts + 1, dtype=torch.int32, device="cuda")}
+        op.ep_attach(b["x_send"], b["x_recv"], b["pairs_recv"], b["pairs_back"], cap)
+        ops.append(op)
+        bufs.append(b)
+    for r in range(world):
+        ops[r].ep_route(0, xs[r], lgs[r], eoff_out=bufs[r]["eoff"])
+    torch.cuda.synchronize()
+    eoff_all = torch.cat([b["eoff"] for b in bufs]).contiguous()
+    eo = eoff_all.cpu().numpy()
+    plans = [ep.p2p_plan(eo, r, world) for r in range(world)]
+    for r in range(world):                      # dispatch
+        for p, src0, dst0, n in plans[r][0]:
+            if n:
+                bufs[p]["x_recv"][dst0:dst0 + n].copy_(bufs[r]["x_send"][src0:src0 + n])
+    for r in range(world):                      # experts
+        if split:
+            ops[r].ep_experts(0, eoff_all, part=2)
+            ops[r].ep_experts(0, eoff_all, part=1)
+        else:
+            ops[r].ep_experts(0, eoff_all)
+    torch.cuda.synchronize()
+    for r in range(world):                      # results back to their owners
+        for s, src0, dst0, n in plans[r][1]:
+            if n:
+                bufs[s]["pairs_back"][dst0:dst0 + n].copy_(bufs[r]["pairs_recv"][src0:src0 + n])
+    outs = []
+    for r in range(world):
+        out = torch.full((T, spec.d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops[r].ep_combine(out, T)
+        ops[r].synchronize()
+        outs.append(bf16_out_to_f32(torch, out))
+    return outs, [p[2] for p in plans]
+
+
+@pytest.mark.parametrize("world,placed", [(2, False), (4, True)])
+def test_ep_phases_match_single_gpu(cuda, world, placed):
+    torch = cuda
+    spec = synth.LayerSpec(experts=16, topk=4, d=512, mid=128)
+    layer = synth.make_layer(spec, seed=120)
+    T = 300
+    placement = None
+    if placed:
+        placement = synth.rng_for(120, 50).permutation(spec.experts)
+    xs, lgs, want = [], [], []
+    single = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, T)
+    single.load_q4cp(0, dev_bytes(torch, layer["gate_up"]), dev_bytes(torch, layer["down"]))
+    for r in range(world):
+        xb = synth.make_x(synth.rng_for(120, 10 + r), T, spec.d)
+        lg = synth.make_logits(synth.rng_for(120, 20 + r), T, spec.experts, zipf=True, zipf_rng=synth.rng_for(120, 77))
+        xs.append(bf16_tensor(torch, xb, (T, spec.d)))
+        lgs.append(torch.from_numpy(np.ascontiguousarray(lg, np.float32)).cuda())
+        out = torch.empty((T, spec.d), dtype=torch.bfloat16, device="cuda")
+        single.moe_b(0, xs[r], lgs[r], out)
+        single.synchronize()
+        want.append(bf16_out_to_f32(torch, out))
+    plain, recv = run_ranks(torch, spec, layer, xs, lgs, world, split=False, placement=placement)
+    assert sum(recv) == world * T * spec.topk          # every pair lands on exactly one rank
+    for r in range(world):
+        assert np.isfinite(plain[r]).all()
+        max_abs, mean_rel = output_errors(plain[r], want[r])
+        # same products and fp32 accumulators; only the combine adds in placed-id order
+        assert max_abs <= 4e-3 and mean_rel <= 1e-5, (r, max_abs, mean_rel)
+    halves, _ = run_ranks(torch, spec, layer, xs, lgs, world, split=True, placement=placement)
+    for r in range(world):
+        assert np.array_equal(bits(halves[r]), bits(plain[r]))
