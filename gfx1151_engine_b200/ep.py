@@ -166,6 +166,10 @@ class ExpertParallelMoe:
         main = torch.cuda.current_stream()
         C = min(self.chunks, (T + self.tc - 1) // self.tc)
         span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
+        # my own result copies of the previous forward read pairs_recv: with the own-rows pass first,
+        # nothing else orders them before this forward's first GEMM writes that buffer
+        if getattr(self, "_back_done", None) is not None:
+            main.wait_event(self._back_done)
         self.seq += 1
         if self.seq >= (1 << 16):
             raise RuntimeError("sequence numbers of the copy-engine transport exhausted")
@@ -246,6 +250,8 @@ class ExpertParallelMoe:
             B = self.buf[c]
             self.ops[c].ep_wait_flags(B["flags"][1], self.world, seq, stream=main)
             self.ops[c].ep_combine(out[a:b], b - a, stream=main)
+        self._back_done = torch.cuda.Event()
+        self._back_done.record(self.comm2)
 
     def load_q4cp(self, layer, gate_up, down):
         """Every rank passes the full tensors; the library keeps this rank's experts."""
