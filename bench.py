@@ -158,19 +158,46 @@ def zipf_logits(torch, T, gen, seed):
 
 
 # ------------------------------------------------------------------ CPU legs
-def cpu_leg(kind, layer_host, x_bits, logits, n_tokens, threads):
-    """Times the CPU implementation on the first n_tokens of the workload. Returns tokens/s."""
+def cpu_leg(layer_host, x_bits, logits, threads, spec=None):
+    """Runs and times the CPU oracle on the given tokens of the workload.
+    Returns (tokens/s, y[n][d] f32, ids[n][16])."""
     import oracle
     from gfx1151_engine_b200 import synth
-    spec = synth.CONFIG3
-    x = synth.bf16_bits_to_f32(x_bits[:n_tokens])
+    spec = spec or synth.CONFIG3
+    x = synth.bf16_bits_to_f32(x_bits)
     t0 = time.perf_counter()
-    if kind == "reference":
-        import dataclasses
-        oracle.ref_moe_layer(dataclasses.replace(spec, shared=True), layer_host, x, threads=threads)
-    else:
-        oracle.moe_forward(spec, layer_host, x, logits=logits[:n_tokens], threads=threads)
-    return n_tokens / (time.perf_counter() - t0)
+    y, ids, _ = oracle.moe_forward(spec, layer_host, x, logits=logits, threads=threads)
+    return x.shape[0] / (time.perf_counter() - t0), y, ids
+
+
+def parity(y_gpu_f32, y_ref_f32, ids_gpu, ids_ref, k):
+    """The CUDA result against the CPU oracle on the same tokens, both rounded to bf16."""
+    from gfx1151_engine_b200 import synth
+    ref = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(y_ref_f32)).astype(np.float64)
+    diff = np.abs(y_gpu_f32.astype(np.float64) - ref)
+    max_abs, mean_rel = float(diff.max()), float(diff.mean() / max(np.abs(ref).mean(), 1e-30))
+    ids_equal = bool(np.array_equal(ids_gpu[:, :k], ids_ref[:, :k]))
+    return {"tokens": int(ref.shape[0]), "max_abs": max_abs, "mean_rel": mean_rel, "ids_equal": ids_equal,
+            "tolerance": {"max_abs": 2e-2, "mean_rel": 1e-3},
+            "ok": bool(ids_equal and max_abs <= 2e-2 and mean_rel <= 1e-3 and np.isfinite(y_gpu_f32).all())}
+
+
+def stratified_tokens(ids, k, n, seed=5):
+    """n token indices of the chunk: a third with a pair on the most loaded expert, a third with
+    a pair on a single-row expert (as far as such tokens exist), the rest at random."""
+    rng = np.random.Generator(np.random.Philox(key=[seed, 0]))
+    T = ids.shape[0]
+    hist = np.bincount(ids[:, :k].reshape(-1), minlength=E)
+    on_hot = np.flatnonzero((ids[:, :k] == int(np.argmax(hist))).any(axis=1))
+    on_single = np.flatnonzero(np.isin(ids[:, :k], np.flatnonzero(hist == 1)).any(axis=1))
+    pick = set(int(t) for t in rng.permutation(on_hot)[: n // 3])
+    pick |= set(int(t) for t in rng.permutation(on_single)[: n // 3])
+    for t in rng.permutation(T):
+        if len(pick) >= n:
+            break
+        pick.add(int(t))
+    sel = np.array(sorted(pick), dtype=np.int64)
+    return sel, {"on_most_loaded_expert": int(np.isin(sel, on_hot).sum()), "on_single_row_experts": int(np.isin(sel, on_single).sum())}
 
 
 def reference_arm(args):
@@ -245,7 +272,9 @@ def main():
                     help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
     ap.add_argument("--ep-split", type=int, default=1,
                     help="N>1, p2p transport: 1 (default) = GEMMs over a rank's own rows run apart from those over the other ranks' rows; 0 = one GEMM pass per chunk")
-    ap.add_argument("--check", action="store_true", help="N>1: compare rank 0's output with the single-GPU operator")
+    ap.add_argument("--check", type=int, default=1,
+                    help="N>1: 1 (default) = compare rank 0's output with the single-GPU operator on the same tokens; 0 = skip")
+    ap.add_argument("--no-gguf", action="store_true", help="skip the GGUF-variant leg (Q4_K gate/up, Q5_1 down, 8192 tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode / verify measurements")
     ap.add_argument("--decode-only", action="store_true",
@@ -315,14 +344,18 @@ def main():
         op_dec.load_q4cp(0, gu, dn)
         sh = [q4cp_blob_device(torch, MID, D, gen2), q4cp_blob_device(torch, MID, D, gen2),
               q4cp_blob_device(torch, D, MID, gen2)]
-        op_dec.load_shared_q4cp(0, sh[0], sh[1], sh[2],
-                                (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16))
+        sh_gw = (torch.randn(D, device="cuda", generator=gen2) * 0.02).to(torch.bfloat16)
+        op_dec.load_shared_q4cp(0, sh[0], sh[1], sh[2], sh_gw)
+        if layer_host is not None:
+            layer_host.update({"sh_gate": sh[0].cpu().numpy(), "sh_up": sh[1].cpu().numpy(), "sh_down": sh[2].cpu().numpy(),
+                               "sh_gate_w": sh_gw.view(torch.int16).cpu().numpy().view(np.uint16)})
     if args.decode_only and op_dec is not None:
         del gu, dn
-        print(json.dumps({"decode": decode_leg(torch, op_dec, peak_hbm, torch.cuda.current_stream(), graph=True)}))
+        print(json.dumps({"decode": decode_leg(torch, op_dec, peak_hbm, torch.cuda.current_stream(), graph=True,
+                                               layer_host=layer_host)}))
         return
     op_ref = None
-    if world > 1 and args.check and rank == 0:
+    if world > 1 and args.check == 1 and rank == 0:
         op_ref = pkg.MoeOperator(E, K_TOP, D, MID, T, device=local)   # whole layer on one GPU, for the check
         op_ref.load_q4cp(0, gu, dn)
     del gu, dn
@@ -448,7 +481,8 @@ def main():
     else:
         # per GPU, over the whole step including both all-to-all exchanges
         achieved = FLOP_PER_TOKEN * T * args.steps / (ms * 1e-3) / 1e12
-        roof_kernel = "whole expert-parallel step per GPU (grouped GEMMs + NCCL all-to-all)"
+        roof_kernel = ("whole expert-parallel step per GPU (grouped GEMMs + dispatch / combine exchanges by %s)"
+                       % ("peer copies of the copy engines" if args.transport == "p2p" else "NCCL all-to-all"))
         stages = {}
     result = {
         "metric": "moe_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -471,7 +505,7 @@ def main():
     }
 
     if op_dec is not None:
-        result["decode"] = decode_leg(torch, op_dec, peak_hbm, stream)
+        result["decode"] = decode_leg(torch, op_dec, peak_hbm, stream, layer_host=layer_host)
     if world == 1 and not gguf:
         # the step in front of the path: router logits from hidden states (random router weight)
         gw = torch.Generator(device="cuda")
@@ -490,21 +524,71 @@ def main():
         result["router_from_hidden"] = {"ms": rms, "tflops": 2.0 * T * E * D / (rms * 1e-3) / 1e12,
                                         "what": "b200moe_router_logits: bf16 tcgen05 GEMM + near-tie recomputation in the reference's arithmetic; not part of `value`"}
     if want_cpu:
+        # The CPU oracle on a sample of the very chunk the GPU just computed: its time is the CPU
+        # baseline, its output the parity check of the benchmarked call (`out` still holds the
+        # result of the last timed step).
         cores = os.cpu_count() or 1
-        n_tok = max(cores, 8) * 4
-        xb = x[:n_tok].view(torch.int16).cpu().numpy().view(np.uint16)
-        lg = logits[:n_tok].cpu().numpy()
-        v = cpu_leg("port", layer_host, xb, lg, n_tok, cores)
+        n_tok = max(64, min(256, cores * 8))
+        ids_gpu = op.get_routing(T)[0]
+        sel, strata = stratified_tokens(ids_gpu, K_TOP, n_tok)
+        sel_dev = torch.from_numpy(sel).cuda()
+        xb = x[sel_dev].view(torch.int16).cpu().numpy().view(np.uint16)
+        lg = logits[sel_dev].cpu().numpy()
+        v, y_ref, ids_ref = cpu_leg(layer_host, xb, lg, cores)
         result["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                  "sample": "first %d tokens of the same chunk, CPU oracle with OpenMP over tokens" % n_tok}
+                                  "sample": "%d tokens of the same chunk (stratified: hot-expert, single-row-expert and random tokens), "
+                                            "CPU oracle with OpenMP over tokens" % len(sel)}
+        result["parity"] = parity(out[sel_dev].float().cpu().numpy(), y_ref, ids_gpu[sel], ids_ref, K_TOP)
+        result["parity"].update(strata)
+        result["parity"]["what"] = "output of the timed 16384-token call against the CPU oracle on a stratified token sample, both rounded to bf16"
+    if world == 1 and not gguf and not args.no_gguf and (E, T) == (512, T_CHUNK):
+        op.close()
+        del op
+        torch.cuda.empty_cache()
+        result["gguf"] = gguf_leg(torch, pkg, peak_tf, stream, local)
     print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
 
 
-def decode_leg(torch, op, peak_hbm, stream, graph=True):
+def gguf_leg(torch, pkg, peak_tf, stream, device, T=8192, steps=10):
+    """configs[3]: the GGUF variant of the layer (Q4_K gate/up, Q5_1 down) at 8192 tokens."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4321)
+    gate = gguf_blocks_device(torch, E * MID, D, "q4k", gen)
+    up = gguf_blocks_device(torch, E * MID, D, "q4k", gen)
+    dn = gguf_blocks_device(torch, E * D, MID, "q51", gen)
+    op = pkg.MoeOperator(E, K_TOP, D, MID, T, device=device)
+    op.load_gguf(0, gate, up, dn)
+    del gate, up, dn
+    torch.cuda.empty_cache()
+    x = torch.randn(T, D, device="cuda", generator=gen).to(torch.bfloat16)
+    logits = zipf_logits(torch, T, gen, 0)
+    out = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        op.moe_b(0, x, logits, out, stream=stream)
+    op.synchronize(stream)
+    op.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        op.moe_b(0, x, logits, out, stream=stream)
+    e1.record(stream)
+    op.synchronize(stream)
+    ms = e0.elapsed_time(e1) / steps
+    stages = op.profile_read()
+    op.close()
+    tf = FLOP_PER_TOKEN * T / (ms * 1e-3) / 1e12
+    return {"workload": "config4: 8192-token prefill, Q4_K gate/up + Q5_1 down, same layer shapes and routing bias",
+            "ms": ms, "tokens_per_s": T / (ms * 1e-3), "tflops": tf, "frac": tf / peak_tf,
+            "stage_ms": {k: round(v, 4) for k, v in stages.items() if k != "calls"},
+            "finite": bool(torch.isfinite(out.float()).all().item())}
+
+
+def decode_leg(torch, op, peak_hbm, stream, graph=True, layer_host=None):
     """configs[1]: T = 1 and T = 5 with the shared expert; 64 rotated routings so that the
-    selected experts are not resident in L2 from the previous call."""
+    selected experts are not resident in L2 from the previous call. With the layer's host
+    copy, the first routing of each T is also checked against the CPU oracle."""
     out = {}
     gen = torch.Generator(device="cuda")
     gen.manual_seed(7)
@@ -516,6 +600,14 @@ def decode_leg(torch, op, peak_hbm, stream, graph=True):
         for i in range(8):
             op.moe_b(0, xs[i], lgs[i], o, stream=stream)
         op.synchronize(stream)
+        par = None
+        if layer_host is not None and "sh_gate" in layer_host:
+            from gfx1151_engine_b200 import synth
+            op.moe_b(0, xs[0], lgs[0], o, stream=stream)
+            op.synchronize(stream)
+            _, y_ref, ids_ref = cpu_leg(layer_host, xs[0].view(torch.int16).cpu().numpy().view(np.uint16),
+                                        lgs[0].cpu().numpy(), os.cpu_count() or 1, spec=synth.CONFIG2)
+            par = parity(o.float().cpu().numpy(), y_ref, op.get_routing(T)[0], ids_ref, K_TOP)
         uniq = []
         for i in range(sets):
             ids = torch.topk(lgs[i], K_TOP, dim=1).indices
@@ -554,7 +646,8 @@ def decode_leg(torch, op, peak_hbm, stream, graph=True):
         out["T%d" % T] = {"us_per_call": us, "us_per_token": us / T, "unique_experts": float(np.mean(uniq)),
                           "algorithmic_bytes": nbytes, "hbm_gbs": gbs, "frac_of_hbm_peak": gbs / peak_hbm,
                           "timing": "CUDA graph replay of 64 rotated routings" if graph else "eager launches, stage timer",
-                          "stage_us_eager": {k: round(v * 1e3, 2) for k, v in stages.items() if k != "calls"}}
+                          "stage_us_eager": {k: round(v * 1e3, 2) for k, v in stages.items() if k != "calls"},
+                          "parity": par}
     return out
 
 

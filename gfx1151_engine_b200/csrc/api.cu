@@ -161,6 +161,25 @@ SrcTensor q4cp_src(const uint8_t* blob, long long rows_total, long long cols,
   return s;
 }
 
+// Turns the device status word (copied to status_host) into a return code and clears it on the
+// device. {1|2|3, site}: a bounded device-side wait gave up; {4, id}: a caller-supplied expert
+// id outside [0, experts) was dropped by the bucketing.
+int report_status(b200moe_handle h, cudaStream_t st) {
+  const int code = h->status_host[0], detail = h->status_host[1];
+  if (code == 0) return B200MOE_OK;
+  cudaError_t e = cudaMemsetAsync(h->status_dev, 0, 16, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(h, B200MOE_ERR_CUDA, std::string("clearing the status word: ") + cudaGetErrorString(e));
+  char buf[160];
+  if (code == 4) {
+    snprintf(buf, sizeof buf, "expert id %d outside [0, %d) in the caller's top-k ids: the pair was dropped", detail,
+             h->cfg.experts);
+    return fail(h, B200MOE_ERR_BAD_ARG, buf);
+  }
+  snprintf(buf, sizeof buf, "device-side wait timed out (code %d, wait site %d)", code, detail);
+  return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
+}
+
 int check_layer(b200moe_handle h, int layer) {
   if (!h) return B200MOE_ERR_BAD_ARG;
   if (layer < 0 || layer >= (int)h->layers.size())
@@ -255,6 +274,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   A((uint8_t**)&h->out_stage, (size_t)Tm * d * 2);
   A(&h->logits_stage, (size_t)Tm * E);
   A(&h->status_dev, 4);
+  h->rb.status = h->status_dev;
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 16);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->status_host, 16);
   if (e == cudaSuccess && !simt_all)
@@ -818,13 +838,7 @@ int b200moe_forward_host(b200moe_handle h, int layer, const void* x_bf16_host, i
   }
   CU_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost, st));
   CU_TRY(h, cudaStreamSynchronize(st));
-  if (h->status_host[0] != 0) {
-    char buf[128];
-    snprintf(buf, sizeof buf, "device-side wait timed out (code %d, detail %d)", h->status_host[0],
-             h->status_host[1]);
-    return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
-  }
-  return B200MOE_OK;
+  return report_status(h, st);  // also clears the condition, as b200moe_synchronize does
 }
 
 int b200moe_debug_get_routing(b200moe_handle h, int T, int32_t* topids_host, float* topw_host,
@@ -840,8 +854,7 @@ int b200moe_debug_get_routing(b200moe_handle h, int T, int32_t* topids_host, flo
   if (eoff_host) CU_TRY(h, cudaMemcpy(eoff_host, h->rb.eoff, ((size_t)h->cfg.experts + 1) * 4, cudaMemcpyDeviceToHost));
   if (pairids_host) CU_TRY(h, cudaMemcpy(pairids_host, h->rb.pairids, pairs * 4, cudaMemcpyDeviceToHost));
   CU_TRY(h, cudaMemcpy(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost));
-  if (h->status_host[0] != 0) return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, "device-side wait timed out");
-  return B200MOE_OK;
+  return report_status(h, nullptr);
 }
 
 int b200moe_profile_enable(b200moe_handle h, int on) {
@@ -912,6 +925,7 @@ int b200moe_share_weights(b200moe_handle h, b200moe_handle owner) {
       free_image(L.sh_gu);
       free_image(L.sh_dn);
       if (L.sh_gate_w) cudaFree(L.sh_gate_w);
+      if (L.router_w) cudaFree(L.router_w);
     }
     L = owner->layers[i];
     L.borrowed = true;
@@ -957,7 +971,7 @@ int b200moe_ep_route(b200moe_handle h, int layer, const void* x, int T, const fl
   int n = 0;
   CU_TRY(h, launch_router_topk(logits, T, c.experts, c.topk, h->rb.topids, h->rb.topw, kIdStride, st));
   if (h->place_dev) {
-    CU_TRY(h, launch_apply_placement(h->rb.topids, kIdStride, T, c.topk, h->place_dev, st));
+    CU_TRY(h, launch_apply_placement(h->rb.topids, kIdStride, T, c.topk, c.experts, h->place_dev, st));
     n++;
   }
   CU_TRY(h, launch_route(h->rb, h->rb.topids, h->rb.topw, kIdStride, T, c.topk, c.experts, h->tile_cap, st, &n));
@@ -1016,15 +1030,7 @@ int b200moe_synchronize(b200moe_handle h, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   CU_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 16, cudaMemcpyDeviceToHost, st));
   CU_TRY(h, cudaStreamSynchronize(st));
-  if (h->status_host[0] != 0) {
-    char buf[128];
-    snprintf(buf, sizeof buf, "device-side wait timed out (code %d, wait site %d)", h->status_host[0],
-             h->status_host[1]);
-    CU_TRY(h, cudaMemsetAsync(h->status_dev, 0, 16, st));
-    CU_TRY(h, cudaStreamSynchronize(st));
-    return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
-  }
-  return B200MOE_OK;
+  return report_status(h, st);
 }
 
 int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int row0, int nrows,

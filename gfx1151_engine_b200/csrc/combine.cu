@@ -57,9 +57,10 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
   __shared__ float s_w[kMaxTopK + 1];
   int n = k;
   if (threadIdx.x < k) {
+    // a negative row marks a pair the bucketing dropped (expert id outside [0, E)): it adds nothing
     int row = pairids[(size_t)t * k + threadIdx.x];
     s_row[threadIdx.x] = row;
-    s_w[threadIdx.x] = pw[row];
+    s_w[threadIdx.x] = row >= 0 ? pw[row] : 0.f;
   }
   if (shared_row0 >= 0) {
     if (threadIdx.x == 0) {
@@ -72,6 +73,7 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
   for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < d; c += gridDim.y * blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int s = 0; s < n; s++) {
+      if (s_row[s] < 0) continue;
       float v[8];
       load8(pairs + (size_t)s_row[s] * d + c, v);
       const float w = s_w[s];
@@ -118,8 +120,9 @@ k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
   for (int s = 0; s < kMaxTopK + 1; s++) {
     if (s < n) {
       const int row = s < k ? pairids[(size_t)t * k + s] : shared_row0 + t;
-      w[s] = pw[row];
-      v[s] = *(const float4*)(pairs + (size_t)row * d + c);
+      const bool live = row >= 0;  // negative: a pair the bucketing dropped (expert id outside [0, E))
+      w[s] = live ? pw[row] : 0.f;
+      v[s] = live ? *(const float4*)(pairs + (size_t)row * d + c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -150,8 +153,14 @@ k_combine_small(const float* __restrict__ pairs, const float* __restrict__ pw,
   *(uint2*)(out + (size_t)t * d + c) = o;
 }
 
+// Finite values saturate to the fp16 range; NaN stays NaN (fminf/fmaxf alone would turn it into
+// a finite number and hide a broken activation from the caller).
+__device__ __forceinline__ float clamp_f16_range(float v) {
+  return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f);
+}
+
 // x_sorted[row][:] = fp16(x[tokidx[row]][:]); bf16 -> fp16 is exact for 2^-14 <= |v| < 65520,
-// larger magnitudes saturate to the largest finite half.
+// larger magnitudes (infinities included) saturate to the largest finite half, NaN stays NaN.
 // One warp per row: the token index is read once, a lane keeps four 16-byte loads in flight.
 __global__ void __launch_bounds__(256)
 k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx, int rows, int d,
@@ -175,9 +184,7 @@ k_gather_f16(const uint16_t* __restrict__ x, const int32_t* __restrict__ tokidx,
           __half2* oh = (__half2*)&o;
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            const float f0 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j]), -65504.f), 65504.f);
-            const float f1 = fminf(fmaxf(bf16_bits_to_f32(b[2 * j + 1]), -65504.f), 65504.f);
-            oh[j] = __floats2half2_rn(f0, f1);
+            oh[j] = __floats2half2_rn(clamp_f16_range(bf16_bits_to_f32(b[2 * j])), clamp_f16_range(bf16_bits_to_f32(b[2 * j + 1])));
           }
           dst[v0 + 32 * i] = o;
         }
@@ -210,8 +217,14 @@ cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32
 
 cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
                               __half* x_sorted, cudaStream_t st) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sms * 8) blocks = sms * 8;
   if (blocks < 1) blocks = 1;
   k_gather_f16<<<blocks, 256, 0, st>>>((const uint16_t*)x_bf16, tokidx, rows, d, x_sorted);
   return cudaGetLastError();

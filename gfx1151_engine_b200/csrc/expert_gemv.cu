@@ -110,8 +110,10 @@ __device__ __forceinline__ float chunk_dot5(const uint4 c, uint32_t qh, uint32_t
   return s0 + s1;
 }
 
+// finite values saturate to the fp16 range, NaN stays NaN
+__device__ __forceinline__ float sat_f16(float v) { return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f); }
 __device__ __forceinline__ uint32_t pack_half2_sat(float a, float b) {
-  __half2 h = __floats2half2_rn(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f));
+  __half2 h = __floats2half2_rn(sat_f16(a), sat_f16(b));
   return *(uint32_t*)&h;
 }
 
@@ -335,7 +337,7 @@ k_gemv(const GemvParams p) {
                 const float up = __shfl_down_sync(0xffffffffu, tot, 16);
                 if (lane < 16)
                   p.hid[(size_t)run.first * p.mid + cj * 16 + lane] =
-                      __float2half_rn(fminf(fmaxf(silu_f32(tot) * up, -65504.f), 65504.f));
+                      __float2half_rn(sat_f16(silu_f32(tot) * up));
               }
             } else {
               if (warp < 2) {

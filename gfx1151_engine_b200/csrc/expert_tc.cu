@@ -239,6 +239,9 @@ __device__ __forceinline__ uint32_t instr_desc(int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// finite values saturate to the fp16 range (as on the GEMV path), NaN stays NaN
+__device__ __forceinline__ float sat_f16(float v) { return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f); }
+
 struct KParams {
   Image img;
   const Tile* tiles;
@@ -626,13 +629,13 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
 #pragma unroll
             for (int j = 0; j < 16; j++) {
               const float g = __uint_as_float(v[j]), u = xu[(pq * 16 + j) * 32 + lane];
-              outs[j * 64 + pq * 32 + lane] = __float2half_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+              outs[j * 64 + pq * 32 + lane] = __float2half_rn(sat_f16(__fdividef(g, 1.f + __expf(-g)) * u));
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
               const float u = __uint_as_float(v[16 + j]), g = xg[(pq * 16 + j) * 32 + lane];
-              outs[(16 + j) * 64 + pq * 32 + lane] = __float2half_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+              outs[(16 + j) * 64 + pq * 32 + lane] = __float2half_rn(sat_f16(__fdividef(g, 1.f + __expf(-g)) * u));
             }
           }
           asm volatile("bar.sync 3, 128;" ::: "memory");
@@ -646,7 +649,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         } else {
           __half* outs = (__half*)ubuf;  // [32][128]
 #pragma unroll
-          for (int j = 0; j < 32; j++) outs[j * 128 + e128] = __float2half_rn(__uint_as_float(v[j]));
+          for (int j = 0; j < 32; j++) outs[j * 128 + e128] = __float2half_rn(sat_f16(__uint_as_float(v[j])));
           asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
           for (int k = 0; k < 4; k++) {

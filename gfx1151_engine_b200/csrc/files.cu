@@ -223,23 +223,42 @@ int gguf_find(const Mapping& m, const std::string& name, View* out) {
   return 0;
 }
 
-// NAME-0000i-of-0000n.gguf -> all n shard names; anything else -> the path itself
+// Five decimal digits at s[pos..pos+4] as a number; -1 when one of them is not a digit.
+int five_digits(const std::string& s, size_t pos) {
+  int v = 0;
+  for (size_t i = pos; i < pos + 5; i++) {
+    if (s[i] < '0' || s[i] > '9') return -1;
+    v = v * 10 + (s[i] - '0');
+  }
+  return v;
+}
+
+// A sharded model is a set of files STEM-<i>-of-<n>.gguf, i and n written with five digits,
+// i = 1..n. Given any member, returns the n member names in order; a path that does not end in
+// such a suffix (or whose numbers are inconsistent) is a single file.
 std::vector<std::string> gguf_shards(const std::string& path) {
-  std::vector<std::string> files{path};
-  const size_t p = path.rfind("-of-");
-  if (p != std::string::npos && p >= 6 && path.size() == p + 4 + 5 + 5 && path.compare(path.size() - 5, 5, ".gguf") == 0) {
-    const int n = atoi(path.substr(p + 4, 5).c_str());
-    if (n >= 1 && n < 100000) {
-      const std::string stem = path.substr(0, p - 5);
-      files.clear();
-      for (int i = 1; i <= n; i++) {
-        char buf[32];
-        snprintf(buf, sizeof buf, "%05d-of-%05d.gguf", i, n);
-        files.push_back(stem + buf);
+  constexpr size_t kTail = 5 + 4 + 5 + 5;  // "00001" "-of-" "00003" ".gguf"
+  if (path.size() > kTail) {
+    const size_t t = path.size() - kTail;  // where the shard number starts
+    const int i = five_digits(path, t), n = five_digits(path, t + 9);
+    if (path[t - 1] == '-' && path.compare(t + 5, 4, "-of-") == 0 && path.compare(t + 14, 5, ".gguf") == 0 &&
+        i >= 1 && n >= 1 && i <= n) {
+      std::vector<std::string> all;
+      const std::string stem = path.substr(0, t);
+      for (int k = 1; k <= n; k++) {
+        char tail[24];
+        snprintf(tail, sizeof tail, "%05d-of-%05d.gguf", k, n);
+        all.push_back(stem + tail);
       }
+      return all;
     }
   }
-  return files;
+  return std::vector<std::string>{path};
+}
+
+// bytes of a q4cp blob [rows, cols]: code book, codes, per-row scale records padded to 16 bytes (src/hgn.h:219-238)
+uint64_t q4cp_blob_bytes(uint64_t rows, uint64_t cols) {
+  return 64 + rows * cols / 2 + rows * (((cols / 32 * 2) + 15) & ~(uint64_t)15);
 }
 
 std::string layer_name(const char* fmt, int layer) {
@@ -273,6 +292,14 @@ extern "C" int b200moe_load_hgn_file(b200moe_handle h, int layer, const char* pa
         hgn_find(m, layer_name("layers.%d.mlp.shared_expert_gate.weight", model_layer), &sw))
       return B200MOE_ERR_BAD_ARG;
     if (sg.dtype != 5 || su.dtype != 5 || sd.dtype != 5 || sw.dtype != 0 || sw.size < d * 2) return B200MOE_ERR_UNSUPPORTED;
+    // b200moe_load_shared_q4cp takes no sizes and reads whole [mid,d] / [d,mid] blobs: the
+    // mapped tensors must have exactly that shape and size
+    const uint64_t gu_b = q4cp_blob_bytes(mid, d), dn_b = q4cp_blob_bytes(d, mid);
+    if (sg.ndims != 2 || su.ndims != 2 || sd.ndims != 2 || sg.dims[0] != mid || sg.dims[1] != d || su.dims[0] != mid ||
+        su.dims[1] != d || sd.dims[0] != d || sd.dims[1] != mid)
+      return B200MOE_ERR_UNSUPPORTED;
+    if (sg.size != gu_b || su.size != gu_b || sd.size != dn_b) return B200MOE_ERR_BAD_ARG;
+    if (((uintptr_t)sg.data | (uintptr_t)su.data | (uintptr_t)sd.data) & 15) return B200MOE_ERR_BAD_ARG;
     if (int s = b200moe_load_shared_q4cp(h, layer, sg.data, su.data, sd.data, sw.data)) return s;
   }
   View rw;

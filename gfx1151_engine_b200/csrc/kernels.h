@@ -73,6 +73,7 @@ struct RouteBuffers {
   Tile* tiles_sh;    // work list of the shared expert (all T tokens)
   int32_t* n_tiles;  // [2]: routed, shared
   float* sgate;      // [T] sigmoid gate of the shared expert
+  int32_t* status;   // the handle's status word (may be null): {4, id} when an expert id outside [0, E) was dropped
 };
 cudaError_t launch_router_topk(const float* logits, int T, int E, int k, int32_t* ids, float* w,
                                int stride, cudaStream_t st);
@@ -87,7 +88,7 @@ cudaError_t launch_route_small(const RouteBuffers& rb, const float* logits, cons
 cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, int T, int d,
                                int k, const RouteBuffers& rb, cudaStream_t st);
 
-cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, const int32_t* place,
+cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E, const int32_t* place,
                                    cudaStream_t st);
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
                             Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st,

@@ -19,6 +19,8 @@ namespace b200moe {
 namespace {
 
 constexpr int kRouterWarps = 8;
+constexpr int kBadKey = 0x7fffffff;   // sort key of a dropped pair (expert id outside [0, E))
+constexpr int kStatusBadId = 4;       // status word {4, offending id}: reported as B200MOE_ERR_BAD_ARG
 constexpr int kChunk = 512;  // pairs handled by one single-warp block of the bucketing kernels
 
 __device__ __forceinline__ double shfl_double(double v, int src) {
@@ -91,8 +93,12 @@ __device__ __forceinline__ void router_one_token(const float* __restrict__ lg, i
   float my_p = 0.f;
   double kept = 0;
   for (int r = 0; r < k; r++) {
+    // The search starts from an id inside [0, E) (the reference's GPU router starts at `lane`,
+    // src/gpu/parts/20_kernels_gemv.inc:1517): with a non-finite logit every probability is NaN, no
+    // comparison below is ever true, and the ids written are then still valid expert numbers
+    // (with NaN weights, so the token's output is NaN) instead of an out-of-range value.
     float bv = -1.f;
-    int bi = 0x7fffffff;
+    int bi = min(lane, E - 1);
 #pragma unroll
     for (int j = 0; j < 16; j++)
       if (v[j] > bv) {
@@ -108,6 +114,9 @@ __device__ __forceinline__ void router_one_token(const float* __restrict__ lg, i
         bi = oi;
       }
     }
+    bi = __shfl_sync(0xffffffffu, bi, 0);  // (NaN probabilities: the lanes may disagree; take lane 0's)
+    bv = __shfl_sync(0xffffffffu, bv, 0);
+    if (bv < 0.f) bv = __int_as_float(0x7fc00000);  // nothing was selectable: the weight is NaN, as in the reference
 #pragma unroll
     for (int j = 0; j < 16; j++)
       if (j == (bi >> 5) && lane == (bi & 31)) v[j] = -1.f;
@@ -300,6 +309,12 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
       for (int o = 16; o; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
       if (lane == 0) s_bv[0][warp] = wm;
       if (tid == 0) s_wcnt[16] = 0;
+      if (tid < k) {
+        // non-finite logits make every probability NaN and no candidate is ever ranked: the
+        // selection then stays at these in-range ids with NaN weights
+        s_key[tid] = tid;
+        s_w[tid] = __int_as_float(0x7fc00000);
+      }
       __syncthreads();
       if (warp == 0) {
         const float m = lane < 16 ? s_bv[0][lane] : -1.f;
@@ -310,7 +325,7 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
           rank += (o > m) || (o == m && i < lane);
         }
         const unsigned hit = __ballot_sync(0xffffffffu, lane < 16 && rank == min(k, 16) - 1);
-        const float bound = __shfl_sync(0xffffffffu, m, __ffs(hit) - 1);
+        const float bound = hit ? __shfl_sync(0xffffffffu, m, __ffs(hit) - 1) : __int_as_float(0x7fc00000);
         if (lane == 0) s_bv[1][0] = bound;
       }
       __syncthreads();
@@ -349,7 +364,7 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
       // k rounds of arg-max over the group's values: lanes, then the group's warps
       for (int r = 0; r < k; r++) {
         float bv = -1.f;
-        int bi = 0x7fffffff;
+        int bi = min(wq * 32 + lane, E - 1);  // an id inside [0, E) even when nothing compares greater (NaN)
 #pragma unroll
         for (int j = 0; j < 16; j++)
           if (v[j] > bv) {  // ascending expert id within a lane: the first maximum is the lowest id
@@ -373,7 +388,7 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
           __syncthreads();
           // lane l < W takes the candidate of the group's warp l; W <= 8 lanes are merged
           bv = lane < W ? s_bv[r & 1][ts * W + lane] : -1.f;
-          bi = lane < W ? s_bi[r & 1][ts * W + lane] : 0x7fffffff;
+          bi = lane < W ? s_bi[r & 1][ts * W + lane] : s_bi[r & 1][ts * W];
 #pragma unroll
           for (int o = 4; o; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -383,9 +398,10 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
               bi = oi;
             }
           }
-          bv = __shfl_sync(0xffffffffu, bv, 0);
-          bi = __shfl_sync(0xffffffffu, bi, 0);
         }
+        bv = __shfl_sync(0xffffffffu, bv, 0);  // (with NaN probabilities the lanes may disagree: take lane 0's)
+        bi = __shfl_sync(0xffffffffu, bi, 0);
+        if (bv < 0.f) bv = __int_as_float(0x7fc00000);  // nothing was selectable: the weight is NaN
 #pragma unroll
         for (int j = 0; j < 16; j++)
           if ((j * W + wq) * 32 + lane == bi) v[j] = -1.f;
@@ -410,23 +426,32 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
     }
   } else {
     for (int p = tid; p < P; p += blockDim.x) {
-      s_key[p] = ids_in[(size_t)(p / k) * stride_in + p % k];
+      // a caller-supplied id outside [0, E) must never index anything: the pair is dropped
+      // (key kBadKey sorts behind every expert) and the status word records it
+      const int id = ids_in[(size_t)(p / k) * stride_in + p % k];
+      const bool bad = (unsigned)id >= (unsigned)E;
+      if (bad && rb.status && atomicCAS(rb.status, 0, kStatusBadId) == 0) rb.status[1] = id;
+      s_key[p] = bad ? kBadKey : id;
       s_w[p] = w_in[(size_t)(p / k) * stride_in + p % k];
     }
   }
   __syncthreads();
   // pair p -> row = number of pairs ordered before it by (expert, p)
+  int n_bad = 0;
   if (tid < P) {
     const int key = s_key[tid], t = tid / k;
     int row = 0, rank = 0;
     for (int q = 0; q < P; q++) {
       const int kq = s_key[q];
       row += (kq < key) || (kq == key && q < tid);
+      n_bad += kq == kBadKey;
     }
-    for (int q = t * k; q < t * k + k; q++) rank += s_key[q] < key;
+    // slot of the pair in the token's reduce order: ascending expert id; equal ids (a caller's
+    // duplicate, or two dropped pairs) keep their slot order, so every slot is written
+    for (int q = t * k; q < t * k + k; q++) rank += (s_key[q] < key) || (s_key[q] == key && q < tid);
     rb.tokidx[row] = t;
     rb.pw[row] = s_w[tid];
-    rb.pairids[(size_t)t * k + rank] = row;
+    rb.pairids[(size_t)t * k + rank] = key == kBadKey ? -1 : row;  // the combine skips negative rows
   }
   // expert e: offset, count, position among the non-empty experts
   int cnt = 0, lt = 0;
@@ -450,7 +475,7 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
     rb.tiles[before] = Tile{tid, lt, cnt};
   }
   if (tid == 0) {
-    rb.eoff[E] = P;
+    rb.eoff[E] = P - n_bad;  // pairs actually placed (thread 0 counted the dropped ones above)
     rb.n_runs[0] = n_active;
     rb.n_runs[1] = 1;
     rb.runs[kMaxExperts] = Run{0, P, T};
@@ -462,7 +487,7 @@ k_route_small(const float* __restrict__ logits, const int32_t* __restrict__ ids_
 
 __global__ void __launch_bounds__(32)
 k_route_count(const int32_t* __restrict__ ids, int stride, int pairs, int k, int E,
-              int32_t* __restrict__ blockcnt) {
+              int32_t* __restrict__ blockcnt, int32_t* __restrict__ status) {
   __shared__ int hist[kMaxExperts];
   const int lane = threadIdx.x;
   for (int e = lane; e < E; e += 32) hist[e] = 0;
@@ -470,7 +495,11 @@ k_route_count(const int32_t* __restrict__ ids, int stride, int pairs, int k, int
   const int base = blockIdx.x * kChunk;
   for (int it = 0; it < kChunk / 32; it++) {
     int p = base + it * 32 + lane;
-    if (p < pairs) atomicAdd(&hist[ids[(size_t)(p / k) * stride + p % k]], 1);
+    if (p < pairs) {
+      const int e = ids[(size_t)(p / k) * stride + p % k];
+      if ((unsigned)e < (unsigned)E) atomicAdd(&hist[e], 1);  // ids outside [0, E) are dropped, never used as an index
+      else if (status && atomicCAS(status, 0, kStatusBadId) == 0) status[1] = e;
+    }
   }
   __syncwarp();
   for (int e = lane; e < E; e += 32) blockcnt[(size_t)blockIdx.x * E + e] = hist[e];
@@ -524,7 +553,7 @@ k_route_scan(int32_t* __restrict__ blockcnt, int nblk, int E, int pairs, int T, 
   const int total_full = s_c[kMaxExperts - 1];
   if (e < E) eoff[e] = first;
   if (e == 0) {
-    eoff[E] = pairs;
+    eoff[E] = s_a[kMaxExperts - 1];  // pairs placed (= T*k unless ids outside [0, E) were dropped)
     n_runs[0] = s_b[kMaxExperts - 1];
     n_runs[1] = 1;  // the shared expert's run, kept at runs[kMaxExperts]
     runs[kMaxExperts] = Run{0, pairs, T};
@@ -569,20 +598,30 @@ k_route_place(const int32_t* __restrict__ ids, const float* __restrict__ w, int 
     if (live) {
       const int t = p / k, s = p % k;
       const int e = ids[(size_t)t * stride + s];
-      const unsigned same = __match_any_sync(act, e);
+      const bool good = (unsigned)e < (unsigned)E;
+      const unsigned same = __match_any_sync(act, good ? e : -1);
       const int leader = __ffs(same) - 1;
       int start = 0;
-      if (lane == leader) {
+      if (good && lane == leader) {
         start = cursor[e];
         cursor[e] = start + __popc(same);
       }
       start = __shfl_sync(same, start, leader);
       const int row = start + __popc(same & ((1u << lane) - 1u));
-      tokidx[row] = t;
-      pw[row] = w[(size_t)t * stride + s];
+      if (good) {
+        tokidx[row] = t;
+        pw[row] = w[(size_t)t * stride + s];
+      }
+      // slot in the token's reduce order: ascending expert id; equal ids keep their slot order,
+      // so every slot is written; a dropped pair's slot holds -1 (the combine skips it)
       int rank = 0;
-      for (int q = 0; q < k; q++) rank += ids[(size_t)t * stride + q] < e;
-      pairids[(size_t)t * k + rank] = row;
+      const int key = good ? e : kBadKey;
+      for (int q = 0; q < k; q++) {
+        const int eq = ids[(size_t)t * stride + q];
+        const int kq = (unsigned)eq < (unsigned)E ? eq : kBadKey;  // dropped pairs sort behind every expert
+        rank += (kq < key) || (kq == key && q < s);
+      }
+      pairids[(size_t)t * k + rank] = good ? row : -1;
     }
     __syncwarp();
   }
@@ -626,7 +665,7 @@ cudaError_t launch_route(const RouteBuffers& rb, const int32_t* ids, const float
                          int T, int k, int E, int tile_cap, cudaStream_t st, int* launches) {
   const int pairs = T * k;
   const int nblk = (pairs + kChunk - 1) / kChunk;
-  k_route_count<<<nblk, 32, 0, st>>>(ids, stride, pairs, k, E, rb.blockcnt);
+  k_route_count<<<nblk, 32, 0, st>>>(ids, stride, pairs, k, E, rb.blockcnt, rb.status);
   k_route_scan<<<1, kMaxExperts, 0, st>>>(rb.blockcnt, nblk, E, pairs, T, tile_cap, rb.eoff, rb.runs,
                                            rb.n_runs, rb.tiles, rb.tiles_sh, rb.n_tiles);
   k_route_place<<<nblk, 32, 0, st>>>(ids, w, stride, pairs, k, E, rb.blockcnt, rb.eoff, rb.tokidx,
@@ -644,12 +683,12 @@ cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, 
 
 // ---- expert parallelism ---------------------------------------------------------------
 // ids <- place[ids]: experts renumbered so that rank r owns the ids [r*E/G, (r+1)*E/G).
-__global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, int k,
+__global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, int k, int E,
                                   const int32_t* __restrict__ place) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p < T * k) {
     int32_t* q = ids + (size_t)(p / k) * stride + p % k;
-    *q = place[*q];
+    if ((unsigned)*q < (unsigned)E) *q = place[*q];
   }
 }
 
@@ -708,9 +747,9 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
   }
 }
 
-cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, const int32_t* place,
+cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E, const int32_t* place,
                                    cudaStream_t st) {
-  k_apply_placement<<<(T * k + 255) / 256, 256, 0, st>>>(ids, stride, T, k, place);
+  k_apply_placement<<<(T * k + 255) / 256, 256, 0, st>>>(ids, stride, T, k, E, place);
   return cudaGetLastError();
 }
 

@@ -21,8 +21,15 @@
 // calls of one GPU on one stream, or order them with events.
 //
 // First call on a device: resolves the array's device address (cudaGetSymbolAddress) for
-// the device that is current, and caches it. Make that first call outside any stream
-// capture; later calls only launch kernels.
+// the device that is current, and caches it per device ordinal for the life of the process.
+// Make that first call outside any stream capture; later calls only launch kernels. A host
+// that calls cudaDeviceReset() destroys the context the cached address belongs to: this entry
+// point must not be used on that device afterwards (the library has no way to notice).
+//
+// Ids the caller passes are checked on the device: a pair whose expert id is outside
+// [0, experts) is dropped -- it is not counted, gets no row, and its slot of pairids holds -1 --
+// and eoff[experts] (the number of rows placed) is then smaller than T*topk, which is how the
+// caller detects it.
 //
 // The kernels repeat the arithmetic of route.cu (stable bucketing by expert, offsets for
 // empty experts, pairids = rank among the token's experts) on caller-provided outputs.
@@ -57,7 +64,11 @@ k_static_count(const int32_t* __restrict__ ids, int stride, int pairs, int k, in
   const int base = blockIdx.x * kStaticChunk;
   for (int it = 0; it < kStaticChunk / 32; it++) {
     const int p = base + it * 32 + lane;
-    if (p < pairs) atomicAdd(&hist[ids[(size_t)(p / k) * stride + p % k]], 1);
+    if (p < pairs) {
+      // an id outside [0, E) never becomes an index: the pair is dropped (see the header)
+      const int e = ids[(size_t)(p / k) * stride + p % k];
+      if ((unsigned)e < (unsigned)E) atomicAdd(&hist[e], 1);
+    }
   }
   __syncwarp();
   // every entry of this chunk's row is written, so stale contents never survive
@@ -65,8 +76,7 @@ k_static_count(const int32_t* __restrict__ ids, int stride, int pairs, int k, in
 }
 
 __global__ void __launch_bounds__(kStaticMaxExperts)
-k_static_scan(int32_t* __restrict__ chunkcnt, int nchunks, int E, int pairs,
-              int32_t* __restrict__ eoff) {
+k_static_scan(int32_t* __restrict__ chunkcnt, int nchunks, int E, int32_t* __restrict__ eoff) {
   __shared__ int s[kStaticMaxExperts];
   const int e = threadIdx.x;
   int cnt = 0;
@@ -85,7 +95,7 @@ k_static_scan(int32_t* __restrict__ chunkcnt, int nchunks, int E, int pairs,
     __syncthreads();
   }
   if (e < E) eoff[e] = s[e] - cnt;
-  if (e == 0) eoff[E] = pairs;
+  if (e == 0) eoff[E] = s[kStaticMaxExperts - 1];  // pairs placed: T*topk unless ids outside [0, E) were dropped
 }
 
 __global__ void __launch_bounds__(32)
@@ -104,20 +114,30 @@ k_static_place(const int32_t* __restrict__ ids, const float* __restrict__ w, int
     if (live) {
       const int t = p / k, slot = p % k;
       const int e = ids[(size_t)t * stride + slot];
-      const unsigned same = __match_any_sync(act, e);
+      const bool good = (unsigned)e < (unsigned)E;
+      const unsigned same = __match_any_sync(act, good ? e : -1);
       const int leader = __ffs(same) - 1;
       int start = 0;
-      if (lane == leader) {
+      if (good && lane == leader) {
         start = cursor[e];
         cursor[e] = start + __popc(same);
       }
       start = __shfl_sync(same, start, leader);
       const int row = start + __popc(same & ((1u << lane) - 1u));
-      tokidx[row] = t;
-      pw[row] = w[(size_t)t * stride + slot];
+      if (good) {
+        tokidx[row] = t;
+        pw[row] = w[(size_t)t * stride + slot];
+      }
+      // slot in the token's reduce order: ascending expert id, equal ids in slot order (every
+      // slot is written); a dropped pair's slot holds -1
       int rank = 0;
-      for (int q = 0; q < k; q++) rank += ids[(size_t)t * stride + q] < e;
-      pairids[(size_t)t * k + rank] = row;
+      const int key = good ? e : 0x7fffffff;  // dropped pairs sort behind every expert
+      for (int q = 0; q < k; q++) {
+        const int eq = ids[(size_t)t * stride + q];
+        const int kq = (unsigned)eq < (unsigned)E ? eq : 0x7fffffff;
+        rank += (kq < key) || (kq == key && q < slot);
+      }
+      pairids[(size_t)t * k + rank] = good ? row : -1;
     }
     __syncwarp();
   }
@@ -162,7 +182,7 @@ extern "C" int b200moe_route_static(const int32_t* topids_dev, const float* topw
   const int pairs = T * topk;
   const int nchunks = (pairs + kStaticChunk - 1) / kStaticChunk;
   if (nchunks > 0) k_static_count<<<nchunks, 32, 0, st>>>(topids_dev, stride, pairs, topk, experts, scratch);
-  k_static_scan<<<1, kStaticMaxExperts, 0, st>>>(scratch, nchunks, experts, pairs, eoff_dev);
+  k_static_scan<<<1, kStaticMaxExperts, 0, st>>>(scratch, nchunks, experts, eoff_dev);
   if (nchunks > 0)
     k_static_place<<<nchunks, 32, 0, st>>>(topids_dev, topw_dev, stride, pairs, topk, experts, scratch,
                                            eoff_dev, tokidx_dev, pw_dev, pairids_dev);

@@ -174,7 +174,9 @@ int b200moe_router_topk(b200moe_handle h, const float* logits_dev, int T, int32_
 
 /* Replaces: GpuMoeRouting::run + k_moe_tiles (src/gpu/parts/10_ple_io.inc:784-861). Builds, in
  * the handle's workspace, the stable (expert, pair) permutation, expert offsets, reduce
- * order and tile list for the given selection. */
+ * order and tile list for the given selection. Ids are checked on the device: a pair whose expert
+ * id is outside [0, experts) is dropped (it contributes nothing to the layer output) and the next
+ * b200moe_synchronize returns B200MOE_ERR_BAD_ARG; the same holds for b200moe_forward_routed. */
 int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw_dev, int stride,
                   int T, void* stream);
 
@@ -188,8 +190,11 @@ int b200moe_route(b200moe_handle h, const int32_t* topids_dev, const float* topw
  * device: tokidx[T*topk], pw[T*topk], eoff[experts+1], pairids[T*topk], same definitions and
  * same bytes as b200moe_route produces. All calls on a GPU share the scratch: calls whose
  * kernels overlap (unordered streams, several threads) race; keep them on one stream. The
- * first call on a device looks up the scratch's device address -- make it before any stream
- * capture. */
+ * first call on a device looks up the scratch's device address and caches it for the life of
+ * the process -- make that call before any stream capture, and do not use this entry point on a
+ * device after the host has called cudaDeviceReset() on it (the cached address would be stale).
+ * Expert ids outside [0, experts) are never used as an index: such a pair is dropped (no row, its
+ * pairids slot is -1) and eoff[experts], the number of rows placed, is then below T*topk. */
 int b200moe_route_static(const int32_t* topids_dev, const float* topw_dev, int stride, int T,
                          int topk, int experts, int32_t* tokidx_dev, float* pw_dev,
                          int32_t* eoff_dev, int32_t* pairids_dev, void* stream);
@@ -246,8 +251,9 @@ int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int
                          float* out_dev, void* stream);
 
 /* Waits for `stream` and reports B200MOE_ERR_DEVICE_TIMEOUT if a kernel of an earlier
- * forward gave up a bounded wait (replaces the implicit check of CK() after
- * hipStreamSynchronize in the reference's layer loop). Clears the recorded condition. */
+ * forward gave up a bounded wait, or B200MOE_ERR_BAD_ARG if a caller-supplied expert id was out
+ * of range (replaces the implicit check of CK() after hipStreamSynchronize in the reference's
+ * layer loop). Clears the recorded condition. */
 int b200moe_synchronize(b200moe_handle h, void* stream);
 
 /* Stage timer (replaces the reference's event-ring kernel profiler KP()/kprof,

@@ -26,10 +26,15 @@ class OrcLayer(ctypes.Structure):
                 ("sh_gate", _P), ("sh_up", _P), ("sh_down", _P), ("sh_gate_w", _P)]
 
 
-def build(ref_dir="/root/reference"):
-    """Compile the checker libraries (make -C oracle)."""
-    subprocess.run(["make", "-C", _HERE, "REF_DIR=" + ref_dir], check=True,
-                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+def build(ref_dir=None):
+    """Compile the checker libraries (make -C oracle). The reference tree is looked for in
+    `ref_dir`, else in the environment's REF_DIR, else in reference/ next to the repository and
+    in baseline/_ref/ inside it; without one only the restated oracle is built."""
+    cmd = ["make", "-C", _HERE]
+    ref_dir = ref_dir or os.environ.get("REF_DIR")
+    if ref_dir:
+        cmd.append("REF_DIR=" + ref_dir)
+    subprocess.run(cmd, check=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
 
 
 _orc = None
@@ -59,7 +64,7 @@ def ref():
     global _ref
     if _ref is None:
         L = ctypes.CDLL(REF_SO)
-        for n in ("ref_moe_layer", "ref_q4cp_rows", "ref_gguf_rows"):
+        for n in ("ref_moe_layer", "ref_q4cp_rows", "ref_gguf_rows", "ref_hgn_tensor", "ref_gguf_tensor"):
             getattr(L, n).restype = ctypes.c_int
         _ref = L
     return _ref
@@ -176,6 +181,21 @@ def ref_moe_layer(spec, layer, x_f32, threads=0):
                              _p(x_f32), T, _p(y), threads)
     assert rc == 0
     return y
+
+
+def ref_file_tensor(kind, path, name):
+    """Tensor `name` of a model file as the reference's own reader sees it (hgn::Checkpoint /
+    gguf::File): dict with dtype, ndims, dims, size, crc32; None when the file has no such tensor.
+    Raises when the reference refuses the file."""
+    meta = np.zeros(8, np.uint64)
+    f = ref().ref_hgn_tensor if kind == "hgn" else ref().ref_gguf_tensor
+    rc = f(path.encode(), name.encode(), _p(meta))
+    if rc == 1:
+        return None
+    if rc != 0:
+        raise RuntimeError("the reference reader refused %s" % path)
+    return {"dtype": int(meta[0]), "ndims": int(meta[1]), "dims": [int(v) for v in meta[2:6]],
+            "size": int(meta[6]), "crc32": int(meta[7])}
 
 
 def threads():

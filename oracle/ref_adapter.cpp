@@ -6,6 +6,9 @@
 //   * Model::moe                      src/ref.cpp:563-637   (unmodified, called as is)
 //   * hgn::Checkpoint::q4cp_row       src/hgn.h:249-261
 //   * gguf::dequant_row               src/gguf.h:339-443
+//   * hgn::Checkpoint(path), gguf::File(path)   src/hgn.h:295-363, src/gguf.h:136-314
+//     (the reference's file readers: prove that the files the loader tests write are files
+//     the reference itself accepts, and that it sees the same tensor bytes)
 // The reference's `main` is renamed so that the file can be included as a library
 // (the reference's own kernel test does the same to its engine, tools/ktest.cu:1-5).
 //
@@ -120,6 +123,68 @@ int ref_gguf_rows(uint32_t type, const uint8_t* src, uint64_t k, uint64_t n, flo
     return 0;
   } catch (const std::exception& e) {
     fprintf(stderr, "ref_gguf_rows: %s\n", e.what());
+    return -1;
+  }
+}
+
+}  // extern "C"
+
+namespace {
+// CRC-32 (IEEE, the polynomial of zlib.crc32) of a byte range
+uint32_t crc32_bytes(const uint8_t* p, uint64_t n) {
+  static uint32_t table[256];
+  static bool init = false;
+  if (!init) {
+    for (uint32_t i = 0; i < 256; i++) {
+      uint32_t c = i;
+      for (int k = 0; k < 8; k++) c = (c & 1) ? 0xEDB88320u ^ (c >> 1) : c >> 1;
+      table[i] = c;
+    }
+    init = true;
+  }
+  uint32_t c = 0xFFFFFFFFu;
+  for (uint64_t i = 0; i < n; i++) c = table[(c ^ p[i]) & 0xFF] ^ (c >> 8);
+  return c ^ 0xFFFFFFFFu;
+}
+}  // namespace
+
+extern "C" {
+
+// Opens `path` with the reference's hgn::Checkpoint and reports tensor `name`:
+// meta = {dtype, ndims, dims[0..3], data_size, crc32 of the data}. 0 ok, 1 no such tensor, -1 the
+// reference refused the file.
+int ref_hgn_tensor(const char* path, const char* name, uint64_t* meta8) {
+  try {
+    hgn::Checkpoint ck(path);
+    const hgn::Tensor* t = ck.find(name);
+    if (!t) return 1;
+    meta8[0] = t->dtype;
+    meta8[1] = t->ndims;
+    for (int i = 0; i < 4; i++) meta8[2 + i] = t->dims[i];
+    meta8[6] = t->data_size;
+    meta8[7] = crc32_bytes(t->data, t->data_size);
+    return 0;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "ref_hgn_tensor: %s\n", e.what());
+    return -1;
+  }
+}
+
+// The same through the reference's gguf::File (all shards of a sharded model are opened):
+// meta = {type, nd, ne[0..3], nbytes, crc32 of the data}.
+int ref_gguf_tensor(const char* path, const char* name, uint64_t* meta8) {
+  try {
+    gguf::File f{std::string(path)};
+    const gguf::Tensor* t = f.find(name);
+    if (!t) return 1;
+    meta8[0] = t->type;
+    meta8[1] = t->nd;
+    for (int i = 0; i < 4; i++) meta8[2 + i] = t->ne[i];
+    meta8[6] = t->nbytes;
+    meta8[7] = crc32_bytes(t->data, t->nbytes);
+    return 0;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "ref_gguf_tensor: %s\n", e.what());
     return -1;
   }
 }

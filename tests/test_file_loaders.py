@@ -55,6 +55,108 @@ def write_gguf(path, tensors, alignment=32, extra_kv=True):
         f.write(head + b"".join(blobs))
 
 
+def hgn_tensors(spec, layer, L):
+    E, d, mid = spec.experts, spec.d, spec.mid
+    return [
+        ("tok_embeddings.weight", 0, (4, d), np.zeros(4 * d, np.uint16).tobytes()),
+        ("layers.%d.mlp.gate.weight" % L, 0, (E, d), layer["router_w"].tobytes()),
+        ("layers.%d.mlp.experts.gate_up_proj.weight" % L, 5, (E * 2 * mid, d), layer["gate_up"].tobytes()),
+        ("layers.%d.mlp.experts.down_proj.weight" % L, 5, (E * d, mid), layer["down"].tobytes()),
+        ("layers.%d.mlp.shared_expert.gate_proj.weight" % L, 5, (mid, d), layer["sh_gate"].tobytes()),
+        ("layers.%d.mlp.shared_expert.up_proj.weight" % L, 5, (mid, d), layer["sh_up"].tobytes()),
+        ("layers.%d.mlp.shared_expert.down_proj.weight" % L, 5, (d, mid), layer["sh_down"].tobytes()),
+        ("layers.%d.mlp.shared_expert_gate.weight" % L, 0, (1, d), layer["sh_gate_w"].tobytes()),
+    ]
+
+
+needs_ref = pytest.mark.skipif(not __import__("oracle").have_ref(),
+                               reason="oracle/_ref/libref.so (the reference compiled from its sources) is not built here")
+
+
+@needs_ref
+def test_reference_reader_accepts_the_synthetic_hgn_file(tmp_path):
+    """The .hgn files these tests write are files the reference's own hgn::Checkpoint(path)
+    (src/hgn.h:295-363) opens, and it sees the tensors with the dtype, dims and bytes written."""
+    import zlib
+
+    import oracle
+    spec = synth.LayerSpec(experts=4, topk=2, d=256, mid=64, shared=True, router=True)
+    layer = synth.make_layer(spec, seed=21)
+    path = str(tmp_path / "model.hgn")
+    tensors = hgn_tensors(spec, layer, 3)
+    write_hgn(path, tensors)
+    for name, dtype, dims, raw in tensors:
+        t = oracle.ref_file_tensor("hgn", path, name)
+        assert t is not None, name
+        assert t["dtype"] == dtype and t["ndims"] == len(dims) and t["dims"][:len(dims)] == list(dims)
+        assert t["size"] == len(raw) and t["crc32"] == zlib.crc32(raw)
+    assert oracle.ref_file_tensor("hgn", path, "layers.4.mlp.gate.weight") is None
+    with open(path, "r+b") as f:     # a file whose header size field is wrong is refused
+        f.seek(32)
+        f.write(struct.pack("<Q", 12345))
+    with pytest.raises(RuntimeError):
+        oracle.ref_file_tensor("hgn", path, tensors[0][0])
+
+
+@needs_ref
+@pytest.mark.parametrize("sharded", [False, True])
+def test_reference_reader_accepts_the_synthetic_gguf_files(tmp_path, sharded):
+    """The same for GGUF through the reference's gguf::File(path) (src/gguf.h:136-314), sharded or
+    not, with the key/value section these tests put in front of the tensor infos."""
+    import zlib
+
+    import oracle
+    spec = synth.LayerSpec(experts=4, topk=2, d=512, mid=256, fmt="gguf", gg_gu=12, gg_dn=7)
+    layer = synth.make_layer(spec, seed=22)
+    E, d, mid = spec.experts, spec.d, spec.mid
+    t_gate = ("blk.1.ffn_gate_exps.weight", (d, mid, E), 12, layer["gate"].tobytes())
+    t_up = ("blk.1.ffn_up_exps.weight", (d, mid, E), 12, layer["up"].tobytes())
+    t_down = ("blk.1.ffn_down_exps.weight", (mid, d, E), 7, layer["down"].tobytes())
+    t_other = ("blk.1.attn_norm.weight", (d,), 0, np.ones(d, np.float32).tobytes())
+    if sharded:
+        write_gguf(str(tmp_path / "m-00001-of-00002.gguf"), [t_other, t_gate])
+        write_gguf(str(tmp_path / "m-00002-of-00002.gguf"), [t_down, t_up], alignment=64, extra_kv=False)
+        path = str(tmp_path / "m-00002-of-00002.gguf")
+    else:
+        write_gguf(str(tmp_path / "m.gguf"), [t_other, t_gate, t_up, t_down])
+        path = str(tmp_path / "m.gguf")
+    for name, ne, typ, raw in (t_gate, t_up, t_down, t_other):
+        t = oracle.ref_file_tensor("gguf", path, name)
+        assert t is not None, name
+        assert t["dtype"] == typ and t["ndims"] == len(ne) and t["dims"][:len(ne)] == list(ne)
+        assert t["size"] == len(raw) and t["crc32"] == zlib.crc32(raw)
+    assert oracle.ref_file_tensor("gguf", path, "blk.0.ffn_up_exps.weight") is None
+
+
+@pytest.mark.gpu
+def test_hgn_file_with_a_short_shared_tensor_is_refused(cuda, tmp_path):
+    """A shared-expert tensor whose size or shape does not match the handle is refused with a
+    status code before anything reads past the mapping."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=4, topk=2, d=256, mid=64, shared=True, router=True)
+    layer = synth.make_layer(spec, seed=23)
+    good = hgn_tensors(spec, layer, 0)
+    op = make_op(torch, spec, 8)
+    for victim, cut in (("shared_expert.gate_proj", 64), ("shared_expert.down_proj", 16), ("shared_expert.up_proj", 0)):
+        tensors = []
+        for name, dtype, dims, raw in good:
+            if victim in name:
+                if cut:
+                    raw = raw[:len(raw) - cut]                  # truncated blob, dims unchanged
+                else:
+                    dims = (dims[0] // 2, dims[1] * 2)          # same bytes, another shape
+            tensors.append((name, dtype, dims, raw))
+        path = str(tmp_path / ("bad_%s.hgn" % victim))
+        write_hgn(path, tensors)
+        with pytest.raises(pkg.B200MoeError) as e:
+            op.load_hgn_file(0, path, model_layer=0)
+        assert e.value.status in (1, 2)
+    path = str(tmp_path / "good.hgn")
+    write_hgn(path, good)
+    op.load_hgn_file(0, path, model_layer=0)                    # the untouched file still loads
+    op.close()
+
+
 @pytest.mark.gpu
 def test_hgn_file_with_shared_expert_and_router(cuda, tmp_path):
     torch = cuda

@@ -148,3 +148,20 @@ def test_empty_and_single_token():
     assert y.shape == (1, 128) and np.isfinite(y).all()
     tok, pw, eoff, pid = oracle.route(np.zeros((0, 16), np.int32), np.zeros((0, 16), np.float32), 2, 8)
     assert eoff.tolist() == [0] * 9
+
+
+def test_non_finite_logits_keep_ids_in_range():
+    """A NaN logit (or a row of -inf) makes every probability NaN (src/ref.cpp:574-582: the maximum
+    skips NaN, exp(NaN) poisons the sum): the selection is then arbitrary but the ids are expert
+    numbers, the weights NaN and the token's output NaN. The CUDA router is held to the same."""
+    spec = synth.LayerSpec(experts=16, topk=4, d=256, mid=64)
+    layer = synth.make_layer(spec, seed=5)
+    logits = synth.make_logits(synth.rng_for(5, 1), 3, spec.experts)
+    logits[0, 3] = np.nan
+    logits[1, :] = -np.inf
+    ids, w = oracle.router_topk(logits, spec.topk)
+    assert ((ids[:, :spec.topk] >= 0) & (ids[:, :spec.topk] < spec.experts)).all()
+    assert np.isnan(w[:2, :spec.topk]).all() and np.isfinite(w[2, :spec.topk]).all()
+    xb = synth.make_x(synth.rng_for(5, 9), 3, spec.d)
+    y, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+    assert np.isnan(y[:2]).all() and np.isfinite(y[2]).all()
