@@ -529,6 +529,8 @@ def main():
         # result of the last timed step).
         cores = os.cpu_count() or 1
         n_tok = max(64, min(256, cores * 8))
+        op.moe_b(0, x, logits, out, stream=stream)   # (the host-buffer leg above left the routing of its last token range)
+        op.synchronize(stream)
         ids_gpu = op.get_routing(T)[0]
         sel, strata = stratified_tokens(ids_gpu, K_TOP, n_tok)
         sel_dev = torch.from_numpy(sel).cuda()

@@ -304,8 +304,9 @@ def test_caller_ids_out_of_range_are_dropped(cuda, T):
     pw2 = torch.zeros((T * 2,), dtype=torch.float32, device="cuda")
     eoff2 = torch.zeros((9,), dtype=torch.int32, device="cuda")
     pid2 = torch.full((T * 2,), -7, dtype=torch.int32, device="cuda")
-    st = pkg.lib().b200moe_route_static(torch.from_numpy(ids_bad).cuda().data_ptr(), torch.from_numpy(w).cuda().data_ptr(),
-                                        16, T, 2, 8, tok2.data_ptr(), pw2.data_ptr(), eoff2.data_ptr(), pid2.data_ptr(), None)
+    ids_dev, w_dev = torch.from_numpy(ids_bad).cuda(), torch.from_numpy(w).cuda()   # (kept alive across the call)
+    st = pkg.lib().b200moe_route_static(ids_dev.data_ptr(), w_dev.data_ptr(), 16, T, 2, 8, tok2.data_ptr(), pw2.data_ptr(),
+                                        eoff2.data_ptr(), pid2.data_ptr(), None)
     assert st == 0
     torch.cuda.synchronize()
     assert np.array_equal(eoff2.cpu().numpy(), eoff) and np.array_equal(pid2.cpu().numpy(), pid)
