@@ -50,6 +50,7 @@ struct b200moe_ctx {
   float* logits_stage = nullptr;
   int32_t* status_dev = nullptr;
   int32_t* status_host = nullptr;  // pinned
+  unsigned* grid_bar = nullptr;    // {arrival count, generation} of the fused decode kernel's grid-wide barrier
   // forward_host: copy streams and per-chunk events of the pipelined host path
   static constexpr int kHostChunks = 4;
   cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -168,6 +169,8 @@ int report_status(b200moe_handle h, cudaStream_t st) {
   const int code = h->status_host[0], detail = h->status_host[1];
   if (code == 0) return B200MOE_OK;
   cudaError_t e = cudaMemsetAsync(h->status_dev, 0, 16, st);
+  // a grid-wide barrier that gave up leaves its arrival count behind: start it afresh
+  if (e == cudaSuccess && code == 5) e = cudaMemsetAsync(h->grid_bar, 0, 16, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return fail(h, B200MOE_ERR_CUDA, std::string("clearing the status word: ") + cudaGetErrorString(e));
   char buf[160];
@@ -276,6 +279,8 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   A(&h->status_dev, 4);
   h->rb.status = h->status_dev;
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 16);
+  A(&h->grid_bar, 4);
+  if (e == cudaSuccess) e = cudaMemset(h->grid_bar, 0, 16);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->status_host, 16);
   if (e == cudaSuccess && !simt_all)
     e = tc_create(&h->tc, h->x_sorted, (__half*)h->hid, (long long)rows, d, mid);
@@ -551,6 +556,23 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     ev = &h->prof_ev[(size_t)h->prof_head * kProfEvents];
     // ev[0] was recorded by the caller of forward_impl (before the router) when it ran one
     if (!router_timed) CU_TRY(h, cudaEventRecord(ev[0], st));
+  }
+  // decode / verify of q4cp layers: routing, both GEMVs and the combine as one kernel
+  // (B200MOE_NO_FUSED_DECODE=1 keeps the separate kernels, for A/B measurements)
+  static const bool no_fused = getenv("B200MOE_NO_FUSED_DECODE") != nullptr;
+  if (!no_fused && c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max && T <= decode_max_tokens() &&
+      ((uintptr_t)x & 15) == 0 && (size_t)T * (k + (shared ? 1 : 0)) <= (size_t)h->dec_rows &&
+      decode_supported(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, T, k, E, d, mid)) {
+    CU_TRY(h, launch_decode(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, logits, ids, w, stride, x,
+                            shared ? L.sh_gate_w : nullptr, T, E, k, d, mid, (__half*)h->hid, out, h->hc_w4, h->hc_state,
+                            h->rb, h->grid_bar, h->status_dev, st));
+    if (ev) {
+      for (int i = 1; i <= 5; i++) CU_TRY(h, cudaEventRecord(ev[i], st));  // one kernel: no stage boundaries
+      h->prof_head = (h->prof_head + 1) % kProfRing;
+      if (h->prof_pending < kProfRing) h->prof_pending++;
+    }
+    h->launches += 1;
+    return B200MOE_OK;
   }
   if (T * k <= route_small_max_pairs() && T <= 16) {
     CU_TRY(h, launch_route_small(h->rb, logits, ids, w, stride, T, k, E, x, shared ? L.sh_gate_w : nullptr,

@@ -115,6 +115,20 @@ cudaError_t launch_up_gemv(const Image& img, const Image* img_sh, const void* x_
 cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half* hid16, int d, int mid,
                              const Run* runs, const int32_t* n_runs, float* pairs_f32, cudaStream_t st);
 
+// ---- decode.cu (q4cp decode / verify, T <= decode_max_tokens(), as one kernel) ----
+// Routing (from logits, or from the caller's ids / w when logits is null), gate/up GEMV + SwiGLU,
+// down GEMV and the weighted combine in one launch; every expert is read once for all the rows
+// that use it. sh_gu / sh_dn: the shared expert's images or null. hid16: workspace
+// [T*k + T][mid]. bar: two zero-initialised words in device memory (grid-wide barrier).
+// out_bf16, or hc_w4 + hc_state for the residual write-back. x_bf16 must be 16-byte aligned.
+int decode_max_tokens();
+bool decode_supported(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, int T, int k, int E, int d,
+                      int mid);
+cudaError_t launch_decode(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, const float* logits,
+                          const int32_t* ids, const float* w, int stride, const void* x_bf16, const uint16_t* gate_w, int T,
+                          int E, int k, int d, int mid, __half* hid16, void* out_bf16, const float* hc_w4, void* hc_state,
+                          const RouteBuffers& rb, unsigned* bar, int32_t* status, cudaStream_t st);
+
 // Bounded wait (2 s) until n <= 32 flags written by other GPUs have reached `expected`; a
 // timeout sets status {3, flag index}.
 cudaError_t launch_wait_flags(const int32_t* flags, int n, int32_t expected, int32_t* status, cudaStream_t st);

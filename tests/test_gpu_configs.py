@@ -198,21 +198,34 @@ def test_odd_k_block_count_in_down_gemm(cuda, mid):
 
 # ---------------------------------------------------------------- invariance audits on the production kernels
 def test_row_invariance_gemv_path(cuda):
-    """A token's bytes do not depend on the other tokens of the call on the GEMV path either
-    (the reference's audit, tools/ktest.cu:920-923, 1152-1271): T=1 equals the token's row inside
-    T=5 and T=16 calls, bit for bit."""
+    """A token's bytes do not depend on the other tokens of the call on the decode paths either
+    (the reference's audit, tools/ktest.cu:920-923, 1152-1271). The fused decode kernel (T <= 8)
+    reads an expert once for all the rows that use it: a token alone (T=1, the plain path) equals
+    its row inside T=2, 5 and 8 calls bit for bit, which is the reference's "dedup == plain" check
+    (tools/moe_gguf_gemv_test.cu:197-223). The separate GEMV kernels (9 <= T <= 16) likewise
+    among themselves. The routing is drawn from 12 experts so that several tokens share experts."""
     torch = cuda
-    spec = synth.LayerSpec(experts=64, topk=10, d=512, mid=256, shared=True)
+    spec = synth.LayerSpec(experts=12, topk=4, d=512, mid=256, shared=True, book="random")
     layer = synth.make_layer(spec, seed=71)
     logits = synth.make_logits(synth.rng_for(71, 1), 16, spec.experts)
     xb = synth.make_x(synth.rng_for(71, 9), 16, spec.d)
     op = make_op(torch, spec, 16, layer=layer)
-    y16 = run_layer(torch, op, spec, xb, logits)
-    y5 = run_layer(torch, op, spec, xb[:5], logits[:5])
-    assert np.array_equal(bits(y5), bits(y16[:5]))
-    for t in (0, 4, 15):
+    y8 = run_layer(torch, op, spec, xb[:8], logits[:8])
+    counts = np.bincount(op.get_routing(8)[0][:, :spec.topk].reshape(-1), minlength=spec.experts)
+    assert counts.max() >= 3, "the test wants an expert shared by three or more rows"
+    y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb[:8]), logits=logits[:8])
+    assert_output_close(y8, y_o, "T=8 decode")
+    for T in (2, 5):
+        yT = run_layer(torch, op, spec, xb[:T], logits[:T])
+        assert np.array_equal(bits(yT), bits(y8[:T])), "T=%d rows differ from the T=8 call" % T
+    for t in (0, 4, 7):
         y1 = run_layer(torch, op, spec, xb[t:t + 1], logits[t:t + 1])
-        assert np.array_equal(bits(y1[0]), bits(y16[t])), "token %d differs between T=1 and T=16" % t
+        assert np.array_equal(bits(y1[0]), bits(y8[t])), "token %d differs between T=1 and T=8" % t
+    y16 = run_layer(torch, op, spec, xb, logits)
+    y9 = run_layer(torch, op, spec, xb[:9], logits[:9])
+    assert np.array_equal(bits(y9), bits(y16[:9]))
+    y_o16, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+    assert_output_close(y16, y_o16, "T=16 decode")
     op.close()
 
 
