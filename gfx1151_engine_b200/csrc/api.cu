@@ -51,6 +51,7 @@ struct b200moe_ctx {
   int32_t* status_dev = nullptr;
   int32_t* status_host = nullptr;  // pinned
   unsigned* grid_bar = nullptr;    // {arrival count, generation} of the fused decode kernel's grid-wide barrier
+  unsigned long long* dec_trace = nullptr;  // debug timeline of the fused decode kernel (environment B200MOE_DECODE_TRACE=<file>)
   // forward_host: copy streams and per-chunk events of the pipelined host path
   static constexpr int kHostChunks = 4;
   cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -281,6 +282,10 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 16);
   A(&h->grid_bar, 4);
   if (e == cudaSuccess) e = cudaMemset(h->grid_bar, 0, 16);
+  if (getenv("B200MOE_DECODE_TRACE")) {
+    A(&h->dec_trace, (size_t)1024 * 8);
+    if (e == cudaSuccess) e = cudaMemset(h->dec_trace, 0, 1024 * 8 * sizeof(unsigned long long));
+  }
   if (e == cudaSuccess) e = cudaMallocHost((void**)&h->status_host, 16);
   if (e == cudaSuccess && !simt_all)
     e = tc_create(&h->tc, h->x_sorted, (__half*)h->hid, (long long)rows, d, mid);
@@ -300,6 +305,15 @@ int b200moe_destroy(b200moe_handle h) {
   if (!h) return B200MOE_ERR_BAD_ARG;
   cudaSetDevice(h->cfg.device);
   cudaDeviceSynchronize();
+  if (h->dec_trace) {
+    // debug aid: per-block phase time stamps (ns) of the last fused decode launch, raw uint64 [1024][8]
+    std::vector<unsigned long long> host((size_t)1024 * 8);
+    if (cudaMemcpy(host.data(), h->dec_trace, host.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess)
+      if (FILE* f = fopen(getenv("B200MOE_DECODE_TRACE") ? getenv("B200MOE_DECODE_TRACE") : "decode_trace.bin", "wb")) {
+        fwrite(host.data(), 8, host.size(), f);
+        fclose(f);
+      }
+  }
   for (auto& L : h->layers) {
     if (L.borrowed) continue;
     free_image(L.gu);
@@ -565,7 +579,7 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
       decode_supported(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, T, k, E, d, mid)) {
     CU_TRY(h, launch_decode(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, logits, ids, w, stride, x,
                             shared ? L.sh_gate_w : nullptr, T, E, k, d, mid, (__half*)h->hid, out, h->hc_w4, h->hc_state,
-                            h->rb, h->grid_bar, h->status_dev, st));
+                            h->rb, h->grid_bar, h->status_dev, st, h->dec_trace));
     if (ev) {
       for (int i = 1; i <= 5; i++) CU_TRY(h, cudaEventRecord(ev[i], st));  // one kernel: no stage boundaries
       h->prof_head = (h->prof_head + 1) % kProfRing;

@@ -127,7 +127,8 @@ bool decode_supported(const Image& gu, const Image& dn, const Image* sh_gu, cons
 cudaError_t launch_decode(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, const float* logits,
                           const int32_t* ids, const float* w, int stride, const void* x_bf16, const uint16_t* gate_w, int T,
                           int E, int k, int d, int mid, __half* hid16, void* out_bf16, const float* hc_w4, void* hc_state,
-                          const RouteBuffers& rb, unsigned* bar, int32_t* status, cudaStream_t st);
+                          const RouteBuffers& rb, unsigned* bar, int32_t* status, cudaStream_t st,
+                          unsigned long long* trace = nullptr);  // trace: debug, [SMs][8] phase time stamps of the last launch
 
 // Bounded wait (2 s) until n <= 32 flags written by other GPUs have reached `expected`; a
 // timeout sets status {3, flag index}.

@@ -58,11 +58,22 @@ struct RouteSmallOut {
 __device__ __forceinline__ void rs_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // Run by threads 0..511 of a block (tid = threadIdx.x < 512). Inputs as k_route_small's.
-template <int NROW>
+// GU: 16-byte pieces of the shared expert's gate product a lane loads before it uses any (a
+// register-hungry prefetch: 8 where the body has the whole SM's registers, 2 inside a larger kernel).
+template <int NROW, int GU = 8>
 __device__ __forceinline__ void route_small_body(
     const float* __restrict__ logits, const int32_t* __restrict__ ids_in, const float* __restrict__ w_in,
     int stride_in, int T, int E, int k, const uint16_t* __restrict__ x, const uint16_t* __restrict__ gw, int d,
-    RouteSmallScratch<NROW>& sc, const RouteSmallOut& o1, const RouteSmallOut& o2, int32_t* status) {
+    RouteSmallScratch<NROW>& sc, const RouteSmallOut& o1, const RouteSmallOut& o2, int32_t* status,
+    unsigned long long* dbg = nullptr) {
+#define RS_STAMP(i)                                                     \
+  do {                                                                  \
+    if (dbg && threadIdx.x == 0) {                                      \
+      unsigned long long t_;                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));            \
+      dbg[i] = t_;                                                      \
+    }                                                                   \
+  } while (0)
   float (*s_p)[kMaxExperts] = sc.p;
   int* s_key = sc.key;
   float* s_w = sc.w;
@@ -86,10 +97,10 @@ __device__ __forceinline__ void route_small_body(
       const uint4* gv = (const uint4*)gw;
       // eight pieces per lane are loaded before any is used (with one warp per token the loop
       // would otherwise pay a global-load latency per piece); the additions keep their order
-      for (int c0 = wq * 32 + lane; c0 < d / 8; c0 += W * 32 * 8) {
-        uint4 xa[8], ga[8];
+      for (int c0 = wq * 32 + lane; c0 < d / 8; c0 += W * 32 * GU) {
+        uint4 xa[GU], ga[GU];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < GU; u++) {
           const int c = c0 + u * W * 32;
           if (c < d / 8) {
             xa[u] = xv[c];
@@ -97,7 +108,7 @@ __device__ __forceinline__ void route_small_body(
           }
         }
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < GU; u++) {
           if (c0 + u * W * 32 < d / 8) {
             const uint32_t xw[4] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w}, gq[4] = {ga[u].x, ga[u].y, ga[u].z, ga[u].w};
 #pragma unroll
@@ -124,6 +135,7 @@ __device__ __forceinline__ void route_small_body(
       RS_PUT(pw, P + ts, gate);
     }
     rs_sync();  // s_part is reused by the router
+  RS_STAMP(0);
   }
   if (logits) {
     // Router: the token's W warps share its exponentials, divisions and the selection, so
@@ -143,6 +155,7 @@ __device__ __forceinline__ void route_small_body(
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) s_bv[0][warp] = mx;
     rs_sync();
+  RS_STAMP(1);
     for (int w2 = 0; w2 < W; w2++) mx = fmaxf(mx, s_bv[0][ts * W + w2]);
     const double dmx = (double)mx;
 #pragma unroll
@@ -154,6 +167,7 @@ __device__ __forceinline__ void route_small_body(
       }
     }
     rs_sync();
+  RS_STAMP(2);
     // Sum of the exponentials, as the reference takes it: in double, in index order. All terms
     // are floats in (0, 1]: when the smallest non-zero one is at least 2^(B - 30), B = bits of
     // the total's integer part, every partial sum of ANY order is a multiple of one grid that
@@ -180,6 +194,7 @@ __device__ __forceinline__ void route_small_body(
       }
     }
     rs_sync();
+  RS_STAMP(3);
     if (tok && wq == 0 && lane == 0) {
       double se = 0;
       float mn = 2.f;
@@ -198,6 +213,7 @@ __device__ __forceinline__ void route_small_body(
       s_se[ts] = se;
     }
     rs_sync();
+  RS_STAMP(4);
     const double se = tok ? s_se[ts] : 1.0;
 #pragma unroll
     for (int j = 0; j < 16; j++) {
@@ -345,6 +361,7 @@ __device__ __forceinline__ void route_small_body(
     }
   }
   rs_sync();
+  RS_STAMP(5);
   // pair p -> row = number of pairs ordered before it by (expert, p)
   int n_bad = 0;
   if (tid < P) {
@@ -373,6 +390,7 @@ __device__ __forceinline__ void route_small_body(
   const unsigned active = __ballot_sync(0xffffffffu, cnt > 0);
   if (lane == 0) s_wcnt[warp] = __popc(active);
   rs_sync();
+  RS_STAMP(6);
   int before = __popc(active & ((1u << lane) - 1u)), n_active = 0;
   for (int w2 = 0; w2 < 16; w2++) {
     if (w2 < warp) before += s_wcnt[w2];
@@ -395,6 +413,7 @@ __device__ __forceinline__ void route_small_body(
   }
 }
 #undef RS_PUT
+#undef RS_STAMP
 
 
 }  // namespace b200moe
