@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200moe.so")
 
 GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
+DECODE_AUTO, DECODE_FUSED = 0, 1
 GGML_Q5_1, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 13, 20, 23
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
@@ -26,7 +27,7 @@ class Config(ctypes.Structure):
     """Field-for-field mirror of b200moe_config."""
     _fields_ = [(n, ctypes.c_int32) for n in (
         "experts", "topk", "d_model", "d_mid", "n_layers", "max_tokens", "has_shared", "device",
-        "gemm_impl", "decode_max_tokens", "ep_rank", "ep_size", "ep_sm_margin")] + [("reserved", ctypes.c_int32 * 3)]
+        "gemm_impl", "decode_max_tokens", "ep_rank", "ep_size", "ep_sm_margin", "decode_impl")] + [("reserved", ctypes.c_int32 * 2)]
 
 
 SYMBOLS = {
@@ -121,9 +122,10 @@ class MoeOperator:
     """
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, n_layers=1, has_shared=False,
-                 device=0, gemm_impl=GEMM_AUTO, decode_max_tokens=0, ep_rank=0, ep_size=1, ep_sm_margin=0):
+                 device=0, gemm_impl=GEMM_AUTO, decode_max_tokens=0, ep_rank=0, ep_size=1, ep_sm_margin=0,
+                 decode_impl=DECODE_AUTO):
         self.cfg = Config(experts, topk, d_model, d_mid, n_layers, max_tokens, int(has_shared), device,
-                          gemm_impl, decode_max_tokens, ep_rank, ep_size, ep_sm_margin)
+                          gemm_impl, decode_max_tokens, ep_rank, ep_size, ep_sm_margin, decode_impl)
         self._h = _P()
         st = lib().b200moe_create(ctypes.byref(self.cfg), ctypes.byref(self._h))
         if st != 0:

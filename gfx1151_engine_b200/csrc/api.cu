@@ -50,7 +50,7 @@ struct b200moe_ctx {
   float* logits_stage = nullptr;
   int32_t* status_dev = nullptr;
   int32_t* status_host = nullptr;  // pinned
-  unsigned* grid_bar = nullptr;    // {arrival count, generation} of the fused decode kernel's grid-wide barrier
+  unsigned long long* grid_bar = nullptr;  // arrival counter of the fused decode kernel's grid-wide barrier
   unsigned long long* dec_trace = nullptr;  // debug timeline of the fused decode kernel (environment B200MOE_DECODE_TRACE=<file>)
   // forward_host: copy streams and per-chunk events of the pipelined host path
   static constexpr int kHostChunks = 4;
@@ -280,7 +280,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
   A(&h->status_dev, 4);
   h->rb.status = h->status_dev;
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 16);
-  A(&h->grid_bar, 4);
+  A(&h->grid_bar, 2);
   if (e == cudaSuccess) e = cudaMemset(h->grid_bar, 0, 16);
   if (getenv("B200MOE_DECODE_TRACE")) {
     A(&h->dec_trace, (size_t)1024 * 8);
@@ -571,10 +571,13 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     // ev[0] was recorded by the caller of forward_impl (before the router) when it ran one
     if (!router_timed) CU_TRY(h, cudaEventRecord(ev[0], st));
   }
-  // decode / verify of q4cp layers: routing, both GEMVs and the combine as one kernel
-  // (B200MOE_NO_FUSED_DECODE=1 keeps the separate kernels, for A/B measurements)
-  static const bool no_fused = getenv("B200MOE_NO_FUSED_DECODE") != nullptr;
-  if (!no_fused && c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max && T <= decode_max_tokens() &&
+  // decode / verify of q4cp layers as ONE kernel (routing, both GEMVs, combine, every expert read
+  // once for all its rows): opt-in with decode_impl = B200MOE_DECODE_FUSED in the configuration or B200MOE_FUSED_DECODE=1. Measured slower than the
+  // separate kernels (whose launches overlap through programmatic dependent launch), so they
+  // stay the default.
+  static const bool fused_env = getenv("B200MOE_FUSED_DECODE") != nullptr && atoi(getenv("B200MOE_FUSED_DECODE")) != 0;
+  const bool fused = fused_env || c.decode_impl == B200MOE_DECODE_FUSED;
+  if (fused && c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max && T <= decode_max_tokens() &&
       ((uintptr_t)x & 15) == 0 && (size_t)T * (k + (shared ? 1 : 0)) <= (size_t)h->dec_rows &&
       decode_supported(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, T, k, E, d, mid)) {
     CU_TRY(h, launch_decode(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, logits, ids, w, stride, x,
@@ -588,7 +591,12 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
     h->launches += 1;
     return B200MOE_OK;
   }
-  if (T * k <= route_small_max_pairs() && T <= 16) {
+  static const bool slow_router = getenv("B200MOE_EXACT_ROUTER") != nullptr;  // A/B: the general routing body for every call
+  if (logits && !slow_router && T <= decode_max_tokens() && T * k <= 128 && d % 8 == 0 && (!shared || ((uintptr_t)x & 15) == 0)) {
+    // decode / verify: the compact router (ids from the logits' order, general body only on a near-tie)
+    CU_TRY(h, launch_route_fast(h->rb, logits, T, k, E, x, shared ? L.sh_gate_w : nullptr, d, st));
+    n++;
+  } else if (T * k <= route_small_max_pairs() && T <= 16) {
     CU_TRY(h, launch_route_small(h->rb, logits, ids, w, stride, T, k, E, x, shared ? L.sh_gate_w : nullptr,
                                  d, st));
     n++;

@@ -70,6 +70,7 @@ struct DecShared {
   Run runs[kDecMaxPairs + 1];          // routed runs in ascending expert id; the shared expert's run last
   int32_t n_runs[2];
   int32_t uf[kDecMaxPairs + 2];        // exclusive prefix over the routed runs of their sub-units (<= kDecRows rows each)
+  int32_t uw[kMaxRecs + 2];            // exclusive prefix over the gate/up units of their cost per task
   float book[5][16];                   // gate/up routed, shared gate, shared up, down routed, shared down
   int32_t cnt[kRedBufs];               // arrivals at each partial-sum buffer (never reset)
   int32_t done[kRedBufs];              // uses of each buffer that have been added up
@@ -102,7 +103,7 @@ struct DecParams {
   const float* hc_w4;
   uint16_t* hc_state;
   RouteBuffers rb;              // global routing results (written by block 0)
-  unsigned* bar;                // [2]: arrival count, generation
+  unsigned long long* bar;      // arrival counter of the grid-wide barrier (never reset)
   int32_t* status;
   unsigned long long* trace;    // debug: [blocks][8] nanosecond stamps of the phase boundaries, or null
 };
@@ -150,6 +151,12 @@ __device__ __forceinline__ void fma_pair(float& acc, uint32_t w, uint32_t x) {
 
 // finite values saturate to the fp16 range, NaN stays NaN
 __device__ __forceinline__ float sat_f16(float v) { return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f); }
+// two bf16 values -> two fp16 values (round to nearest, magnitudes beyond the fp16 range saturate)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t u) {
+  uint32_t h;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(__uint_as_float(u & 0xFFFF0000u)), "f"(__uint_as_float(u << 16)));
+  return h;
+}
 
 // Dot products of one 16-byte chunk (32 codes of one 32-group of the lane's weight row) with the
 // matching 32 fp16 activations of NR rows. xa: shared address of row 0's activations, rows
@@ -411,28 +418,28 @@ __device__ __forceinline__ void route_fast_place(const DecParams& p, FastScratch
   }
 }
 
-// Bounded grid-wide barrier. bar[0] counts arrivals, bar[1] is the generation; the last block
-// resets the count and bumps the generation. Every block reads the generation before it
-// arrives, so the barrier cannot complete (and the generation cannot move) before that read.
+// Bounded grid-wide barrier on ONE 64-bit arrival counter that is never reset: every launch
+// adds gridDim.x to it, so a block that read the counter at any time before its own arrival
+// (target_of) knows the value that means "all blocks of this launch have arrived" -- the next
+// multiple of the grid size. One release-add and acquire polls; no reset, no second word.
 // Returns false when the wait gave up after 2 s (status {5, block}); the caller stops working.
-__device__ __forceinline__ bool grid_barrier(unsigned* bar, DecShared* res, int32_t* status) {
+__device__ __forceinline__ unsigned long long barrier_target(const unsigned long long* ctr) {
+  unsigned long long c;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
+  return (c / gridDim.x + 1) * gridDim.x;
+}
+__device__ __forceinline__ bool grid_barrier(unsigned long long* ctr, unsigned long long target, DecShared* res, int32_t* status) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    unsigned gen;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(bar + 1) : "memory");
-    __threadfence();
-    const unsigned old = atomicAdd(bar, 1u);
-    if (old == gridDim.x - 1) {
-      bar[0] = 0;
-      __threadfence();
-      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen + 1) : "memory");
-    } else {
+    unsigned long long old;
+    asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(old) : "l"(ctr) : "memory");
+    if (old + 1 < target) {
       unsigned long long t0;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
       for (uint32_t spin = 0;; spin++) {
-        unsigned g;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(g) : "l"(bar + 1) : "memory");
-        if (g != gen) break;
+        unsigned long long c;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
+        if (c >= target) break;
         if ((spin & 63u) == 63u) {
           unsigned long long t1;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
@@ -441,9 +448,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, DecShared* res, int3
             res->abort = 1;
             break;
           }
-          __nanosleep(100);
         }
       }
+    } else {
+      __threadfence();  // (acquire side of the last arrival)
     }
   }
   __syncthreads();
@@ -476,6 +484,7 @@ k_decode(const DecParams p) {
   }
   DecShared* const res = (DecShared*)(smem + kOffRes);
   DEC_TRACE(0);
+  unsigned long long bar_target = 0;
   const bool has_sh = p.sh_gu.data != nullptr;
   const int T = p.T, P = p.T * p.k, mid = p.mid, d = p.d;
   pdl_trigger();
@@ -510,27 +519,30 @@ k_decode(const DecParams p) {
   build_table(0, 0);
   pdl_wait();  // from here on: inputs an earlier kernel may have written, buffers it may still read
   DEC_TRACE(1);
+  if (tid == 0) bar_target = barrier_target(p.bar);  // (long before this block's own arrival; only thread 0 uses it)
 
   // ---- routing, repeated by every block for itself: warps 0..15 the router and the bucketing,
   // warps 16..31 the shared expert's scalar gate (src/ref.cpp:623-626: a d-long dot product in double) ----
   FastScratch& fs = *(FastScratch*)(smem + kOffRing);
   if (warp < 16) {
-    RouteOuts ro;
-    ro.loc.tokidx = res->tokidx;
-    ro.loc.pw = res->pw;
-    ro.loc.runs = res->runs;
-    ro.loc.shared_slot = kDecMaxPairs;
-    ro.loc.n_runs = res->n_runs;
-    if (blockIdx.x == 0) {
-      RouteSmallOut& g = ro.glob;
-      g.topids = p.rb.topids; g.topw = p.rb.topw; g.tokidx = p.rb.tokidx; g.pw = p.rb.pw;
-      g.pairids = p.rb.pairids; g.eoff = p.rb.eoff; g.runs = p.rb.runs; g.shared_slot = kMaxExperts;
-      g.n_runs = p.rb.n_runs; g.tiles = p.rb.tiles; g.tiles_sh = p.rb.tiles_sh; g.n_tiles = p.rb.n_tiles;
-    }
+    auto fill_outs = [&](RouteSmallOut& loc, RouteSmallOut& glob) {
+      loc.tokidx = res->tokidx;
+      loc.pw = res->pw;
+      loc.runs = res->runs;
+      loc.shared_slot = kDecMaxPairs;
+      loc.n_runs = res->n_runs;
+      if (blockIdx.x == 0) {
+        glob.topids = p.rb.topids; glob.topw = p.rb.topw; glob.tokidx = p.rb.tokidx; glob.pw = p.rb.pw;
+        glob.pairids = p.rb.pairids; glob.eoff = p.rb.eoff; glob.runs = p.rb.runs; glob.shared_slot = kMaxExperts;
+        glob.n_runs = p.rb.n_runs; glob.tiles = p.rb.tiles; glob.tiles_sh = p.rb.tiles_sh; glob.n_tiles = p.rb.n_tiles;
+      }
+    };
+    RouteSmallOut loc, glob;
+    fill_outs(loc, glob);
     bool placed = false;
     if (p.logits) {
-      if (route_fast_select(p, fs, ro.glob)) {
-        route_fast_place(p, fs, ro.loc, ro.glob);
+      if (route_fast_select(p, fs, glob)) {
+        route_fast_place(p, fs, loc, glob);
         placed = true;
       }
     } else {
@@ -544,11 +556,16 @@ k_decode(const DecParams p) {
         fs.w[q] = p.w[(size_t)(q / p.k) * p.stride + q % p.k];
       }
       rs_sync();
-      route_fast_place(p, fs, ro.loc, ro.glob);
+      route_fast_place(p, fs, loc, glob);
       placed = true;
     }
-    if (!placed)  // a near-tie or a non-finite logit: the reference's arithmetic decides (block-uniform)
+    if (!placed) {
+      // a near-tie or a non-finite logit: the reference's arithmetic decides (block-uniform, rare;
+      // its argument block is only built here so that the common path keeps everything in registers)
+      RouteOuts ro;
+      fill_outs(ro.loc, ro.glob);
       route_exact(p, (RouteSmallScratch<kDecMaxT>*)(smem + kOffRing + sizeof(FastScratch)), &ro, blockIdx.x == 0 ? p.status : nullptr);
+    }
   } else if (has_sh) {
     const int gtid = tid - 512, gw = warp - 16;
 #pragma unroll 1
@@ -661,10 +678,47 @@ k_decode(const DecParams p) {
     const int kb0 = warp * kpw;
     const int my_k = max(0, min(kpw, KB - kb0));
     const int tpu = mid / 16;
-    const int total = (nu_shared + nu_routed) * tpu;
-    const int base_n = total / (int)gridDim.x, rem = total % (int)gridDim.x;
-    const int c0 = (int)blockIdx.x * base_n + min((int)blockIdx.x, rem);
-    const int n_tasks = base_n + ((int)blockIdx.x < rem ? 1 : 0);
+    // The tasks are cut into one contiguous range per block by COST, not by count: a task over two
+    // rows does almost twice the arithmetic of a task over one (the kernel is bound by instruction
+    // issue, not by bytes). Cost 5 per single-row task, 8 per two-row task; res->uw = exclusive
+    // prefix of the units' costs per task (shared sub-units first).
+    const int n_units = nu_shared + nu_routed;
+    if (warp == 0) {
+      int carry = 0;
+      for (int i0 = 0; i0 < n_units; i0 += 32) {
+        const int u = i0 + lane;
+        int cst = 0;
+        if (u < n_units) {
+          Rec r;
+          unit_rec(u < nu_shared ? u : u - nu_shared, u < nu_shared, r);
+          cst = (r.info & 255) > 1 ? 8 : 5;
+        }
+        int incl = cst;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        if (u < n_units) res->uw[u] = carry + incl - cst;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) res->uw[n_units] = carry;
+    }
+    __syncthreads();
+    // global task index at which the cost prefix reaches `target` (cost units x tasks per unit)
+    auto task_at = [&](long long target) -> int {
+      int lo = 0, hi = n_units;  // first unit u with uw[u + 1] * tpu > target
+      while (lo < hi) {
+        const int m = (lo + hi) >> 1;
+        if ((long long)res->uw[m + 1] * tpu > target) hi = m; else lo = m + 1;
+      }
+      if (lo >= n_units) return n_units * tpu;
+      const int per = res->uw[lo + 1] - res->uw[lo];
+      return lo * tpu + (int)((target - (long long)res->uw[lo] * tpu + per - 1) / per);
+    };
+    const long long total_cost = (long long)res->uw[n_units] * tpu;
+    const int c0 = task_at(total_cost * blockIdx.x / gridDim.x);
+    const int n_tasks = task_at(total_cost * (blockIdx.x + 1) / gridDim.x) - c0;
     int gt = 0;  // tasks of this block done so far
     for (int b0 = 0; b0 < n_tasks; b0 += kMaxRecs) {
       const int nb = min(kMaxRecs, n_tasks - b0);
@@ -736,16 +790,8 @@ k_decode(const DecParams p) {
           const uint32_t sb = slot_base(c_s);
           // activations bf16 -> fp16 in place (finite values saturate; exact for |v| in [2^-14, 65504])
           const uint32_t xa = sb + 1280;
-          {
-            const uint32_t u = lds32(xa + lane * 4);
-            const __half2 h = __floats2half2_rn(sat_f16(__uint_as_float(u << 16)), sat_f16(__uint_as_float(u & 0xFFFF0000u)));
-            sts32(xa + lane * 4, *(const uint32_t*)&h);
-          }
-          if (cnt > 1) {
-            const uint32_t u = lds32(xa + 128 + lane * 4);
-            const __half2 h = __floats2half2_rn(sat_f16(__uint_as_float(u << 16)), sat_f16(__uint_as_float(u & 0xFFFF0000u)));
-            sts32(xa + 128 + lane * 4, *(const uint32_t*)&h);
-          }
+          sts32(xa + lane * 4, bf16x2_to_f16x2(lds32(xa + lane * 4)));
+          if (cnt > 1) sts32(xa + 128 + lane * 4, bf16x2_to_f16x2(lds32(xa + 128 + lane * 4)));
           __syncwarp();
           const uint4 ca = lds128(sb + lane * 16), cb = lds128(sb + 512 + lane * 16);
           const uint32_t m = lds32(sb + 1024 + lane * 4);
@@ -883,7 +929,7 @@ k_decode(const DecParams p) {
       advance_q();
     }
   }
-  if (!grid_barrier(p.bar, res, p.status)) {
+  if (!grid_barrier(p.bar, bar_target, res, p.status)) {
     cp_wait<0>();
     return;
   }
@@ -984,6 +1030,79 @@ k_decode(const DecParams p) {
   DEC_TRACE(5);
 }
 
+
+// The same routing as a kernel of its own, for the decode path that keeps the GEMVs and the
+// combine as separate kernels: 512 threads select and bucket, 512 threads form the shared
+// expert's gate. Writes what k_route_small writes.
+struct RouteFastParams {
+  const float* logits;
+  const uint16_t* x;
+  const uint16_t* gate_w;  // null: no shared expert
+  int T, E, k, d;
+  RouteBuffers rb;
+};
+
+__global__ void __launch_bounds__(kDecThreads, 1)
+k_route_fast(const RouteFastParams q) {
+  extern __shared__ __align__(16) uint8_t rsm[];
+  FastScratch& fs = *(FastScratch*)rsm;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = q.T, P = q.T * q.k, d = q.d;
+  DecParams p{};  // the fields the routing pieces read
+  p.logits = q.logits; p.x = q.x; p.gate_w = q.gate_w; p.T = q.T; p.E = q.E; p.k = q.k; p.d = q.d;
+  p.status = q.rb.status;
+  pdl_trigger();
+  pdl_wait();  // inputs may come from the previous kernel; the buffers written here may still be read by it
+  if (warp < 16) {
+    RouteSmallOut out, none;
+    out.topids = q.rb.topids; out.topw = q.rb.topw; out.tokidx = q.rb.tokidx; out.pw = q.rb.pw;
+    out.pairids = q.rb.pairids; out.eoff = q.rb.eoff; out.runs = q.rb.runs; out.shared_slot = kMaxExperts;
+    out.n_runs = q.rb.n_runs; out.tiles = q.rb.tiles; out.tiles_sh = q.rb.tiles_sh; out.n_tiles = q.rb.n_tiles;
+    if (route_fast_select(p, fs, out)) {
+      // (loc and glob are the same arrays here: the placement writes each result twice, harmlessly)
+      route_fast_place(p, fs, out, out);
+    } else {
+      RouteOuts ro;
+      ro.loc = out;
+      ro.glob = none;
+      route_exact(p, (RouteSmallScratch<kDecMaxT>*)(rsm + sizeof(FastScratch)), &ro, q.rb.status);
+    }
+  } else if (q.gate_w) {
+    const int gtid = tid - 512, gw = warp - 16;
+#pragma unroll 1
+    for (int t = 0; t < T; t++) {
+      double a = 0;
+      const uint4* xv = (const uint4*)(q.x + (size_t)t * d);
+      const uint4* gv = (const uint4*)q.gate_w;
+#pragma unroll 1
+      for (int c = gtid; c < d / 8; c += 512) {
+        const uint4 xa = xv[c], ga = __ldg(gv + c);
+        const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, gq[4] = {ga.x, ga.y, ga.z, ga.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          a += (double)__uint_as_float(gq[i] << 16) * (double)__uint_as_float(xw[i] << 16);
+          a += (double)__uint_as_float(gq[i] & 0xFFFF0000u) * (double)__uint_as_float(xw[i] & 0xFFFF0000u);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1)
+        a += __hiloint2double(__shfl_xor_sync(0xffffffffu, __double2hiint(a), o),
+                              __shfl_xor_sync(0xffffffffu, __double2loint(a), o));
+      if (lane == 0) fs.gpart[t][gw] = a;
+    }
+  }
+  __syncthreads();
+  if (q.gate_w && tid < T) {
+    double tot = 0;
+#pragma unroll 1
+    for (int w2 = 0; w2 < 16; w2++) tot += fs.gpart[tid][w2];
+    const float gate = sigmoid_f32((float)tot);
+    q.rb.sgate[tid] = gate;
+    q.rb.tokidx[P + tid] = tid;
+    q.rb.pw[P + tid] = gate;
+  }
+}
+
 }  // namespace
 
 int decode_max_tokens() { return kDecMaxT; }
@@ -998,7 +1117,7 @@ bool decode_supported(const Image& gu, const Image& dn, const Image* sh_gu, cons
 cudaError_t launch_decode(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, const float* logits,
                           const int32_t* ids, const float* w, int stride, const void* x_bf16, const uint16_t* gate_w, int T,
                           int E, int k, int d, int mid, __half* hid16, void* out_bf16, const float* hc_w4, void* hc_state,
-                          const RouteBuffers& rb, unsigned* bar, int32_t* status, cudaStream_t st, unsigned long long* trace) {
+                          const RouteBuffers& rb, unsigned long long* bar, int32_t* status, cudaStream_t st, unsigned long long* trace) {
   static bool attr_done = false;
   static int sms = 0;
   const int smem = (int)(kDecSmemEnd - 1024);
@@ -1025,6 +1144,23 @@ cudaError_t launch_decode(const Image& gu, const Image& dn, const Image* sh_gu, 
   p.hid = hid16; p.out = (uint16_t*)out_bf16; p.hc_w4 = hc_w4; p.hc_state = (uint16_t*)hc_state;
   p.rb = rb; p.bar = bar; p.status = status; p.trace = trace;
   return launch_pdl(k_decode, dim3(sms), dim3(kDecThreads), (size_t)smem, st, p);
+}
+
+
+// Routing stage of a decode call (logits given, T <= decode_max_tokens(), T*k <= 128) in one launch;
+// same outputs as launch_route_small.
+cudaError_t launch_route_fast(const RouteBuffers& rb, const float* logits, int T, int k, int E, const void* x_bf16,
+                              const uint16_t* gate_w_bf16, int d, cudaStream_t st) {
+  static bool attr_done = false;
+  const int smem = (int)(sizeof(FastScratch) + sizeof(RouteSmallScratch<kDecMaxT>));
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(k_route_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  RouteFastParams q{};
+  q.logits = logits; q.x = (const uint16_t*)x_bf16; q.gate_w = gate_w_bf16; q.T = T; q.E = E; q.k = k; q.d = d; q.rb = rb;
+  return launch_pdl(k_route_fast, dim3(1), dim3(kDecThreads), (size_t)smem, st, q);
 }
 
 }  // namespace b200moe

@@ -119,7 +119,7 @@ cudaError_t launch_down_gemv(const Image& img, const Image* img_sh, const __half
 // Routing (from logits, or from the caller's ids / w when logits is null), gate/up GEMV + SwiGLU,
 // down GEMV and the weighted combine in one launch; every expert is read once for all the rows
 // that use it. sh_gu / sh_dn: the shared expert's images or null. hid16: workspace
-// [T*k + T][mid]. bar: two zero-initialised words in device memory (grid-wide barrier).
+// [T*k + T][mid]. bar: one zero-initialised 64-bit word in device memory (grid-wide barrier).
 // out_bf16, or hc_w4 + hc_state for the residual write-back. x_bf16 must be 16-byte aligned.
 int decode_max_tokens();
 bool decode_supported(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, int T, int k, int E, int d,
@@ -127,8 +127,13 @@ bool decode_supported(const Image& gu, const Image& dn, const Image* sh_gu, cons
 cudaError_t launch_decode(const Image& gu, const Image& dn, const Image* sh_gu, const Image* sh_dn, const float* logits,
                           const int32_t* ids, const float* w, int stride, const void* x_bf16, const uint16_t* gate_w, int T,
                           int E, int k, int d, int mid, __half* hid16, void* out_bf16, const float* hc_w4, void* hc_state,
-                          const RouteBuffers& rb, unsigned* bar, int32_t* status, cudaStream_t st,
+                          const RouteBuffers& rb, unsigned long long* bar, int32_t* status, cudaStream_t st,
                           unsigned long long* trace = nullptr);  // trace: debug, [SMs][8] phase time stamps of the last launch
+
+// The routing stage alone with the decode kernel's compact router (logits given, T <= decode_max_tokens(),
+// T*k <= 128, x 16-byte aligned when gate_w_bf16 is given); same outputs as launch_route_small.
+cudaError_t launch_route_fast(const RouteBuffers& rb, const float* logits, int T, int k, int E, const void* x_bf16,
+                              const uint16_t* gate_w_bf16, int d, cudaStream_t st);
 
 // Bounded wait (2 s) until n <= 32 flags written by other GPUs have reached `expected`; a
 // timeout sets status {3, flag index}.

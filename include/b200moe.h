@@ -50,6 +50,13 @@ enum {
   B200MOE_GEMM_TC = 2      /* tcgen05 grouped GEMM even for T <= decode_max_tokens */
 };
 
+/* How decode / verify calls (T <= decode_max_tokens) of q4cp layers run. */
+enum {
+  B200MOE_DECODE_AUTO = 0,   /* routing, gate/up GEMV, down GEMV, combine as four kernels chained by programmatic dependent launch */
+  B200MOE_DECODE_FUSED = 1   /* T <= 8: ONE kernel for the whole call; every expert is read once for all the rows that use it
+                                (the reference's expert dedup, src/gpu/parts/26_kernels_moe_gguf.inc:749-793), bit-identical to T = 1 */
+};
+
 typedef struct {
   int32_t experts;        /* routed experts E (<= 512, as in k_router_topk, src/gpu/parts/20_kernels_gemv.inc:1443) */
   int32_t topk;           /* experts per token k (<= 16) */
@@ -64,7 +71,8 @@ typedef struct {
   int32_t ep_rank;        /* expert-parallel rank and size; size 1 = single GPU */
   int32_t ep_size;
   int32_t ep_sm_margin;   /* expert parallelism: SMs the grouped GEMM leaves free for the all-to-all kernels */
-  int32_t reserved[3];
+  int32_t decode_impl;    /* B200MOE_DECODE_*: how calls of T <= decode_max_tokens run */
+  int32_t reserved[2];
 } b200moe_config;
 
 /* Replaces: GpuModel construction of the MoE workspaces (src/gpu/parts/40_model.inc:611-655)

@@ -37,7 +37,7 @@ def test_version_and_status_strings():
 
 def _create(**kw):
     base = dict(experts=8, topk=2, d_model=128, d_mid=64, n_layers=1, max_tokens=4, has_shared=0,
-                device=0, gemm_impl=0, decode_max_tokens=0, ep_rank=0, ep_size=1, ep_sm_margin=0)
+                device=0, gemm_impl=0, decode_max_tokens=0, ep_rank=0, ep_size=1, ep_sm_margin=0, decode_impl=0)
     base.update(kw)
     cfg = pkg.Config(*[base[n] for n, _ in pkg.Config._fields_[:-1]])
     h = ctypes.c_void_p()

@@ -59,14 +59,16 @@ def check_integer_routing(op, logits, k, E):
     return ids
 
 
+@pytest.mark.parametrize("decode_impl", [pkg.DECODE_AUTO, pkg.DECODE_FUSED])
 @pytest.mark.parametrize("T", [1, 5])
-def test_config2_decode_and_verify(cuda, big_layer, T):
-    """Decode (T=1) and verify (T=5) of the benchmark layer with its shared expert: GEMV path."""
+def test_config2_decode_and_verify(cuda, big_layer, T, decode_impl):
+    """Decode (T=1) and verify (T=5) of the benchmark layer with its shared expert: the chained
+    GEMV kernels and the one-kernel variant."""
     torch = cuda
     spec = synth.CONFIG2
     logits = synth.make_logits(synth.rng_for(200, T), T, spec.experts)
     xb = synth.make_x(synth.rng_for(200, 9), T, spec.d)
-    op = make_op(torch, spec, 16, layer=big_layer)
+    op = make_op(torch, spec, 16, layer=big_layer, decode_impl=decode_impl)
     y = run_layer(torch, op, spec, xb, logits)
     check_integer_routing(op, logits, spec.topk, spec.experts)
     y_o, _, _ = oracle.moe_forward(spec, big_layer, synth.bf16_bits_to_f32(xb), logits=logits)
@@ -197,19 +199,21 @@ def test_odd_k_block_count_in_down_gemm(cuda, mid):
 
 
 # ---------------------------------------------------------------- invariance audits on the production kernels
-def test_row_invariance_gemv_path(cuda):
+@pytest.mark.parametrize("decode_impl", [pkg.DECODE_AUTO, pkg.DECODE_FUSED])
+def test_row_invariance_gemv_path(cuda, decode_impl):
     """A token's bytes do not depend on the other tokens of the call on the decode paths either
-    (the reference's audit, tools/ktest.cu:920-923, 1152-1271). The fused decode kernel (T <= 8)
-    reads an expert once for all the rows that use it: a token alone (T=1, the plain path) equals
-    its row inside T=2, 5 and 8 calls bit for bit, which is the reference's "dedup == plain" check
-    (tools/moe_gguf_gemv_test.cu:197-223). The separate GEMV kernels (9 <= T <= 16) likewise
-    among themselves. The routing is drawn from 12 experts so that several tokens share experts."""
+    (the reference's audit, tools/ktest.cu:920-923, 1152-1271). The one-kernel decode (T <= 8,
+    decode_impl = fused) reads an expert once for all the rows that use it: a token alone (T=1, the
+    plain path) equals its row inside T=2, 5 and 8 calls bit for bit, which is the reference's
+    "dedup == plain" check (tools/moe_gguf_gemv_test.cu:197-223). The chained GEMV kernels
+    likewise among themselves (all T <= 16; with the fused implementation 9 <= T <= 16). The routing
+    is drawn from 12 experts so that several tokens share experts."""
     torch = cuda
     spec = synth.LayerSpec(experts=12, topk=4, d=512, mid=256, shared=True, book="random")
     layer = synth.make_layer(spec, seed=71)
     logits = synth.make_logits(synth.rng_for(71, 1), 16, spec.experts)
     xb = synth.make_x(synth.rng_for(71, 9), 16, spec.d)
-    op = make_op(torch, spec, 16, layer=layer)
+    op = make_op(torch, spec, 16, layer=layer, decode_impl=decode_impl)
     y8 = run_layer(torch, op, spec, xb[:8], logits[:8])
     counts = np.bincount(op.get_routing(8)[0][:, :spec.topk].reshape(-1), minlength=spec.experts)
     assert counts.max() >= 3, "the test wants an expert shared by three or more rows"
@@ -325,3 +329,59 @@ def test_caller_ids_out_of_range_are_dropped(cuda, T):
     assert np.array_equal(eoff2.cpu().numpy(), eoff) and np.array_equal(pid2.cpu().numpy(), pid)
     assert np.array_equal(tok2.cpu().numpy()[:T * 2 - 1], tok[:T * 2 - 1])
     op.close()
+
+
+@pytest.mark.parametrize("shape", [dict(experts=64, topk=10, d=512, mid=256, shared=True),
+                                   dict(experts=16, topk=4, d=2560, mid=640, shared=True, book="random"),
+                                   dict(experts=8, topk=2, d=256, mid=192, shared=False, book="random"),
+                                   dict(experts=100, topk=16, d=384, mid=2048, shared=True)])
+def test_fused_decode_kernel_shapes(cuda, shape):
+    """The one-kernel decode on shapes that exercise its corners: fewer K blocks than warps, an
+    intermediate size beyond one 32-group per warp, E not a power of two with k = 16, no shared
+    expert; T = 1..8 against the oracle, the caller-ids entry point, and the residual write-back."""
+    torch = cuda
+    spec = synth.LayerSpec(**shape)
+    layer = synth.make_layer(spec, seed=75)
+    op = make_op(torch, spec, 8, layer=layer, decode_impl=pkg.DECODE_FUSED)
+    for T in (1, 3, 8):
+        logits = synth.make_logits(synth.rng_for(75, T), T, spec.experts)
+        xb = synth.make_x(synth.rng_for(75, 9), T, spec.d)
+        y_o, ids_o, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+        y = run_layer(torch, op, spec, xb, logits)
+        ids, w, tok, pw, eoff, pid = op.get_routing(T)
+        assert np.array_equal(ids[:, :spec.topk], ids_o[:, :spec.topk])
+        tok_o, pw_o, eoff_o, pid_o = oracle.route(ids, w, spec.topk, spec.experts)
+        assert np.array_equal(tok, tok_o) and np.array_equal(eoff, eoff_o) and np.array_equal(pid, pid_o)
+        assert_output_close(y, y_o, "fused decode %r T=%d" % (shape, T))
+        # the seam below the router: caller-supplied ids and weights give the same bytes
+        x = bf16_tensor(torch, xb, (T, spec.d))
+        out = torch.full((T, spec.d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        op.moe_q4w_run(0, x, torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), out)
+        op.synchronize()
+        assert np.array_equal(bits(bf16_out_to_f32(torch, out)), bits(y))
+    op.close()
+
+
+def test_fused_decode_near_tie_takes_the_exact_router(cuda):
+    """Two logits of a token's leaders closer than 1e-6: the compact router hands the call to the
+    general routing body (the reference's arithmetic); ids and order are the oracle's either way."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=64, topk=4, d=256, mid=128, shared=True)
+    layer = synth.make_layer(spec, seed=76)
+    T = 3
+    logits = synth.make_logits(synth.rng_for(76, 1), T, spec.experts)
+    top = np.argsort(-logits[1])[:2]
+    logits[1, top[1]] = np.nextafter(logits[1, top[0]], np.float32(-np.inf))    # one ulp below the leader
+    xb = synth.make_x(synth.rng_for(76, 9), T, spec.d)
+    y_o, ids_o, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
+    _, _, probs = oracle.router_topk(logits, spec.topk, want_probs=True)
+    for impl in (pkg.DECODE_AUTO, pkg.DECODE_FUSED):
+        op = make_op(torch, spec, 8, layer=layer, decode_impl=impl)
+        y = run_layer(torch, op, spec, xb, logits)
+        ids = op.get_routing(T)[0]
+        if oracle.count_topk_ties(probs, spec.topk) == 0:
+            assert np.array_equal(ids[:, :spec.topk], ids_o[:, :spec.topk])
+        else:   # the two probabilities are one float: the rule is the lowest id first
+            assert sorted(ids[1, :2].tolist()) == sorted(top.tolist()) and ids[1, 0] == min(top)
+        assert_output_close(y, y_o, "near tie impl %d" % impl)
+        op.close()
