@@ -271,7 +271,9 @@ def main():
     ap.add_argument("--zipf-strength", type=float, default=1.0,
                     help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
     ap.add_argument("--ep-split", type=int, default=1,
-                    help="N>1, p2p transport: 1 (default) = GEMMs over a rank's own rows run apart from those over the other ranks' rows; 0 = one GEMM pass per chunk")
+                    help="N>1, p2p transport: 1 (default) = the rows a rank keeps are multiplied in place (no copy), apart from the other ranks' rows; 0 = one GEMM pass per chunk over copied rows")
+    ap.add_argument("--own-order", default="first", choices=["first", "ends"],
+                    help="N>1, --ep-split 1: the in-place own-rows passes all up front, or the last chunk's at the very end")
     ap.add_argument("--check", type=int, default=1,
                     help="N>1: 1 (default) = compare rank 0's output with the single-GPU operator on the same tokens; 0 = skip")
     ap.add_argument("--no-gguf", action="store_true", help="skip the GGUF-variant leg (Q4_K gate/up, Q5_1 down, 8192 tokens)")
@@ -323,7 +325,7 @@ def main():
         placement = ep.greedy_placement(load, world)
         epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement,
                                    chunks=args.chunks, sm_margin=args.sm_margin, transport=args.transport,
-                                   split_local=args.ep_split == 1)
+                                   split_local=args.ep_split == 1, own_order=args.own_order)
         epm.load_q4cp(0, gu, dn)
         op = epm.op
     else:

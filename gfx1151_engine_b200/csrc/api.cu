@@ -67,6 +67,7 @@ struct b200moe_ctx {
   long long ep_cap_rows = 0;
   int ep_max_tiles = 0;
   TcPlan* tc_ep = nullptr;
+  TcPlan* tc_own = nullptr;        // own-rows pass in place: activations from x_send, results into pairs_back
   int64_t launches = 0;
   // stage timer: ring of event sets, one set (7 events) per forward call
   bool prof = false;
@@ -330,6 +331,7 @@ int b200moe_destroy(b200moe_handle h) {
   if (h->ep_tiles) cudaFree(h->ep_tiles);
   if (h->ep_counts) cudaFree(h->ep_counts);
   if (h->tc_ep) tc_destroy(h->tc_ep);
+  if (h->tc_own) tc_destroy(h->tc_own);
   for (auto& e : h->prof_ev) cudaEventDestroy(e);
   if (h->s_in) cudaStreamDestroy(h->s_in);
   if (h->s_out) cudaStreamDestroy(h->s_out);
@@ -985,7 +987,6 @@ int b200moe_share_weights(b200moe_handle h, b200moe_handle owner) {
 int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_recv, void* pairs_back,
                       int64_t cap_rows) {
   if (!h || !x_send || !x_recv || !pairs_recv || !pairs_back || cap_rows < 1) return B200MOE_ERR_BAD_ARG;
-  if (h->cfg.has_shared) return fail(h, B200MOE_ERR_UNSUPPORTED, "expert parallelism with a shared expert is not implemented");
   if (h->cfg.gemm_impl == B200MOE_GEMM_SIMT) return fail(h, B200MOE_ERR_UNSUPPORTED, "expert parallelism needs the tensor-core path");
   CU_TRY(h, cudaSetDevice(h->cfg.device));
   h->ep_x_send = (__half*)x_send;
@@ -997,11 +998,17 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   if (h->ep_hid) cudaFree(h->ep_hid), h->ep_hid = nullptr;
   if (h->ep_tiles) cudaFree(h->ep_tiles), h->ep_tiles = nullptr;
   if (h->tc_ep) tc_destroy(h->tc_ep), h->tc_ep = nullptr;
-  CU_TRY(h, cudaMalloc((void**)&h->ep_hid, (size_t)cap_rows * h->cfg.d_mid * 2 + 256));
+  if (h->tc_own) tc_destroy(h->tc_own), h->tc_own = nullptr;
+  // the hidden rows of the received rows (indexed like x_recv) and of the own-rows pass in place
+  // (indexed like x_send, the shared expert's rows behind the routed ones)
+  const long long hid_rows = std::max<long long>(cap_rows, h->max_rows);
+  CU_TRY(h, cudaMalloc((void**)&h->ep_hid, (size_t)hid_rows * h->cfg.d_mid * 2 + 256));
   CU_TRY(h, cudaMalloc((void**)&h->ep_tiles, (size_t)h->ep_max_tiles * sizeof(Tile)));
   if (!h->ep_counts) CU_TRY(h, cudaMalloc((void**)&h->ep_counts, 16));
   CU_TRY(h, tc_create(&h->tc_ep, h->ep_x_recv, h->ep_hid, cap_rows, h->cfg.d_model, h->cfg.d_mid));
+  CU_TRY(h, tc_create(&h->tc_own, h->ep_x_send, h->ep_hid, h->max_rows, h->cfg.d_model, h->cfg.d_mid));
   tc_set_sm_margin(h->tc_ep, h->cfg.ep_sm_margin);
+  tc_set_sm_margin(h->tc_own, h->cfg.ep_sm_margin);
   return B200MOE_OK;
 }
 
@@ -1011,6 +1018,9 @@ int b200moe_ep_route(b200moe_handle h, int layer, const void* x, int T, const fl
   if (!x || !logits || T < 1 || T > h->cfg.max_tokens || !h->ep_x_send)
     return fail(h, B200MOE_ERR_BAD_ARG, "ep_route: bad argument or buffers not attached");
   const b200moe_config& c = h->cfg;
+  LayerWeights& L = h->layers[layer];
+  const bool shared = c.has_shared != 0;
+  if (shared && !L.shared_loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "ep_route: shared expert not loaded");
   cudaStream_t st = (cudaStream_t)stream;
   int n = 0;
   CU_TRY(h, launch_router_topk(logits, T, c.experts, c.topk, h->rb.topids, h->rb.topw, kIdStride, st));
@@ -1019,7 +1029,12 @@ int b200moe_ep_route(b200moe_handle h, int layer, const void* x, int T, const fl
     n++;
   }
   CU_TRY(h, launch_route(h->rb, h->rb.topids, h->rb.topw, kIdStride, T, c.topk, c.experts, h->tile_cap, st, &n));
-  CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, T * c.topk, c.d_model, h->ep_x_send, st));
+  if (shared) {
+    // the shared expert stays on the token's own rank: its rows (token order) follow the routed ones
+    CU_TRY(h, launch_shared_gate(x, L.sh_gate_w, T, c.d_model, c.topk, h->rb, st));
+    n++;
+  }
+  CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, T * c.topk + (shared ? T : 0), c.d_model, h->ep_x_send, st));
   if (eoff_out)
     CU_TRY(h, cudaMemcpyAsync(eoff_out, h->rb.eoff, ((size_t)c.experts + 1) * 4, cudaMemcpyDeviceToDevice, st));
   h->launches += n + 2;
@@ -1038,15 +1053,32 @@ int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev,
 
 int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream) {
   if (int s = check_layer(h, layer)) return s;
-  if (!eoff_all_dev || !h->tc_ep || part < 0 || part > 2)
+  if (!eoff_all_dev || !h->tc_ep || part < 0 || part > 3)
     return fail(h, B200MOE_ERR_BAD_ARG, "ep_experts: bad argument or buffers not attached");
   LayerWeights& L = h->layers[layer];
-  if (!L.loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "ep_experts: layer weights not loaded");
   const b200moe_config& c = h->cfg;
+  const bool shared = c.has_shared != 0;
+  if (!L.loaded || (shared && !L.shared_loaded)) return fail(h, B200MOE_ERR_NOT_LOADED, "ep_experts: layer weights not loaded");
   cudaStream_t st = (cudaStream_t)stream;
   const int El = local_experts(c);
   CU_TRY(h, launch_ep_tiles(eoff_all_dev, c.ep_size, c.experts, first_expert(c), El, h->tile_cap, h->ep_tiles,
                             h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part));
+  if (part == 3) {
+    // own rows in place: activations straight from the send buffer, results straight into the
+    // result buffer (same row order) -- no copy in either direction; the shared expert, which
+    // never leaves the token's rank, rides along
+    CU_TRY(h, launch_up_tc(h->tc_own, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
+    if (shared)
+      CU_TRY(h, launch_up_tc(h->tc_own, L.sh_gu, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh, h->ep_hid, h->status_dev, st));
+    CU_TRY(h, launch_down_tc(h->tc_own, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_back, h->status_dev, st));
+    if (shared)
+      CU_TRY(h, launch_down_tc(h->tc_own, L.sh_dn, h->rb.tiles_sh, h->rb.n_tiles + 1, h->max_tiles_sh, h->ep_pairs_back,
+                               h->status_dev, st));
+    h->launches += shared ? 5 : 3;
+    return B200MOE_OK;
+  }
+  if (shared)
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "ep_experts: with a shared expert the own rows must run in place (part 3 + part 2)");
   CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
   CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv,
                            h->status_dev, st));
@@ -1056,8 +1088,8 @@ int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all
 
 int b200moe_ep_combine(b200moe_handle h, int T, void* out, void* stream) {
   if (!h || !out || T < 1 || T > h->cfg.max_tokens || !h->ep_pairs_back) return B200MOE_ERR_BAD_ARG;
-  CU_TRY(h, launch_combine_f16(h->ep_pairs_back, h->rb.pw, h->rb.pairids, T, h->cfg.topk, h->cfg.d_model, -1, out,
-                               (cudaStream_t)stream));
+  CU_TRY(h, launch_combine_f16(h->ep_pairs_back, h->rb.pw, h->rb.pairids, T, h->cfg.topk, h->cfg.d_model,
+                               h->cfg.has_shared ? T * h->cfg.topk : -1, out, (cudaStream_t)stream));
   h->launches++;
   return B200MOE_OK;
 }

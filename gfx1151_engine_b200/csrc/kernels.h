@@ -92,7 +92,7 @@ cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E
                                    cudaStream_t st);
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
                             Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st,
-                            int own_rank = 0, int part = 0);  // part 1: rows from own_rank only, 2: all others
+                            int own_rank = 0, int part = 0);  // part 1: rows from own_rank only, 2: all others, 3: own rows at their place in the send buffer
 
 // ---- expert_simt.cu ----
 cudaError_t launch_up_simt(const Image& img, const void* x_bf16, int d, int mid,

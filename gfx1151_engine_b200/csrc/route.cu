@@ -388,8 +388,10 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
       const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
       first += e2[e0 + El] - e2[e0];
     }
-    // part 1: only the rows this rank sent to itself; part 2: only the other ranks' rows
-    if ((part == 1 && src != own) || (part == 2 && src == own)) cnt = 0;
+    // part 1: only the rows this rank sent to itself; part 2: only the other ranks' rows;
+    // part 3: this rank's own rows where they lie in its SEND buffer (row = its own expert offset)
+    if ((part == 1 && src != own) || (part == 2 && src == own) || (part == 3 && src != own)) cnt = 0;
+    if (part == 3) first = eo[e0 + e];
   }
   const int nfull = cnt / tile_cap, rag = cnt % tile_cap;
   s_c[tid] = nfull;

@@ -75,6 +75,24 @@ def p2p_plan(eoff_all, rank, world):
     return dispatch, back, int(cnt[:, rank].sum())
 
 
+def recv_rows_all(eoff_all, world):
+    """Rows every rank receives (all sources), from the offset tables every rank holds: each rank
+    can therefore see an overflow of ANY rank's receive buffer and all of them stop together,
+    before a single row has been copied."""
+    eo = np.asarray(eoff_all).reshape(world, -1)
+    per = (eo.shape[1] - 1) // world
+    bd = eo[:, ::per].astype(np.int64)
+    return (bd[:, 1:] - bd[:, :-1]).sum(axis=0)
+
+
+def next_seq(seq):
+    """Sequence number of the next forward as a signed 32-bit value that wraps around: the
+    device-side wait compares `flag - expected >= 0` in 32-bit arithmetic, which stays right
+    across the wrap as long as two live numbers are less than 2^31 apart."""
+    seq = (seq + 1) & 0xFFFFFFFF
+    return seq - (1 << 32) if seq >= (1 << 31) else seq
+
+
 class ExpertParallelMoe:
     """The MoE layer sharded by expert over the ranks of a torch.distributed group.
 
@@ -84,7 +102,8 @@ class ExpertParallelMoe:
     compute stream, so the NVLink time hides behind the tensor-core time."""
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
-                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False):
+                 cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False,
+                 has_shared=False, own_order="first"):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
@@ -92,14 +111,21 @@ class ExpertParallelMoe:
         # p2p transport only: GEMMs over the rows a rank sent to itself run apart from those over the
         # other ranks' rows -- first chunk: own rows first (while the others still arrive), last
         # chunk: own rows last (while the others' results already travel back)
-        self.split_local = split_local and transport == "p2p"
+        self.split_local = (split_local or has_shared) and transport == "p2p"
+        if has_shared and transport != "p2p":
+            raise ValueError("a shared expert under expert parallelism needs the p2p transport (its rows run in the in-place own-rows pass)")
+        # where the own-rows passes (which need no exchange) go: "first" = all of them up front, while
+        # the first rows travel; "ends" = first chunk's up front, last chunk's at the very end, while
+        # the last results travel back
+        self.own_order = own_order
+        self.has_shared = has_shared
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
         self.chunks = chunks
         self.tc = (max_tokens + chunks - 1) // chunks            # tokens per chunk
         dev = torch.device("cuda", device)
         self.ops, self.buf = [], []
         for c in range(chunks):
-            op = pkg.MoeOperator(experts, topk, d_model, d_mid, self.tc, device=device,
+            op = pkg.MoeOperator(experts, topk, d_model, d_mid, self.tc, device=device, has_shared=has_shared,
                                  ep_rank=rank, ep_size=world,
                                  ep_sm_margin=sm_margin if (chunks > 1 and transport == "nccl") else 0)
             if c == 0:
@@ -109,6 +135,7 @@ class ExpertParallelMoe:
                 op.share_weights(self.ops[0])
             pairs = self.tc * topk
             cap = int(cap_factor * pairs)
+            own_rows = pairs + (self.tc if has_shared else 0)   # the shared expert's rows sit behind the routed ones
             if transport == "p2p":
                 # written by the peers' copy engines: symmetric memory (mapped into every rank)
                 import torch.distributed._symmetric_memory as symm_mem
@@ -116,12 +143,13 @@ class ExpertParallelMoe:
             else:
                 remote = lambda *shape, dtype=torch.float16: torch.empty(*shape, dtype=dtype, device=dev)
             b = {"cap": cap,
-                 "x_send": torch.empty(pairs, d_model, dtype=torch.float16, device=dev),
+                 "x_send": torch.empty(own_rows, d_model, dtype=torch.float16, device=dev),
                  "x_recv": remote(cap, d_model),
                  "pairs_recv": torch.empty(cap, d_model, dtype=torch.float16, device=dev),
-                 "pairs_back": remote(pairs, d_model),
+                 "pairs_back": remote(own_rows, d_model),
                  "eoff": torch.empty(experts + 1, dtype=torch.int32, device=dev),
-                 "eoff_all": torch.empty(world * (experts + 1), dtype=torch.int32, device=dev)}
+                 "eoff_all": torch.empty(world * (experts + 1), dtype=torch.int32, device=dev),
+                 "eoff_host": torch.empty(world * (experts + 1), dtype=torch.int32).pin_memory()}
             op.ep_attach(b["x_send"], b["x_recv"], b["pairs_recv"], b["pairs_back"], cap)
             self.ops.append(op)
             self.buf.append(b)
@@ -146,7 +174,9 @@ class ExpertParallelMoe:
         group = self.group if self.group is not None else dist.group.WORLD
         self.comm2 = torch.cuda.Stream(device=dev)
         self.seq = 0
-        self.seq_src = torch.arange(1 << 16, dtype=torch.int32, device=dev)   # element i holds i
+        # the flag value of a forward: a one-element tensor filled on the copy stream; a small ring of
+        # them, because the result copies of forward n may still read theirs when forward n+1 starts
+        self.seq_ring = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(4)]
         self._handles = []
         for b in self.buf:
             b["flags"] = symm_mem.empty(2, 32, dtype=torch.int32, device=dev)  # [dispatch | return][source rank]
@@ -166,96 +196,93 @@ class ExpertParallelMoe:
         main = torch.cuda.current_stream()
         C = min(self.chunks, (T + self.tc - 1) // self.tc)
         span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
-        # my own result copies of the previous forward read pairs_recv: with the own-rows pass first,
-        # nothing else orders them before this forward's first GEMM writes that buffer
-        if getattr(self, "_back_done", None) is not None:
-            main.wait_event(self._back_done)
-        self.seq += 1
-        if self.seq >= (1 << 16):
-            raise RuntimeError("sequence numbers of the copy-engine transport exhausted")
+        self.seq = next_seq(self.seq)
         seq = self.seq
+        seq_t = self.seq_ring[seq & 3]
+        # 1. routing of every chunk; the offset tables of all ranks travel to the host one chunk at a
+        #    time, so that the host can plan (and start) chunk 0's copies while chunk 1 still routes
+        routed, tables = [], []
         for c, (a, b) in enumerate(span):
             B = self.buf[c]
             self.ops[c].ep_route(layer, x[a:b], logits[a:b], eoff_out=B["eoff"], stream=main)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            routed.append(ev)
             dist.all_gather_into_tensor(B["eoff_all"], B["eoff"], group=self.group)
-        routed = torch.cuda.Event()
-        routed.record(main)
+            B["eoff_host"].copy_(B["eoff_all"], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            tables.append(ev)
+        in_place = self.split_local
+        if in_place:
+            # the rows that stay on this GPU (and the shared expert's) need no exchange: their GEMMs read
+            # the send buffer and write the result buffer in place, while the first rows travel
+            first_own = range(C) if self.own_order == "first" or C == 1 else range(C - 1)
+            for c in first_own:
+                self.ops[c].ep_experts(layer, self.buf[c]["eoff_all"], stream=main, part=3)
         plans, rows = [], 0
+        with torch.cuda.stream(self.comm):
+            seq_t.fill_(seq)
+            seq_ready = torch.cuda.Event()
+            seq_ready.record(self.comm)
         for c in range(C):
-            plan = p2p_plan(self.buf[c]["eoff_all"].cpu().numpy(), self.rank, self.world)
-            if plan[2] > self.buf[c]["cap"]:
-                raise RuntimeError("expert-parallel receive buffer too small: %d rows > capacity %d"
-                                   % (plan[2], self.buf[c]["cap"]))
+            tables[c].synchronize()
+            eo = self.buf[c]["eoff_host"].numpy()
+            need = recv_rows_all(eo, self.world)
+            if int(need.max()) > self.buf[c]["cap"]:
+                # every rank sees the same table and stops here, before any copy has been issued
+                raise RuntimeError("expert-parallel receive buffer too small: rank %d would receive %d rows, capacity %d"
+                                   % (int(need.argmax()), int(need.max()), self.buf[c]["cap"]))
+            plan = p2p_plan(eo, self.rank, self.world)
             plans.append(plan)
             rows += plan[2]
-        self.last_recv_rows = rows
-        # 1. dispatch: my rows for rank p go behind the rows of the ranks before me in p's buffer.
-        #    (p has finished reading that buffer: I waited for p's results of the previous
-        #    forward, which p sent after its GEMMs.)
-        self.comm.wait_event(routed)
-        own_in = [torch.cuda.Event() for _ in range(C)]
-        with torch.cuda.stream(self.comm):
-            if self.split_local:
-                # the rows that stay on this GPU go first: their GEMMs start without any exchange
-                for c in range(C):
-                    B = self.buf[c]
-                    for p, src0, dst0, n in plans[c][0]:
-                        if p == self.rank:
-                            if n:
-                                B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
-                            B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
-                    own_in[c].record(self.comm)
-            for c in range(C):
-                B = self.buf[c]
-                for p, src0, dst0, n in plans[c][0]:
-                    if self.split_local and p == self.rank:
-                        continue
-                    if n:
+            # 2. dispatch of the chunk: my rows for rank p go behind the rows of the ranks before me in
+            #    p's buffer. (p has finished reading that buffer: I waited for p's results of the
+            #    previous forward, which p sent after its GEMMs.)
+            B = self.buf[c]
+            self.comm.wait_event(routed[c])
+            with torch.cuda.stream(self.comm):
+                for p, src0, dst0, n in plan[0]:
+                    if n and not (in_place and p == self.rank):
                         B["peer_x_recv"][p][dst0:dst0 + n].copy_(B["x_send"][src0:src0 + n], non_blocking=True)
-                    B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
+                    B["peer_flags"][p][0, self.rank:self.rank + 1].copy_(seq_t, non_blocking=True)
+        self.last_recv_rows = rows
+        self.comm2.wait_event(seq_ready)
 
-        def send_back(c, which):
-            # which: None = every source, True = only my own rows, False = only the other ranks' rows
+        def send_back(c):
             B = self.buf[c]
             done = torch.cuda.Event()
             done.record(main)
             self.comm2.wait_event(done)
             with torch.cuda.stream(self.comm2):
                 for s, src0, dst0, n in plans[c][1]:
-                    if which is not None and (s == self.rank) != which:
-                        continue
-                    if n:
+                    if n and not (in_place and s == self.rank):
                         B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
-                    B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(self.seq_src[seq:seq + 1], non_blocking=True)
+                    B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(seq_t, non_blocking=True)
 
-        # 2. experts per chunk once its rows have arrived; results go straight back to their owners
+        # 3. experts per chunk once its rows have arrived; results go straight back to their owners
         for c in range(C):
             B = self.buf[c]
-            if not self.split_local:
-                self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
-                self.ops[c].ep_experts(layer, B["eoff_all"], stream=main)
-                send_back(c, None)
-                continue
-            own_first = c < C - 1 or C == 1
-            for own in ((True, False) if own_first else (False, True)):
-                if own:
-                    main.wait_event(own_in[c])
-                    self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=1)
-                else:
-                    self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
-                    self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=2)
-                send_back(c, own)
-        # 3. combine
+            self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
+            self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=2 if in_place else 0)
+            send_back(c)
+        if in_place and self.own_order != "first" and C > 1:
+            self.ops[C - 1].ep_experts(layer, self.buf[C - 1]["eoff_all"], stream=main, part=3)
+        # 4. combine
         for c, (a, b) in enumerate(span):
             B = self.buf[c]
             self.ops[c].ep_wait_flags(B["flags"][1], self.world, seq, stream=main)
             self.ops[c].ep_combine(out[a:b], b - a, stream=main)
-        self._back_done = torch.cuda.Event()
-        self._back_done.record(self.comm2)
 
     def load_q4cp(self, layer, gate_up, down):
         """Every rank passes the full tensors; the library keeps this rank's experts."""
         self.ops[0].load_q4cp(layer, gate_up, down)
+        for op in self.ops[1:]:
+            op.share_weights(self.ops[0])
+
+    def load_shared_q4cp(self, layer, gate, up, down, gate_w_bf16):
+        """The shared expert is not sharded: every rank holds it and runs it for its own tokens."""
+        self.ops[0].load_shared_q4cp(layer, gate, up, down, gate_w_bf16)
         for op in self.ops[1:]:
             op.share_weights(self.ops[0])
 

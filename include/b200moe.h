@@ -218,7 +218,10 @@ int b200moe_route_static(const int32_t* topids_dev, const float* topw_dev, int s
  *   (all-to-all of pairs_recv back into pairs_back, which then has x_send's row order)
  *   ep_combine:  weighted top-k combine of this rank's tokens.
  * ep_attach hands the library the four fp16 row buffers [rows][d_model] (caller-owned device
- * memory: x_send and pairs_back hold max_tokens*topk rows, x_recv and pairs_recv cap_rows). */
+ * memory: x_send and pairs_back hold max_tokens*topk rows -- plus max_tokens rows behind them when
+ * the layer has a shared expert -- x_recv and pairs_recv cap_rows). A shared expert is not
+ * sharded: every rank holds it and runs it for its own tokens (rows max_tokens*topk.. of x_send /
+ * pairs_back, in token order), as part of the in-place own-rows pass (part 3 below). */
 int b200moe_ep_set_placement(b200moe_handle h, const int32_t* placed_id_of_expert_host);
 /* Makes `h` use the repacked weights (and placement) of `owner` instead of holding its own:
  * several handles with separate workspaces can then work on different token chunks of the same
@@ -234,7 +237,11 @@ int b200moe_ep_offsets(b200moe_handle h, const int32_t** eoff_dev);
 int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev, void* stream);
 /* The same over a part of the received rows: part 1 = the rows this rank sent to itself (they need
  * no exchange, so their GEMMs can run while the other ranks' rows are still arriving), part 2 = the
- * other ranks' rows, 0 = all. Parts 1 and 2 together write what part 0 writes. */
+ * other ranks' rows, 0 = all. Parts 1 and 2 together write what part 0 writes. Part 3 = the own
+ * rows IN PLACE: read from x_send where ep_route left them and written to pairs_back where
+ * ep_combine expects them -- neither direction is copied -- together with the shared expert's rows
+ * when the layer has one. A forward is then part 3 + part 2; the own segment of x_recv / pairs_recv
+ * stays unused. */
 int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream);
 int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream);
 /* For hosts that move the rows with peer copies (copy engines) instead of a collective: every

@@ -99,3 +99,44 @@ def test_p2p_plan_moves_every_row_there_and_back():
             back[s][dst0:dst0 + n] = recv[r][src0:src0 + n]
     for r in range(world):
         assert np.array_equal(back[r], sends[r])
+
+
+def test_sequence_numbers_wrap_and_stay_comparable():
+    """The copy-engine transport numbers its forwards with a signed 32-bit value that wraps; the
+    device-side wait compares `flag - expected >= 0` in 32-bit arithmetic. Far more forwards than
+    the 65535 an earlier version allowed, and across the wrap the newer number still compares as
+    reached while an older one does not."""
+    from gfx1151_engine_b200 import ep
+
+    def reached(flag, expected):          # the kernel's comparison, in int32 arithmetic
+        return np.int32(np.uint32(flag & 0xFFFFFFFF) - np.uint32(expected & 0xFFFFFFFF)) >= 0
+
+    seq = 0
+    for _ in range(70000):
+        nxt = ep.next_seq(seq)
+        assert nxt == seq + 1 and reached(nxt, nxt) and reached(nxt, seq) and not reached(seq, nxt)
+        seq = nxt
+    seq = 2 ** 31 - 3
+    for _ in range(8):
+        nxt = ep.next_seq(seq)
+        assert -2 ** 31 <= nxt < 2 ** 31
+        assert reached(nxt, nxt) and reached(nxt, seq) and not reached(seq, nxt)
+        seq = nxt
+    assert seq < 0                         # the numbers went through the wrap
+
+
+def test_every_rank_sees_every_receive_count():
+    """recv_rows_all gives all ranks' receive counts from the table every rank holds, so that an
+    overflow of one rank's buffer stops all ranks together (no rank is left waiting for rows)."""
+    from gfx1151_engine_b200 import ep
+    world, E, k, T = 4, 16, 2, 50
+    rng = np.random.default_rng(3)
+    tables = []
+    for r in range(world):
+        ids = rng.integers(0, E, size=T * k)
+        tables.append(np.concatenate([[0], np.cumsum(np.bincount(ids, minlength=E))]))
+    eo = np.stack(tables)
+    need = ep.recv_rows_all(eo, world)
+    assert need.sum() == world * T * k
+    for r in range(world):
+        assert need[r] == ep.p2p_plan(eo, r, world)[2] == sum(ep.exchange_splits(eo, r, world)[1])
