@@ -1077,7 +1077,7 @@ int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all
     h->launches += shared ? 5 : 3;
     return B200MOE_OK;
   }
-  if (shared)
+  if (shared && part != 2)
     return fail(h, B200MOE_ERR_UNSUPPORTED, "ep_experts: with a shared expert the own rows must run in place (part 3 + part 2)");
   CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
   CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv,
