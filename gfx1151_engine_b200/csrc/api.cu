@@ -165,8 +165,8 @@ SrcTensor q4cp_src(const uint8_t* blob, long long rows_total, long long cols,
 }
 
 // Turns the device status word (copied to status_host) into a return code and clears it on the
-// device. {1|2|3, site}: a bounded device-side wait gave up; {4, id}: a caller-supplied expert
-// id outside [0, experts) was dropped by the bucketing.
+// device. {1|2|3|5|6, site}: a bounded device-side wait gave up; {4, id}: a caller-supplied expert
+// id outside [0, experts) was dropped by the bucketing; {7, token}: the router's near-tie list overflowed.
 int report_status(b200moe_handle h, cudaStream_t st) {
   const int code = h->status_host[0], detail = h->status_host[1];
   if (code == 0) return B200MOE_OK;
@@ -180,6 +180,11 @@ int report_status(b200moe_handle h, cudaStream_t st) {
     snprintf(buf, sizeof buf, "expert id %d outside [0, %d) in the caller's top-k ids: the pair was dropped", detail,
              h->cfg.experts);
     return fail(h, B200MOE_ERR_BAD_ARG, buf);
+  }
+  if (code == 7) {
+    snprintf(buf, sizeof buf, "router logits: more near-ties than the exact-recomputation list holds (first dropped at token %d); "
+             "the top-k order of this call is not guaranteed to be the reference's", detail);
+    return fail(h, B200MOE_ERR_TOO_LARGE, buf);
   }
   snprintf(buf, sizeof buf, "device-side wait timed out (code %d, wait site %d)", code, detail);
   return fail(h, B200MOE_ERR_DEVICE_TIMEOUT, buf);
@@ -765,10 +770,10 @@ int b200moe_router_logits(b200moe_handle h, int layer, const void* x_bf16_dev, i
     // few tokens: double sums (1e-9 from the reference), then the reference's arithmetic for
     // the experts that decide the top-k where two of them are within a few float ulps
     CU_TRY(h, launch_router_dots(x_bf16_dev, L.router_w, T, E, d, logits_dev, st));
-    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 5e-7f, h->flag_list, h->flag_count, cap, st));
+    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 5e-7f, h->flag_list, h->flag_count, cap, st, h->status_dev));
   } else {
     CU_TRY(h, launch_router_gemm(h->rplan, x_bf16_dev, L.router_w, T, E, d, logits_dev, h->status_dev, st));
-    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 1e-4f, h->flag_list, h->flag_count, cap, st));
+    CU_TRY(h, launch_router_flag(logits_dev, T, E, h->cfg.topk, 1e-4f, h->flag_list, h->flag_count, cap, st, h->status_dev));
   }
   CU_TRY(h, launch_router_pairs(x_bf16_dev, L.router_w, h->flag_list, h->flag_count, cap, E, d, logits_dev, st));
   h->launches += 3;

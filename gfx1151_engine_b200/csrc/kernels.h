@@ -152,7 +152,7 @@ cudaError_t launch_router_dots(const void* x_bf16, const void* w_bf16, int T, in
 // pairs/count <- (token * E + expert) of the experts that decide a token's top-k, for tokens
 // where two of them are closer than rel_margin x magnitude (at most cap pairs are stored)
 cudaError_t launch_router_flag(const float* logits, int T, int E, int k, float rel_margin, int32_t* pairs,
-                               int32_t* count, int cap, cudaStream_t st);
+                               int32_t* count, int cap, cudaStream_t st, int32_t* status = nullptr);  // status {7, token}: list overflow
 // the listed logits in the reference's arithmetic
 cudaError_t launch_router_pairs(const void* x_bf16, const void* w_bf16, const int32_t* pairs, const int32_t* count,
                                 int cap, int E, int d, float* logits, cudaStream_t st);

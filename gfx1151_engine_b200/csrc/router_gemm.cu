@@ -362,7 +362,7 @@ k_router_pairs(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, c
 // pair list (token * E + expert) for recomputation in the reference's arithmetic.
 __global__ void __launch_bounds__(256)
 k_router_flag(const float* __restrict__ logits, int T, int E, int k, float rel_margin, int32_t* __restrict__ pairs,
-              int32_t* __restrict__ count, int cap) {
+              int32_t* __restrict__ count, int cap, int32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -409,6 +409,9 @@ k_router_flag(const float* __restrict__ logits, int T, int E, int k, float rel_m
     if (v0[j] >= floor_v) {
       const int i = atomicAdd(count, 1);
       if (i < cap) pairs[i] = t * E + j * 32 + lane;
+      // more near-ties than the list holds: those logits keep their GEMM values, the order of
+      // the top-k is then not guaranteed to be the reference's -- say so instead of hiding it
+      else if (status && atomicCAS(status, 0, 7) == 0) status[1] = t;
     }
 }
 
@@ -457,10 +460,10 @@ cudaError_t launch_router_gemm(RouterPlan* p, const void* x_bf16, const void* w_
 }
 
 cudaError_t launch_router_flag(const float* logits, int T, int E, int k, float rel_margin, int32_t* pairs,
-                               int32_t* count, int cap, cudaStream_t st) {
+                               int32_t* count, int cap, cudaStream_t st, int32_t* status) {
   cudaError_t e = cudaMemsetAsync(count, 0, sizeof(int32_t), st);
   if (e != cudaSuccess) return e;
-  k_router_flag<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, rel_margin, pairs, count, cap);
+  k_router_flag<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, k, rel_margin, pairs, count, cap, status);
   return cudaGetLastError();
 }
 

@@ -1,5 +1,9 @@
 """Seeded synthetic tensors in the reference's on-disk formats (numpy only).
 
+Test and benchmark data only: the product library (libb200moe.so) and its ctypes binding never
+import this module; it sits in the package so that tests, the smoke check and the benchmark find
+one generator.
+
 Stand-ins for real checkpoints, with the shapes and value distributions of the
 benchmark configurations:
   * hgn q4cp tensors (layout: src/hgn.h:5-9 of the reference): 16 x f32 code book, 4-bit

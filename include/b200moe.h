@@ -37,7 +37,7 @@ enum {
   B200MOE_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up */
   B200MOE_ERR_NCCL = 6,
   B200MOE_ERR_ALLOC = 7,
-  B200MOE_ERR_TOO_LARGE = 8     /* request exceeds the fixed capacity of b200moe_route_static */
+  B200MOE_ERR_TOO_LARGE = 8     /* request exceeds a fixed capacity: b200moe_route_static's scratch, or the router's near-tie list */
 };
 
 /* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
