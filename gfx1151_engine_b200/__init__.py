@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libb200moe.so")
 
 GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
 DECODE_AUTO, DECODE_FUSED = 0, 1
-GGML_Q5_1, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 13, 20, 23
+GGML_Q5_1, GGML_Q8_0, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 8, 12, 13, 20, 23
 
 STATUS = {0: "ok", 1: "bad argument", 2: "unsupported", 3: "CUDA error", 4: "not loaded",
           5: "device timeout", 6: "NCCL error", 7: "out of memory", 8: "too large for the static scratch"}

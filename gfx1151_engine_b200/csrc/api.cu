@@ -404,10 +404,15 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
 }
 
 // Image format, bytes per row of K elements and K granule of a GGUF block type; fmt < 0: not read.
-static void gguf_type_info(int type, bool down, size_t K, int* fmt, size_t* row_bytes, size_t* granule) {
+static void gguf_type_info(int type, bool down, size_t K, int* fmt, size_t* row_bytes, size_t* granule, int* act_shift) {
   *fmt = -1;
   *row_bytes = 0;
   *granule = 256;
+  *act_shift = 0;
+  if (type == B200MOE_GGML_Q8_0) {  // two nibble planes in the Q5_1 image form (common.cuh)
+    *fmt = kQ51, *row_bytes = K / 32 * 34, *granule = 32, *act_shift = 1;
+    return;
+  }
   if (type == B200MOE_GGML_Q4_K && !down) *fmt = kQ4K, *row_bytes = K / 256 * 144;
   else if (type == B200MOE_GGML_Q5_K && !down) *fmt = kQ51, *row_bytes = K / 256 * 176;
   else if (type == B200MOE_GGML_Q5_1 && down) *fmt = kQ51, *row_bytes = K / 32 * 24, *granule = 32;
@@ -429,13 +434,13 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
   if (!gate_src || !up_src || !down_src) return fail(h, B200MOE_ERR_BAD_ARG, "null weight pointer");
   const b200moe_config& c = h->cfg;
   const size_t E = c.experts, d = c.d_model, mid = c.d_mid;
-  int fmt_gu, fmt_dn;
+  int fmt_gu, fmt_dn, ash_gu, ash_dn;
   size_t rb_gu, rb_dn, gr_gu, gr_dn;
-  gguf_type_info(type_gu, false, d, &fmt_gu, &rb_gu, &gr_gu);
-  gguf_type_info(type_dn, true, mid, &fmt_dn, &rb_dn, &gr_dn);
+  gguf_type_info(type_gu, false, d, &fmt_gu, &rb_gu, &gr_gu, &ash_gu);
+  gguf_type_info(type_dn, true, mid, &fmt_dn, &rb_dn, &gr_dn, &ash_dn);
   if (fmt_gu < 0 || fmt_dn < 0)
     return fail(h, B200MOE_ERR_UNSUPPORTED,
-                "GGUF experts: gate/up must be Q4_K, Q5_K, IQ4_NL or IQ4_XS and down Q5_1, IQ4_NL or IQ4_XS");
+                "GGUF experts: gate/up must be Q4_K, Q5_K, Q8_0, IQ4_NL or IQ4_XS and down Q5_1, Q8_0, IQ4_NL or IQ4_XS");
   if (d % gr_gu != 0 || mid % gr_dn != 0)
     return fail(h, B200MOE_ERR_UNSUPPORTED, "GGUF experts: row length is not a whole number of blocks");
   CU_TRY(h, cudaSetDevice(c.device));
@@ -449,7 +454,8 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
   const int nl = local_experts(c), e0 = first_expert(c);
   cudaError_t e = stage(gate_src, gu_bytes, &g, tmp);
   if (e == cudaSuccess) e = stage(up_src, gu_bytes, &u, tmp);
-  if (e == cudaSuccess) e = alloc_image(L.gu, fmt_gu, nl, (int)mid, (int)d, 1);
+  if (e == cudaSuccess) e = alloc_image(L.gu, fmt_gu, nl, (int)mid, (int)d << ash_gu, 1);
+  L.gu.act_shift = ash_gu;
   if (e == cudaSuccess) {
     SrcTensor sg, su;
     sg.codes = g;
@@ -465,7 +471,8 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   free_all(tmp);
   if (e == cudaSuccess) e = stage(down_src, dn_bytes, &dn, tmp);
-  if (e == cudaSuccess) e = alloc_image(L.dn, fmt_dn, nl, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) e = alloc_image(L.dn, fmt_dn, nl, (int)d, (int)mid << ash_dn, 0);
+  L.dn.act_shift = ash_dn;
   if (e == cudaSuccess) {
     SrcTensor a;
     a.codes = dn;
@@ -631,7 +638,8 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   const bool gemv = simt && c.gemm_impl == B200MOE_GEMM_AUTO &&
                     (!shared || (L.gu.fmt == kQ4CP && L.dn.fmt == kQ4CP)) &&
                     pairs + (shared ? T : 0) <= h->dec_rows && std::min(E, pairs) + 1 <= gemv_max_runs() &&
-                    d <= gemv_max_k() && mid <= gemv_max_mid() && d % 32 == 0 && mid % 32 == 0;
+                    (d << L.gu.act_shift) <= gemv_max_k() && (mid << L.dn.act_shift) <= gemv_max_mid() && d % 32 == 0 &&
+                    mid % 32 == 0;
   if (gemv) {
     // decode / verify: persistent dequant GEMV, routed and shared expert in one launch each
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));

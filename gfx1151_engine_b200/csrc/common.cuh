@@ -27,6 +27,12 @@ enum Format : int {
   kQ4K = 1,   // meta: [r]{fp16 d, fp16 dmin, u8 sc0, u8 m0, u8 sc1, u8 m1} -> 1024 B
   kQ51 = 2    // meta: [r][2]{fp16 d, fp16 m, u32 high bits}                -> 2048 B
 };
+// GGUF Q8_0 (int8 codes q, fp16 d per 32: w = d * q) has no tile layout of its own. With the
+// biased code u = q + 128 = 16 * hi + lo the weight is d * (16 * hi - 128) + d * lo: two 4-bit
+// tensors over the SAME activations. The image is kQ51 with twice the K blocks -- for every 64
+// columns a block of the high nibbles (group constants d' = 16 d, m' = -128 d, no fifth bits)
+// followed by a block of the low nibbles (d' = d, m' = 0) -- and act_shift = 1. 16 d and 128 d are
+// exact in fp16, so every kernel reproduces d * q up to its usual single rounding.
 
 __host__ __device__ constexpr int meta_bytes(int fmt) {
   return fmt == kQ4CP ? 512 : fmt == kQ4K ? 1024 : 2048;
@@ -42,6 +48,8 @@ struct Image {
   int n_kblocks = 0;  // K / 64
   int paired = 0;     // 1: gate/up image (tile rows 0..63 gate, 64..127 the matching up rows)
   int dual_book = 0;  // 1: the two halves of a tile use different code books (separate gate / up tensors)
+  int act_shift = 0;  // 1: two-plane image of 8-bit codes (GGUF Q8_0): K block kb of the image multiplies the
+                      //    activations of K block kb >> 1 -- the high and the low nibble plane of the same 64 columns
   float* book = nullptr;  // device [32]: code book of tile rows 0..63, then of rows 64..127
   __host__ __device__ size_t tile_stride() const { return (size_t)tile_bytes(fmt); }
   __host__ __device__ size_t expert_stride() const {

@@ -194,7 +194,8 @@ k_gemv(const GemvParams p) {
   // ---- geometry. gate/up: a task = 16 hidden outputs (lanes 0..15 the gate rows, lanes 16..31
   // the matching up rows), every warp a K slice. down: a task = 64 output rows, warps = 2 row
   // groups x 8 K slices. A warp's share of a task is kpw <= 4 K blocks ("items"). ----
-  const int KB = p.K / kTileK;
+  const int KB = p.img.n_kblocks;        // image K blocks (twice p.K / 64 for a two-plane image of 8-bit codes)
+  const int ash = p.img.act_shift;       // an image K block multiplies the activations of K block (index >> ash)
   constexpr int kSlices = UP ? kGemvWarps : kGemvWarps / 2;
   const int slice = UP ? warp : warp >> 1;
   const int kpw = (KB + kSlices - 1) / kSlices;  // <= kKpw (the host checks K)
@@ -302,7 +303,7 @@ k_gemv(const GemvParams p) {
       for (int s = 0; s < kKpw; s++) {
         if (n0 + s < nseg) {
           if (kb0 + ci < KB) {
-            const uint32_t xa = xs_addr + (uint32_t)(kb0 + ci) * (kTileK * 2);
+            const uint32_t xa = xs_addr + (uint32_t)((kb0 + ci) >> ash) * (kTileK * 2);
             if (FMT == kQ4CP) {
               const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
               acc += half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s].x >> 16)) * d1;
@@ -310,13 +311,13 @@ k_gemv(const GemvParams p) {
               // metadata {fp16 d, fp16 dmin, u8 sc0, u8 m0, u8 sc1, u8 m1}
               const float d0 = chunk_dot(cw[2 * s], lut, xa), d1 = chunk_dot(cw[2 * s + 1], lut, xa + 64);
               const float dd = half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)), dm = half_bits_to_f32((uint16_t)(sw[s].x >> 16));
-              const float x0 = xsum[2 * (kb0 + ci)], x1 = xsum[2 * (kb0 + ci) + 1];
+              const float x0 = xsum[2 * ((kb0 + ci) >> ash)], x1 = xsum[2 * ((kb0 + ci) >> ash) + 1];
               acc += (dd * (float)(sw[s].y & 0xFFu)) * d0 - (dm * (float)((sw[s].y >> 8) & 0xFFu)) * x0;
               acc += (dd * (float)((sw[s].y >> 16) & 0xFFu)) * d1 - (dm * (float)(sw[s].y >> 24)) * x1;
             } else {
               // metadata [2]{fp16 d, fp16 m, u32 fifth bits}
               const float d0 = chunk_dot5(cw[2 * s], sw[s].y, lut, xa), d1 = chunk_dot5(cw[2 * s + 1], sw[s].w, lut, xa + 64);
-              const float x0 = xsum[2 * (kb0 + ci)], x1 = xsum[2 * (kb0 + ci) + 1];
+              const float x0 = xsum[2 * ((kb0 + ci) >> ash)], x1 = xsum[2 * ((kb0 + ci) >> ash) + 1];
               acc += half_bits_to_f32((uint16_t)(sw[s].x & 0xFFFFu)) * d0 + half_bits_to_f32((uint16_t)(sw[s].x >> 16)) * x0;
               acc += half_bits_to_f32((uint16_t)(sw[s].z & 0xFFFFu)) * d1 + half_bits_to_f32((uint16_t)(sw[s].z >> 16)) * x1;
             }

@@ -67,8 +67,10 @@ template <int FMT>
 __device__ __forceinline__ void row_dot(const Image& img, int e, int mt, int r, int k0, int klen,
                                         const float* book, const float (*xs)[kPiece], int nt,
                                         float* acc) {
-  for (int kb = k0 / kTileK; kb < (k0 + klen) / kTileK; kb++) {
-    const uint8_t* tile = img.tile(e, mt, kb);
+  // (a two-plane image of 8-bit codes has 1 << act_shift image K blocks per activation K block)
+  for (int kbi = (k0 / kTileK) << img.act_shift; kbi < ((k0 + klen) / kTileK) << img.act_shift; kbi++) {
+    const int kb = kbi >> img.act_shift;
+    const uint8_t* tile = img.tile(e, mt, kbi);
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const uint4 c4 = *(const uint4*)(tile + h * 2048 + r * 16);

@@ -397,7 +397,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           const uint32_t bar = bars + 8 * (kBarBFull + slot);
           mbar_expect_tx(bar, nk * bytes);
           for (int j = 0; j < nk; j++)
-            tma_load_2d(sbase + M::slot(slot) + j * kBStage, map, (2 * pp + j) * kTileK, t.first, bar);
+            tma_load_2d(sbase + M::slot(slot) + j * kBStage, map, ((2 * pp + j) >> img.act_shift) * kTileK, t.first, bar);
         }
       }
     }

@@ -209,11 +209,12 @@ int gguf_find(const Mapping& m, const std::string& name, View* out) {
   if (!c.ok) return 2;
   if (!found) return 1;
   const uint64_t data0 = (c.pos + alignment - 1) / alignment * alignment;
-  // bytes per row: Q4_K 144 per 256 elements, Q5_1 24 per 32, IQ4_NL 18 per 32, IQ4_XS 136 per 256
+  // bytes per row: Q4_K 144 per 256 elements, Q5_K 176 per 256, Q5_1 24 per 32, Q8_0 34 per 32, IQ4_NL 18 per 32, IQ4_XS 136 per 256
   uint64_t row = 0;
   if (out->dtype == B200MOE_GGML_Q4_K && out->dims[0] % 256 == 0) row = out->dims[0] / 256 * 144;
   else if (out->dtype == B200MOE_GGML_Q5_K && out->dims[0] % 256 == 0) row = out->dims[0] / 256 * 176;
   else if (out->dtype == B200MOE_GGML_Q5_1 && out->dims[0] % 32 == 0) row = out->dims[0] / 32 * 24;
+  else if (out->dtype == B200MOE_GGML_Q8_0 && out->dims[0] % 32 == 0) row = out->dims[0] / 32 * 34;
   else if (out->dtype == B200MOE_GGML_IQ4_NL && out->dims[0] % 32 == 0) row = out->dims[0] / 32 * 18;
   else if (out->dtype == B200MOE_GGML_IQ4_XS && out->dims[0] % 256 == 0) row = out->dims[0] / 256 * 136;
   else return 3;

@@ -1,5 +1,5 @@
 // repack.cu -- one-time conversion of the reference's expert tensor layouts (hgn q4cp,
-// GGUF Q4_K, Q5_K, Q5_1, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
+// GGUF Q4_K, Q5_K, Q5_1, Q8_0, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
 // check: dequantising rows of the image bit-identically to the reference's row
 // dequantisers (q4cp_row, src/hgn.h:249-261; dequant_row, src/gguf.h:360-374, 408-441).
 #include "kernels.h"
@@ -234,11 +234,48 @@ __global__ void k_repack_iq4(Image img, SrcTensor a, SrcTensor b, int K, int fir
   }
 }
 
+// GGUF Q8_0 -> the two-plane kQ51 image (common.cuh): one thread per (image tile, row, half).
+// Image K block 2*kb holds the high nibbles of the biased codes of columns 64*kb .. 64*kb+63,
+// image K block 2*kb+1 the low nibbles (34 bytes per 32 elements: fp16 d, 32 int8; src/gguf.h:352-359).
+__global__ void k_repack_q80(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
+                             const int32_t* __restrict__ emap) {
+  const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 256;
+  const long long row_bytes = (long long)K / 32 * 34;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    int r = (int)(i & 127);
+    int h = (int)((i >> 7) & 1);
+    long long t = i >> 8;
+    int kbi = (int)(t % img.n_kblocks);   // image K block: 2 * (activation K block) + plane
+    long long t2 = t / img.n_kblocks;
+    int mt = (int)(t2 % img.n_mtiles);
+    int e = (int)(t2 / img.n_mtiles);
+    const int kb = kbi >> 1, plane = kbi & 1;  // plane 0: high nibbles, 1: low nibbles
+    uint8_t* dst = const_cast<uint8_t*>(img.tile(e, mt, kbi));
+    const SrcTensor* s;
+    long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
+    const uint8_t* blk = s->codes + row * row_bytes + (long long)(kb * 2 + h) * 34;
+    const int8_t* qs = (const int8_t*)(blk + 2);
+    uint8_t out[16];
+#pragma unroll
+    for (int q = 0; q < 16; q++) {
+      const int u0 = (int)qs[2 * q] + 128, u1 = (int)qs[2 * q + 1] + 128;
+      out[q] = plane ? (uint8_t)((u0 & 15) | ((u1 & 15) << 4)) : (uint8_t)((u0 >> 4) | ((u1 >> 4) << 4));
+    }
+    *(uint4*)(dst + h * 2048 + r * 16) = *(uint4*)out;
+    const float d = half_bits_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    uint8_t* meta = dst + kCodeBytes + r * 16 + h * 8;
+    *(__half*)meta = __float2half_rn(plane ? d : __fmul_rn(d, 16.f));
+    *(__half*)(meta + 2) = __float2half_rn(plane ? 0.f : __fmul_rn(d, -128.f));
+    *(uint32_t*)(meta + 4) = 0u;
+  }
+}
+
 // Rows of an expert, dequantised from the image with the reference's exact operation
 // order (single fp32 multiply for q4cp; multiply then add/subtract, never fused, for GGUF).
 __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int mid_rows,
                                float* out) {
-  const int K = img.n_kblocks * kTileK;
+  const int K = (img.n_kblocks >> img.act_shift) * kTileK;
   const long long total = (long long)nrows * K;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -258,6 +295,17 @@ __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int m
       r = row % 128;
     }
     int kb = c / 64, h = (c / 32) & 1, j = c & 31;
+    if (img.act_shift) {
+      // Q8_0 in two planes: put the code together again and multiply once, as the reference
+      // does (y = d * q, src/gguf.h:352-359)
+      const uint8_t* hi = img.tile(expert, mt, 2 * kb);
+      const uint8_t* lo = img.tile(expert, mt, 2 * kb + 1);
+      const uint8_t bh = hi[h * 2048 + r * 16 + j / 2], bl = lo[h * 2048 + r * 16 + j / 2];
+      const int q = 16 * ((j & 1) ? (bh >> 4) : (bh & 15)) + ((j & 1) ? (bl >> 4) : (bl & 15)) - 128;
+      const float d = half_bits_to_f32(*(const uint16_t*)(lo + kCodeBytes + r * 16 + h * 8));
+      out[i] = __fmul_rn(d, (float)q);
+      continue;
+    }
     const uint8_t* tile = img.tile(expert, mt, kb);
     uint8_t byte = tile[h * 2048 + r * 16 + j / 2];
     int nib = (j & 1) ? (byte >> 4) : (byte & 15);
@@ -296,6 +344,7 @@ cudaError_t launch_repack(const Image& img, const SrcTensor& a, const SrcTensor&
   else if (img.fmt == kQ4CP) k_repack_q4cp<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else if (img.fmt == kQ4K) k_repack_q4k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else if (gguf_type == 13) k_repack_q5k<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
+  else if (gguf_type == 8) k_repack_q80<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   else k_repack_q51<<<blocks, threads, 0, st>>>(img, a, b, K, first_expert, expert_map);
   return cudaGetLastError();
 }

@@ -8,7 +8,7 @@ Stand-ins for real checkpoints, with the shapes and value distributions of the
 benchmark configurations:
   * hgn q4cp tensors (layout: src/hgn.h:5-9 of the reference): 16 x f32 code book, 4-bit
     codes uniform in [0,15], fp16 scales |N(0, 0.02)| per (row, 32 columns);
-  * GGUF Q4_K / Q5_K / Q5_1 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
+  * GGUF Q4_K / Q5_K / Q5_1 / Q8_0 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
     block scales normalised so that dequantised magnitudes match the q4cp case;
   * bf16 activations ~ N(0,1), router logits ~ N(0,1) with an optional per-expert
     Zipf(1.1) bias under a seeded permutation of the expert ids.
@@ -139,13 +139,24 @@ def make_iq4xs(rng, nrows, k, sigma=0.02):
     return blk.reshape(-1)
 
 
-GGML_Q5_1, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 12, 13, 20, 23
-_GG_MAKERS = {GGML_Q5_1: make_q51, GGML_Q4_K: make_q4k, GGML_Q5_K: make_q5k, GGML_IQ4_NL: make_iq4nl, GGML_IQ4_XS: make_iq4xs}
+def make_q80(rng, nrows, k, sigma=0.02):
+    """nrows rows of GGUF Q8_0 blocks (34 bytes per 32 elements: fp16 d, 32 int8 codes; src/gguf.h:352-359).
+    |w| <= a with a = |N(0, sigma)| per block, as for the other formats."""
+    nb = nrows * (k // 32)
+    a = np.abs(rng.normal(0.0, sigma, size=nb))
+    blk = np.zeros((nb, 34), dtype=np.uint8)
+    blk[:, 0:2] = (a / 127.0).astype("<f2").view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(0, 256, size=(nb, 32), dtype=np.uint8)
+    return blk.reshape(-1)
+
+
+GGML_Q5_1, GGML_Q8_0, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 8, 12, 13, 20, 23
+_GG_MAKERS = {GGML_Q8_0: make_q80, GGML_Q5_1: make_q51, GGML_Q4_K: make_q4k, GGML_Q5_K: make_q5k, GGML_IQ4_NL: make_iq4nl, GGML_IQ4_XS: make_iq4xs}
 
 
 def gg_row_bytes(gtype, k):
     """Bytes of one row of k elements in GGUF block type `gtype` (src/gguf.h:49-62)."""
-    per, nbytes = {GGML_Q5_1: (32, 24), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_IQ4_NL: (32, 18), GGML_IQ4_XS: (256, 136)}[gtype]
+    per, nbytes = {GGML_Q8_0: (32, 34), GGML_Q5_1: (32, 24), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_IQ4_NL: (32, 18), GGML_IQ4_XS: (256, 136)}[gtype]
     assert k % per == 0
     return k // per * nbytes
 

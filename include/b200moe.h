@@ -41,7 +41,7 @@ enum {
 };
 
 /* GGUF tensor type ids accepted by b200moe_load_gguf (values of ggml / src/gguf.h:36-41). */
-enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q4_K = 12, B200MOE_GGML_Q5_K = 13, B200MOE_GGML_IQ4_NL = 20, B200MOE_GGML_IQ4_XS = 23 };
+enum { B200MOE_GGML_Q5_1 = 7, B200MOE_GGML_Q8_0 = 8, B200MOE_GGML_Q4_K = 12, B200MOE_GGML_Q5_K = 13, B200MOE_GGML_IQ4_NL = 20, B200MOE_GGML_IQ4_XS = 23 };
 
 /* Which expert GEMM implementation forward uses for T > decode_max_tokens. */
 enum {
@@ -96,9 +96,11 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
 
 /* Replaces: gguf_experts_open / GgExperts (src/gpu/parts/30_host_util.inc:348-452): raw GGUF
  * blocks of blk.L.ffn_{gate,up,down}_exps.weight, expert e's rows at e*rows*row_bytes
- * (src/gguf.h:3-11). type_gu: Q4_K, Q5_K, IQ4_NL or IQ4_XS; type_dn: Q5_1, IQ4_NL or IQ4_XS (the
- * types of moe_gg_up / moe_gg_down and of the table-decoded kernels,
- * src/gpu/parts/27_kernels_moe_lut.inc:4-19, 659-671). The IQ4 types become the q4cp tile image:
+ * (src/gguf.h:3-11). type_gu: Q4_K, Q5_K, Q8_0, IQ4_NL or IQ4_XS; type_dn: Q5_1, Q8_0, IQ4_NL or IQ4_XS
+ * (the types of moe_gg_up / moe_gg_down, src/gpu/parts/26_kernels_moe_gguf.inc:9-20, 93-96, and of the
+ * table-decoded kernels, src/gpu/parts/27_kernels_moe_lut.inc:4-19, 659-671). Q8_0 (the experts of the
+ * MTP sidecar) is stored as two 4-bit planes, high and low nibble of the biased code, with exact
+ * group constants: w = (16 d) * hi - 128 d + d * lo = d * q. The IQ4 types become the q4cp tile image:
  * code book = grid / 256, group scale = fp16(256 * d [* (ls - 32)]), the exact rescale of
  * 27_kernels_moe_lut.inc:312-326; Q5_K becomes the Q5_1 image form (d' = fp16(d*sc),
  * m' = fp16(-dmin*mn) per 32 elements, fifth bits regrouped). */
@@ -148,7 +150,7 @@ int b200moe_get_config(b200moe_handle h, b200moe_config* out);
  *                   and the router weight layers.L.mlp.gate.weight when present (src/ref.cpp:566-633).
  *   load_gguf_file: GGUF v2/v3 (src/gguf.h:1-11, 136-314), sharded or not (pass any shard of
  *                   NAME-0000i-of-0000n.gguf): blk.L.ffn_{gate,up,down}_exps.weight, ne = [K, N, E]
- *                   (src/gpu/parts/30_host_util.inc:384-412), Q4_K gate/up and Q5_1 down.
+ *                   (src/gpu/parts/30_host_util.inc:384-412), any of the block types b200moe_load_gguf reads.
  * B200MOE_ERR_BAD_ARG: file missing, malformed or without the tensors; B200MOE_ERR_UNSUPPORTED:
  * shapes or types that do not match the handle. */
 int b200moe_load_hgn_file(b200moe_handle h, int layer, const char* path, int model_layer);

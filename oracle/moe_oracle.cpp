@@ -12,8 +12,8 @@
 // What each function follows in the reference (paths relative to the reference
 // project root):
 //   orc_q4cp_rows        src/hgn.h:219-261   (q4cp_parse / q4cp_row)
-//   orc_gguf_rows        src/gguf.h:328-336, 360-374, 375-406, 408-441 (scale_min_k4, Q5_1,
-//                        IQ4_NL, IQ4_XS, Q4_K, Q5_K)
+//   orc_gguf_rows        src/gguf.h:328-336, 352-359, 360-374, 375-406, 408-441 (scale_min_k4, Q8_0,
+//                        Q5_1, IQ4_NL, IQ4_XS, Q4_K, Q5_K)
 //   orc_router_topk      src/ref.cpp:574-588 (softmax in double, partial_sort on probs)
 //   orc_route            src/gpu/parts/40_model.inc:4171-4193 (host bucketing) and
 //                        src/gpu/parts/10_ple_io.inc:790-811 (pairids rank rule)
@@ -83,14 +83,15 @@ inline void q4_row(const Q4View& v, uint64_t row, float* out) {
   }
 }
 
-enum { GG_Q5_1 = 7, GG_Q4_K = 12, GG_Q5_K = 13, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
+enum { GG_Q5_1 = 7, GG_Q8_0 = 8, GG_Q4_K = 12, GG_Q5_K = 13, GG_IQ4_NL = 20, GG_IQ4_XS = 23 };
 
-inline bool gg_known(uint32_t t) { return t == GG_Q5_1 || t == GG_Q4_K || t == GG_Q5_K || t == GG_IQ4_NL || t == GG_IQ4_XS; }
+inline bool gg_known(uint32_t t) { return t == GG_Q5_1 || t == GG_Q8_0 || t == GG_Q4_K || t == GG_Q5_K || t == GG_IQ4_NL || t == GG_IQ4_XS; }
 
 inline uint64_t gg_row_bytes(uint32_t type, uint64_t k) {
   if (type == GG_Q4_K) return k / 256 * 144;
   if (type == GG_Q5_K) return k / 256 * 176;
   if (type == GG_Q5_1) return k / 32 * 24;
+  if (type == GG_Q8_0) return k / 32 * 34;
   if (type == GG_IQ4_NL) return k / 32 * 18;
   if (type == GG_IQ4_XS) return k / 256 * 136;
   return 0;
@@ -107,6 +108,15 @@ inline void k4_scale_min(int j, const uint8_t* p, uint8_t& sc, uint8_t& mn) {
 }
 
 inline void gg_row(uint32_t type, const uint8_t* src, float* y, uint64_t k) {
+  if (type == GG_Q8_0) {  // 34 bytes per 32: fp16 d, 32 int8 codes, y = d * q (src/gguf.h:352-359)
+    for (uint64_t b = 0; b < k / 32; b++, src += 34) {
+      uint16_t dh;
+      memcpy(&dh, src, 2);
+      const float d = half_bits_to_float(dh);
+      for (int j = 0; j < 32; j++) y[b * 32 + j] = d * (float)(int8_t)src[2 + j];
+    }
+    return;
+  }
   if (type == GG_Q5_1) {
     for (uint64_t b = 0; b < k / 32; b++, src += 24) {
       uint16_t dh, mh;

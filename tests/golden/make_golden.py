@@ -35,11 +35,13 @@ def layer_crc(layer):
 
 
 def gguf_iq4():
-    """GGUF IQ4_NL / IQ4_XS rows through the reference's dequant_row (src/gguf.h:375-406)."""
+    """GGUF IQ4_NL / IQ4_XS / Q8_0 / Q5_K rows through the reference's dequant_row (src/gguf.h:352-359, 375-441)."""
     nl = synth.make_iq4nl(synth.rng_for(12, 3), 3, 256)
     xs = synth.make_iq4xs(synth.rng_for(12, 4), 3, 512)
     np.savez_compressed(os.path.join(OUT, "gguf_iq4_rows.npz"), iq4nl=nl, iq4nl_rows=oracle.gguf_rows(20, nl, 256, 3, use_ref=True),
                         iq4xs=xs, iq4xs_rows=oracle.gguf_rows(23, xs, 512, 3, use_ref=True))
+    q80 = synth.make_q80(synth.rng_for(12, 6), 3, 256)
+    np.savez_compressed(os.path.join(OUT, "gguf_q80_rows.npz"), q80=q80, q80_rows=oracle.gguf_rows(8, q80, 256, 3, use_ref=True))
     q5k = synth.make_q5k(synth.rng_for(12, 5), 3, 512)
     np.savez_compressed(os.path.join(OUT, "gguf_q5k_rows.npz"), q5k=q5k, q5k_rows=oracle.gguf_rows(13, q5k, 512, 3, use_ref=True))
 

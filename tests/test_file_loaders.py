@@ -194,7 +194,7 @@ def test_hgn_file_with_shared_expert_and_router(cuda, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("sharded,gu,dn", [(False, 12, 7), (True, 12, 7), (False, 20, 23), (True, 23, 20), (False, 13, 7)])
+@pytest.mark.parametrize("sharded,gu,dn", [(False, 12, 7), (True, 12, 7), (False, 20, 23), (True, 23, 20), (False, 13, 7), (True, 8, 8)])
 def test_gguf_file(cuda, tmp_path, sharded, gu, dn):
     torch = cuda
     spec = synth.LayerSpec(experts=8, topk=2, d=512, mid=256, fmt="gguf", gg_gu=gu, gg_dn=dn)

@@ -315,11 +315,33 @@ def test_dequant_q5k(cuda):
         assert np.all(np.abs(got - want).reshape(-1, 256) <= a * 2.0 ** -9)
 
 
-@pytest.mark.parametrize("gu,dn,impl", [(20, 20, pkg.GEMM_AUTO), (23, 23, pkg.GEMM_AUTO), (12, 23, pkg.GEMM_AUTO),
+def test_dequant_q80_bit_exact(cuda):
+    """Q8_0 experts live in the library as two 4-bit planes (high and low nibble of the biased
+    code); put together again they are the reference's rows d * q, bit for bit."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=2, topk=1, d=512, mid=128, fmt="gguf", gg_gu=8, gg_dn=8)
+    layer = synth.make_layer(spec, seed=35)
+    op = make_op(torch, spec, 4, impl=pkg.GEMM_SIMT, layer=layer)
+    for e in range(spec.experts):
+        out = torch.empty((2 * spec.mid, spec.d), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 0, e, 0, 2 * spec.mid, out)
+        rb = synth.gg_row_bytes(8, spec.d)
+        g = oracle.gguf_rows(8, layer["gate"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        u = oracle.gguf_rows(8, layer["up"][e * spec.mid * rb:(e + 1) * spec.mid * rb], spec.d, spec.mid)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(np.concatenate([g, u])))
+        out = torch.empty((spec.d, spec.mid), dtype=torch.float32, device="cuda")
+        op.dequant_rows(0, 1, e, 0, spec.d, out)
+        rb = synth.gg_row_bytes(8, spec.mid)
+        dn = oracle.gguf_rows(8, layer["down"][e * spec.d * rb:(e + 1) * spec.d * rb], spec.mid, spec.d)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(dn))
+
+
+@pytest.mark.parametrize("gu,dn,impl", [(8, 8, pkg.GEMM_AUTO), (12, 8, pkg.GEMM_AUTO), (8, 7, pkg.GEMM_AUTO), (8, 8, pkg.GEMM_SIMT),
+                                        (20, 20, pkg.GEMM_AUTO), (23, 23, pkg.GEMM_AUTO), (12, 23, pkg.GEMM_AUTO),
                                         (20, 7, pkg.GEMM_AUTO), (23, 20, pkg.GEMM_SIMT), (13, 7, pkg.GEMM_AUTO),
                                         (13, 23, pkg.GEMM_AUTO), (13, 7, pkg.GEMM_SIMT)])
 def test_iq4_layer(cuda, gu, dn, impl):
-    """GGUF experts in Q5_K (13), IQ4_NL (20) / IQ4_XS (23), alone and mixed with Q4_K (12) / Q5_1 (7): GEMV
+    """GGUF experts in Q8_0 (8), Q5_K (13), IQ4_NL (20) / IQ4_XS (23), alone and mixed with Q4_K (12) / Q5_1 (7): GEMV
     (T=3), tensor-core (T=40, 300) and fp32 paths against the oracle, which dequantises the raw
     blocks as the reference's dequant_row does."""
     torch = cuda

@@ -150,6 +150,16 @@ def test_empty_and_single_token():
     assert eoff.tolist() == [0] * 9
 
 
+def test_q80_rows_match_reference_golden(golden_dir):
+    """GGUF Q8_0 rows (the MTP sidecar's experts): the restated dequantiser against rows made by
+    the reference's gguf::dequant_row (src/gguf.h:352-359), bit for bit."""
+    g = np.load(os.path.join(golden_dir, "gguf_q80_rows.npz"))
+    src = synth.make_q80(synth.rng_for(12, 6), 3, 256)
+    assert np.array_equal(src, g["q80"]), "generator drifted"
+    got = oracle.gguf_rows(8, src, 256, 3)
+    assert np.array_equal(got.view(np.uint32), g["q80_rows"].view(np.uint32))
+
+
 def test_non_finite_logits_keep_ids_in_range():
     """A NaN logit (or a row of -inf) makes every probability NaN (src/ref.cpp:574-582: the maximum
     skips NaN, exp(NaN) poisons the sum): the selection is then arbitrary but the ids are expert
