@@ -60,6 +60,11 @@ SYMBOLS = {
     "b200moe_ep_experts_part": (_I, [_P, _I, _P, _I, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _P, _P]),
     "b200moe_ep_wait_flags": (_I, [_P, _P, _I, _I, _P]),
+    "b200moe_ep_unique_id": (_I, [_P]),
+    "b200moe_ep_init": (_I, [_P, _P, ctypes.c_double]),
+    "b200moe_ep_forward": (_I, [_P, _I, _P, _I, _P, _P, _P]),
+    "b200moe_ep_shutdown": (_I, [_P]),
+    "b200moe_ep_last_error": (ctypes.c_char_p, [_P]),
     "b200moe_debug_get_routing": (_I, [_P, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_dequant_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_synchronize": (_I, [_P, _P]),
@@ -255,6 +260,23 @@ class MoeOperator:
         """Enqueue a bounded wait until flags[0..n) (int32, written by peer GPUs) reach `expected`."""
         self._check(lib().b200moe_ep_wait_flags(self._h, _ptr(flags), n, expected, _stream(stream)))
 
+    # -- expert parallelism with the host inside the library (NCCL, no torch.distributed) --------
+    def ep_init(self, unique_id, cap_factor=2.0):
+        """Collective over the ranks: communicator from the 128-byte id (ep_unique_id() on rank 0,
+        carried to the others by the caller), row buffers allocated and attached."""
+        buf = (ctypes.c_char * 128).from_buffer_copy(bytes(unique_id))
+        self._check(lib().b200moe_ep_init(self._h, ctypes.addressof(buf), float(cap_factor)))
+
+    def ep_forward(self, layer, x, logits, out, T=None, stream=None):
+        T = x.shape[0] if T is None else T
+        st = lib().b200moe_ep_forward(self._h, layer, _ptr(x), T, _ptr(logits), _ptr(out), _stream(stream))
+        if st != 0:
+            detail = (lib().b200moe_ep_last_error(self._h) or b"").decode() or (lib().b200moe_last_error(self._h) or b"").decode()
+            raise B200MoeError(st, detail)
+
+    def ep_shutdown(self):
+        self._check(lib().b200moe_ep_shutdown(self._h))
+
     def synchronize(self, stream=None):
         """Wait for the stream and raise if a device-side wait gave up."""
         self._check(lib().b200moe_synchronize(self._h, _stream(stream)))
@@ -299,6 +321,15 @@ def _nbytes(obj):
     if hasattr(obj, "numel"):
         return int(obj.numel() * obj.element_size())
     raise TypeError("cannot size %r" % type(obj))
+
+
+def ep_unique_id():
+    """The 128-byte NCCL id of a new expert-parallel group (make it on one rank, hand it to the rest)."""
+    buf = (ctypes.c_char * 128)()
+    st = lib().b200moe_ep_unique_id(ctypes.addressof(buf))
+    if st != 0:
+        raise B200MoeError(st, "b200moe_ep_unique_id")
+    return bytes(buf)
 
 
 def version():

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["api.cu", "repack.cu", "route.cu", "expert_simt.cu", "expert_gemv.cu", "expert_tc.cu", "combine.cu", "route_static.cu", "router_gemm.cu", "files.cu", "decode.cu"]
+SOURCES = ["api.cu", "repack.cu", "route.cu", "expert_simt.cu", "expert_gemv.cu", "expert_tc.cu", "combine.cu", "route_static.cu", "router_gemm.cu", "files.cu", "decode.cu", "ep_host.cu"]
 HEADERS = ["common.cuh", "kernels.h", "tc.h", "route_small.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
@@ -48,7 +48,7 @@ def build(force=False, verbose=False):
         if verbose:
             print(out)
         objs.append(obj)
-    cmd = [NVCC, "-shared", "-o", LIB, "-ccbin", "/usr/bin/g++"] + objs + ["-lcudart"]
+    cmd = [NVCC, "-shared", "-o", LIB, "-ccbin", "/usr/bin/g++"] + objs + ["-lcudart", "-ldl"]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout)

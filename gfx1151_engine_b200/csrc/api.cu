@@ -311,6 +311,7 @@ int b200moe_destroy(b200moe_handle h) {
   if (!h) return B200MOE_ERR_BAD_ARG;
   cudaSetDevice(h->cfg.device);
   cudaDeviceSynchronize();
+  b200moe_ep_shutdown(h);  // the library-side expert-parallel host, if one was set up on this handle
   if (h->dec_trace) {
     // debug aid: per-block phase time stamps (ns) of the last fused decode launch, raw uint64 [1024][8]
     std::vector<unsigned long long> host((size_t)1024 * 8);

@@ -35,7 +35,7 @@ enum {
   B200MOE_ERR_CUDA = 3,         /* a CUDA runtime or driver call failed */
   B200MOE_ERR_NOT_LOADED = 4,   /* forward before the layer's weights were loaded */
   B200MOE_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up */
-  B200MOE_ERR_NCCL = 6,
+  B200MOE_ERR_NCCL = 6,         /* libnccl missing, or an NCCL call of b200moe_ep_init / b200moe_ep_forward failed */
   B200MOE_ERR_ALLOC = 7,
   B200MOE_ERR_TOO_LARGE = 8     /* request exceeds a fixed capacity: b200moe_route_static's scratch, or the router's near-tie list */
 };
@@ -252,6 +252,26 @@ int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream
  * reached `expected`. The wait is bounded (2 s): a timeout is reported by b200moe_synchronize as
  * B200MOE_ERR_DEVICE_TIMEOUT and the stream continues. */
 int b200moe_ep_wait_flags(b200moe_handle h, const int32_t* flags_dev, int n, int32_t expected, void* stream);
+
+/* The host side of expert parallelism inside the library, for hosts written in C / C++ (no
+ * counterpart in the reference): the exchanges are NCCL point-to-point groups, NCCL is loaded at run
+ * time (libnccl.so.2; B200MOE_ERR_NCCL when it is missing or a call fails).
+ *   ep_unique_id: rank 0 makes the 128-byte NCCL id; the host carries it to the other ranks.
+ *   ep_init:      collective over the ep_size ranks (handles created with ep_rank / ep_size): builds
+ *                 the communicator, allocates the four row buffers (receive side cap_factor x
+ *                 max_tokens*topk rows, >= 1.0; 2.0 is ample with a balanced placement) and attaches them.
+ *   ep_forward:   one layer call of this rank's T tokens: route, all-gather of the offset tables,
+ *                 own rows in place, dispatch, other ranks' rows, return, combine -- all on `stream`,
+ *                 with one host wait for the tables. Every rank must call it (with its own T).
+ *                 B200MOE_ERR_TOO_LARGE on EVERY rank when some rank's receive buffer would overflow
+ *                 (nothing has been exchanged then); B200MOE_ERR_NCCL with b200moe_ep_last_error.
+ *   ep_shutdown:  frees the communicator and the buffers (b200moe_destroy does it too). */
+int b200moe_ep_unique_id(void* id128);
+int b200moe_ep_init(b200moe_handle h, const void* id128, double cap_factor);
+int b200moe_ep_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int T, const float* logits_dev,
+                       void* out_bf16_dev, void* stream);
+int b200moe_ep_shutdown(b200moe_handle h);
+const char* b200moe_ep_last_error(b200moe_handle h);
 
 /* Reads back what the last forward / route call left in the workspace (host buffers; any may
  * be NULL): tokidx[T*k], pw[T*k], eoff[E+1], pairids[T*k] as defined by
