@@ -252,6 +252,40 @@ def test_row_invariance_tensor_core_path(cuda):
     op.close()
 
 
+def test_fp16_range_is_handled_alike_on_both_paths(cuda):
+    """The SwiGLU product is stored as fp16 between the two GEMMs on the GEMV path (T <= 16) and
+    on the tensor-core path (T > 16) alike. Weights and activations scaled so that many products
+    leave the fp16 range: both paths store the largest fp16 number (no infinity), so a token's
+    output is finite and the same on both paths (1e-2 of the output's scale: the paths round
+    differently), while the fp32 oracle, which has no fp16 intermediate, differs visibly -- the
+    proof that the case does saturate. A NaN activation row stays NaN on the tensor-core path
+    (it is not clamped to a finite number) and leaves the other rows' bytes untouched."""
+    torch = cuda
+    spec = synth.LayerSpec(experts=8, topk=2, d=256, mid=128)
+    layer = {"gate_up": synth.make_q4cp(synth.rng_for(81, 1), spec.experts * 2 * spec.mid, spec.d, scale_sigma=2.0),
+             "down": synth.make_q4cp(synth.rng_for(81, 2), spec.experts * spec.d, spec.mid, scale_sigma=0.002)}
+    T = 40
+    logits = synth.make_logits(synth.rng_for(81, 3), T, spec.experts)
+    x = synth.rng_for(81, 9).normal(0.0, 16.0, size=(T, spec.d)).astype(np.float32)
+    xb = synth.f32_to_bf16_bits(x)
+    op = make_op(torch, spec, T, layer=layer)
+    y_tc = run_layer(torch, op, spec, xb, logits)
+    y_gv = run_layer(torch, op, spec, xb[:4], logits[:4])
+    assert np.isfinite(y_tc).all() and np.isfinite(y_gv).all()
+    scale = np.abs(y_tc[:4]).max()
+    assert np.abs(y_tc[:4] - y_gv).max() <= 1e-2 * scale
+    y_o, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb[:4]), logits=logits[:4])
+    assert np.abs(y_o - y_gv).max() > 5e-2 * scale, "the case does not leave the fp16 range; scale it up"
+    # NaN activations on the tensor-core path
+    xn = xb.copy()
+    xn[3, :] = 0x7FC0
+    y_n = run_layer(torch, op, spec, xn, logits)
+    assert np.isnan(y_n[3]).all()
+    keep = np.arange(T) != 3
+    assert np.array_equal(bits(y_n[keep]), bits(y_tc[keep]))
+    op.close()
+
+
 # ---------------------------------------------------------------- non-finite logits, ids out of range
 @pytest.mark.parametrize("T", [3, 40])
 def test_non_finite_logits_give_valid_ids_and_nan_rows(cuda, T):
