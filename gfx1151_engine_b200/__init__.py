@@ -36,6 +36,7 @@ SYMBOLS = {
     "b200moe_status_string": (ctypes.c_char_p, [_I]),
     "b200moe_last_error": (ctypes.c_char_p, [_P]),
     "b200moe_load_q4cp": (_I, [_P, _I, _P, _SZ, _P, _SZ]),
+    "b200moe_load_i4r": (_I, [_P, _I, _P, _SZ, _P, _SZ, _P, _P, _P, _P]),
     "b200moe_load_gguf": (_I, [_P, _I, _P, _P, _P, _I, _I]),
     "b200moe_load_shared_q4cp": (_I, [_P, _I, _P, _P, _P, _P]),
     "b200moe_forward": (_I, [_P, _I, _P, _I, _P, _P, _P]),
@@ -161,6 +162,12 @@ class MoeOperator:
     def load_q4cp(self, layer, gate_up, down):
         self._check(lib().b200moe_load_q4cp(self._h, layer, _ptr(gate_up), _nbytes(gate_up),
                                             _ptr(down), _nbytes(down)))
+
+    def load_i4r(self, layer, gate_up, down, gu_suh, gu_svh, dn_suh, dn_svh):
+        """hgn v2 i4r experts (dtype 23 blobs) with their four fp16 sign-scale planes
+        (moe_b_v2, src/gpu/parts/40_model.inc:4559-4680 of the reference)."""
+        self._check(lib().b200moe_load_i4r(self._h, layer, _ptr(gate_up), _nbytes(gate_up), _ptr(down), _nbytes(down),
+                                           _ptr(gu_suh), _ptr(gu_svh), _ptr(dn_suh), _ptr(dn_svh)))
 
     def load_gguf(self, layer, gate, up, down, type_gu=GGML_Q4_K, type_dn=GGML_Q5_1):
         self._check(lib().b200moe_load_gguf(self._h, layer, _ptr(gate), _ptr(up), _ptr(down),

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["api.cu", "repack.cu", "route.cu", "expert_simt.cu", "expert_gemv.cu", "expert_tc.cu", "combine.cu", "route_static.cu", "router_gemm.cu", "files.cu", "decode.cu", "ep_host.cu"]
+SOURCES = ["api.cu", "repack.cu", "route.cu", "expert_simt.cu", "expert_gemv.cu", "expert_tc.cu", "combine.cu", "route_static.cu", "router_gemm.cu", "files.cu", "decode.cu", "ep_host.cu", "rotate.cu"]
 HEADERS = ["common.cuh", "kernels.h", "tc.h", "route_small.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [

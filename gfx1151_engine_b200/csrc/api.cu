@@ -25,6 +25,10 @@ struct LayerWeights {
   uint16_t* router_w = nullptr;  // bf16 [E][d], null until b200moe_load_router
   bool loaded = false, shared_loaded = false;
   bool borrowed = false;  // images belong to another handle
+  // hgn v2 i4r: the images hold rotated weights (gu is a plain, unpaired image of 2*mid rows);
+  // rot = one allocation [d + 2*mid + mid + d] f32: gu_suh, gu_svh, dn_suh, dn_svh
+  bool i4r = false;
+  float* rot = nullptr;
 };
 
 }  // namespace
@@ -39,6 +43,7 @@ struct b200moe_ctx {
   void* hid = nullptr;      // [rows][mid] fp32 (GEMV path) or fp16 (tensor-core path)
   void* pairs = nullptr;    // [rows][d]   fp32 or fp16
   __half* x_sorted = nullptr;
+  __half* x_rot = nullptr;  // [max_tokens][d] fp16: rotated activations of hgn v2 i4r layers (allocated by the first such load)
   int dec_rows = 0;
   RouterPlan* rplan = nullptr;     // router logits from hidden states
   const float* hc_w4 = nullptr;    // set for the duration of b200moe_forward_hc: the combine
@@ -329,6 +334,7 @@ int b200moe_destroy(b200moe_handle h) {
     free_image(L.sh_dn);
     if (L.sh_gate_w) cudaFree(L.sh_gate_w);
     if (L.router_w) cudaFree(L.router_w);
+    if (L.rot) cudaFree(L.rot);
   }
   free_all(h->allocs);
   if (h->place_dev && !h->place_borrowed) cudaFree(h->place_dev);
@@ -370,6 +376,7 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
   free_image(L.gu);
   free_image(L.dn);
   L.loaded = false;
+  L.i4r = false;
   std::vector<void*> tmp;
   const uint8_t *gu = nullptr, *dn = nullptr;
   const int nl = local_experts(c), e0 = first_expert(c);
@@ -400,6 +407,93 @@ int b200moe_load_q4cp(b200moe_handle h, int layer, const void* gate_up_src, size
     return fail(h, e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA,
                 std::string("load_q4cp: ") + cudaGetErrorString(e));
   }
+  L.loaded = true;
+  return B200MOE_OK;
+}
+
+int b200moe_load_i4r(b200moe_handle h, int layer, const void* gate_up_src, size_t gate_up_bytes,
+                     const void* down_src, size_t down_bytes, const void* gu_suh_f16, const void* gu_svh_f16,
+                     const void* dn_suh_f16, const void* dn_svh_f16) {
+  if (int s = check_layer(h, layer)) return s;
+  if (!gate_up_src || !down_src || !gu_suh_f16 || !gu_svh_f16 || !dn_suh_f16 || !dn_svh_f16)
+    return fail(h, B200MOE_ERR_BAD_ARG, "load_i4r: null pointer");
+  const b200moe_config& c = h->cfg;
+  const size_t E = c.experts, d = c.d_model, mid = c.d_mid;
+  if (d % 128 || mid % 128 || 2 * mid > d)
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "load_i4r: needs d % 128 == 0, mid % 128 == 0 and 2*mid <= d");
+  if (c.has_shared || c.ep_size > 1 || c.gemm_impl == B200MOE_GEMM_SIMT || !h->tc)
+    return fail(h, B200MOE_ERR_UNSUPPORTED,
+                "load_i4r: not with a shared expert, expert parallelism or the fp32 kernels");
+  auto i4r_bytes = [](size_t rows, size_t cols) { return rows * cols / 2 + rows * (cols / 128) * 2; };
+  if (gate_up_bytes != i4r_bytes(E * 2 * mid, d) || down_bytes != i4r_bytes(E * d, mid))
+    return fail(h, B200MOE_ERR_BAD_ARG, "i4r blob size does not match [E*2*mid,d] / [E*d,mid]");
+  if (((uintptr_t)gate_up_src | (uintptr_t)down_src) & 15)
+    return fail(h, B200MOE_ERR_BAD_ARG, "i4r blobs must be 16-byte aligned");
+  CU_TRY(h, cudaSetDevice(c.device));
+  LayerWeights& L = h->layers[layer];
+  free_image(L.gu);
+  free_image(L.dn);
+  if (L.rot) cudaFree(L.rot);
+  L.rot = nullptr;
+  L.loaded = false;
+  L.i4r = false;
+  std::vector<void*> tmp;
+  cudaError_t e = cudaSuccess;
+  if (!h->x_rot) e = dev_alloc(h, &h->x_rot, (size_t)c.max_tokens * d);
+  static const float kBook[32] = {-8, -7, -6, -5, -4, -3, -2, -1, 0, 1, 2, 3, 4, 5, 6, 7,
+                                  -8, -7, -6, -5, -4, -3, -2, -1, 0, 1, 2, 3, 4, 5, 6, 7};
+  const uint8_t* src = nullptr;
+  // gate_up: a plain image of 2*mid rows per expert (the rotation mixes 128 consecutive output
+  // rows, so gate row r and up row r cannot share a tile the way the q4cp image pairs them)
+  if (e == cudaSuccess) e = stage(gate_up_src, gate_up_bytes, &src, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.gu, kQ4CP, (int)E, (int)(2 * mid), (int)d, 0);
+  if (e == cudaSuccess) {
+    SrcTensor a;
+    a.codes = src;
+    a.scales = src + E * 2 * mid * d / 2;
+    a.rows_per_expert = (long long)(2 * mid);
+    a.scale_stride = (long long)(d / 128 * 2);
+    a.scale_group = 128;
+    e = launch_repack(L.gu, a, a, (int)d, 0, 0, nullptr);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(L.gu.book, kBook, sizeof kBook, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e == cudaSuccess) e = stage(down_src, down_bytes, &src, tmp);
+  if (e == cudaSuccess) e = alloc_image(L.dn, kQ4CP, (int)E, (int)d, (int)mid, 0);
+  if (e == cudaSuccess) {
+    SrcTensor a;
+    a.codes = src;
+    a.scales = src + E * d * mid / 2;
+    a.rows_per_expert = (long long)d;
+    a.scale_stride = (long long)(mid / 128 * 2);
+    a.scale_group = 128;
+    e = launch_repack(L.dn, a, a, (int)mid, 0, 0, nullptr);
+    h->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(L.dn.book, kBook, sizeof kBook, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  // the four sign-scale planes, fp16 -> f32 as the reference uploads them (30_host_util.inc:824-838)
+  if (e == cudaSuccess) e = cudaMalloc((void**)&L.rot, (2 * d + 3 * mid) * sizeof(float));
+  const void* planes[4] = {gu_suh_f16, gu_svh_f16, dn_suh_f16, dn_svh_f16};
+  const size_t lens[4] = {d, 2 * mid, mid, d};
+  size_t off = 0;
+  for (int i = 0; i < 4 && e == cudaSuccess; i++) {
+    e = stage(planes[i], lens[i] * 2, &src, tmp);
+    if (e == cudaSuccess) e = launch_f16_to_f32(src, L.rot + off, (int)lens[i], 0);
+    h->launches++;
+    off += lens[i];
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  free_all(tmp);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(h, e == cudaErrorMemoryAllocation ? B200MOE_ERR_ALLOC : B200MOE_ERR_CUDA,
+                std::string("load_i4r: ") + cudaGetErrorString(e));
+  }
+  L.i4r = true;
   L.loaded = true;
   return B200MOE_OK;
 }
@@ -449,6 +543,7 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
   free_image(L.gu);
   free_image(L.dn);
   L.loaded = false;
+  L.i4r = false;
   const size_t gu_bytes = E * mid * rb_gu, dn_bytes = E * d * rb_dn;
   std::vector<void*> tmp;
   const uint8_t *g = nullptr, *u = nullptr, *dn = nullptr;
@@ -592,7 +687,9 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   // stay the default.
   static const bool fused_env = getenv("B200MOE_FUSED_DECODE") != nullptr && atoi(getenv("B200MOE_FUSED_DECODE")) != 0;
   const bool fused = fused_env || c.decode_impl == B200MOE_DECODE_FUSED;
-  if (fused && c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max && T <= decode_max_tokens() &&
+  if (L.i4r && (c.gemm_impl == B200MOE_GEMM_SIMT || !h->tc || !h->x_rot))
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "forward: hgn v2 i4r layers run on the tensor-core path only");
+  if (fused && !L.i4r && c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max && T <= decode_max_tokens() &&
       ((uintptr_t)x & 15) == 0 && (size_t)T * (k + (shared ? 1 : 0)) <= (size_t)h->dec_rows &&
       decode_supported(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, T, k, E, d, mid)) {
     CU_TRY(h, launch_decode(L.gu, L.dn, shared ? &L.sh_gu : nullptr, shared ? &L.sh_dn : nullptr, logits, ids, w, stride, x,
@@ -631,8 +728,8 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   }
   if (ev) CU_TRY(h, cudaEventRecord(ev[1], st));
   const int pairs = T * k;
-  const bool simt = c.gemm_impl == B200MOE_GEMM_SIMT ||
-                    (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max);
+  const bool simt = !L.i4r && (c.gemm_impl == B200MOE_GEMM_SIMT ||
+                                (c.gemm_impl == B200MOE_GEMM_AUTO && T <= h->decode_max));
   if (simt && c.gemm_impl != B200MOE_GEMM_SIMT && T > h->decode_max)
     return fail(h, B200MOE_ERR_BAD_ARG, "forward: T exceeds the GEMV path's workspace");
   // (the shared expert's images are q4cp: it can ride along only with q4cp routed experts)
@@ -680,6 +777,30 @@ static int forward_impl(b200moe_handle h, int layer, const void* x, int T, const
   } else {
     if (!h->tc) return fail(h, B200MOE_ERR_UNSUPPORTED, "tensor-core path not available on this handle");
     const int rows = pairs + (shared ? T : 0);
+    if (L.i4r) {
+      // hgn v2 i4r (rotate.cu): rotate the tokens once, gather the rotated rows, plain GEMM into
+      // the pair buffer (2*mid <= d columns of it), then the Hadamard / SwiGLU / Hadamard step
+      CU_TRY(h, launch_rot_in(x, L.rot, T, d, h->x_rot, st));
+      CU_TRY(h, launch_gather_f16(h->x_rot, h->rb.tokidx, rows, d, h->x_sorted, st, true));
+      n += 2;
+      if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
+      CU_TRY(h, launch_raw_tc(h->tc, L.gu, h->rb.tiles, h->rb.n_tiles, h->max_tiles, (__half*)h->pairs, h->status_dev, st));
+      CU_TRY(h, launch_i4r_mid((const __half*)h->pairs, L.rot + d, L.rot + d + 2 * mid, rows, mid, (__half*)h->hid, st));
+      n += 2;
+      if (ev) CU_TRY(h, cudaEventRecord(ev[3], st));
+      CU_TRY(h, launch_down_tc(h->tc, L.dn, h->rb.tiles, h->rb.n_tiles, h->max_tiles, (__half*)h->pairs, h->status_dev, st));
+      if (ev) CU_TRY(h, cudaEventRecord(ev[4], st));
+      CU_TRY(h, launch_combine_f16_rot((const __half*)h->pairs, h->rb.pw, h->rb.pairids, T, k, d, L.rot + d + 3 * mid, out, st,
+                                       h->hc_w4, h->hc_state));
+      n += 2;
+      if (ev) {
+        CU_TRY(h, cudaEventRecord(ev[5], st));
+        h->prof_head = (h->prof_head + 1) % kProfRing;
+        if (h->prof_pending < kProfRing) h->prof_pending++;
+      }
+      h->launches += n;
+      return B200MOE_OK;
+    }
     CU_TRY(h, launch_gather_f16(x, h->rb.tokidx, rows, d, h->x_sorted, st));
     n++;
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], st));
@@ -986,9 +1107,12 @@ int b200moe_share_weights(b200moe_handle h, b200moe_handle owner) {
       free_image(L.sh_dn);
       if (L.sh_gate_w) cudaFree(L.sh_gate_w);
       if (L.router_w) cudaFree(L.router_w);
+      if (L.rot) cudaFree(L.rot);
     }
     L = owner->layers[i];
     L.borrowed = true;
+    if (L.i4r && !h->x_rot)
+      CU_TRY(h, dev_alloc(h, &h->x_rot, (size_t)h->cfg.max_tokens * h->cfg.d_model));
   }
   if (h->place_dev && !h->place_borrowed) cudaFree(h->place_dev);
   if (h->source_of_placed_dev && !h->place_borrowed) cudaFree(h->source_of_placed_dev);
@@ -1133,7 +1257,7 @@ int b200moe_dequant_rows(b200moe_handle h, int layer, int which, int expert, int
   if (sh ? !L.shared_loaded : !L.loaded) return fail(h, B200MOE_ERR_NOT_LOADED, "dequant_rows: not loaded");
   const Image& img = which == 0 ? L.gu : which == 1 ? L.dn : which == 2 ? L.sh_gu : L.sh_dn;
   const int e_local = sh ? expert : expert - first_expert(h->cfg);
-  const int rows_per = img.paired ? 2 * h->cfg.d_mid : h->cfg.d_model;
+  const int rows_per = img.paired ? 2 * h->cfg.d_mid : img.n_mtiles * kTileM;
   if (e_local < 0 || e_local >= img.n_experts || row0 + nrows > rows_per)
     return fail(h, B200MOE_ERR_BAD_ARG, "dequant_rows: expert or rows out of range");
   if (nrows == 0) return B200MOE_OK;

@@ -47,11 +47,17 @@ __device__ __forceinline__ uint32_t hc_add2(uint32_t r, float inj, float a, floa
 }
 
 // One block per (token, 2048-column slice); each thread owns 8 consecutive columns.
-template <typename TP>
+// ROT (hgn v2 i4r experts, rotate.cu): the weighted sum is still in the rotated domain; 16
+// neighbouring threads hold one 128-column block of it and turn it into rot_post * H128(sum) /
+// sqrt(128) (natural-order Hadamard: three butterfly levels inside the thread, four by lane
+// shuffles) before the result is stored or written back -- k_v2_reduce_rot of the reference
+// (src/gpu/parts/28_kernels_hgn_v2.inc:145-152). d is a multiple of 128, so a half-warp is in
+// range or out of range as a whole; the loop runs warp-uniformly so that the shuffles are legal.
+template <typename TP, bool ROT = false>
 __global__ void __launch_bounds__(256)
 k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
           const int32_t* __restrict__ pairids, int k, int d, int shared_row0,
-          __nv_bfloat16* __restrict__ out, HcWriteBack hc) {
+          __nv_bfloat16* __restrict__ out, HcWriteBack hc, const float* __restrict__ rot_post = nullptr) {
   const int t = blockIdx.x;
   __shared__ int s_row[kMaxTopK + 1];
   __shared__ float s_w[kMaxTopK + 1];
@@ -70,15 +76,42 @@ k_combine(const TP* __restrict__ pairs, const float* __restrict__ pw,
     n = k + 1;
   }
   __syncthreads();
-  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < d; c += gridDim.y * blockDim.x * 8) {
+  const int lane8 = (threadIdx.x & 31) * 8;
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c - (ROT ? lane8 : 0) < d; c += gridDim.y * blockDim.x * 8) {
+    const bool live = !ROT || c < d;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int s = 0; s < n; s++) {
-      if (s_row[s] < 0) continue;
+      if (s_row[s] < 0 || !live) continue;
       float v[8];
       load8(pairs + (size_t)s_row[s] * d + c, v);
       const float w = s_w[s];
 #pragma unroll
       for (int i = 0; i < 8; i++) acc[i] = fmaf(w, v[i], acc[i]);
+    }
+    if (ROT) {
+#pragma unroll
+      for (int b = 1; b < 8; b <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          if (!(i & b)) {
+            const float p = acc[i], q = acc[i | b];
+            acc[i] = p + q;
+            acc[i | b] = p - q;
+          }
+#pragma unroll
+      for (int bit = 1; bit < 16; bit <<= 1) {
+        const bool upper = (threadIdx.x & bit) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float o = __shfl_xor_sync(0xffffffffu, acc[i], bit);
+          acc[i] = upper ? o - acc[i] : acc[i] + o;
+        }
+      }
+      if (!live) continue;
+      float post[8];
+      load8(rot_post + c, post);
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[i] = acc[i] * 0.08838834764831845f * post[i];
     }
     if (hc.w4) {
 #pragma unroll
@@ -159,6 +192,19 @@ __device__ __forceinline__ float clamp_f16_range(float v) {
   return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f);
 }
 
+// plain row gather of fp16 rows (the source is already fp16: rotated activations of hgn v2 i4r layers)
+__global__ void __launch_bounds__(256)
+k_gather_rows16(const uint4* __restrict__ x, const int32_t* __restrict__ tokidx, int rows, int per_row,
+                uint4* __restrict__ xs) {
+  const int lane = threadIdx.x & 31;
+  const int n_warps = gridDim.x * (blockDim.x >> 5);
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += n_warps) {
+    const uint4* src = x + (size_t)tokidx[row] * per_row;
+    uint4* dst = xs + (size_t)row * per_row;
+    for (int v = lane; v < per_row; v += 32) dst[v] = src[v];
+  }
+}
+
 // x_sorted[row][:] = fp16(x[tokidx[row]][:]); bf16 -> fp16 is exact for 2^-14 <= |v| < 65520,
 // larger magnitudes (infinities included) saturate to the largest finite half, NaN stays NaN.
 // One warp per row: the token index is read once, a lane keeps four 16-byte loads in flight.
@@ -215,8 +261,17 @@ cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32
   return cudaGetLastError();
 }
 
+cudaError_t launch_combine_f16_rot(const __half* pairs, const float* pw, const int32_t* pairids, int T,
+                                   int k, int d, const float* rot_post, void* out_bf16, cudaStream_t st,
+                                   const float* hc_w4, void* hc_state) {
+  if (d % 128 != 0 || !rot_post) return cudaErrorInvalidValue;
+  k_combine<__half, true><<<dim3(T, (d + 2047) / 2048), 256, 0, st>>>(pairs, pw, pairids, k, d, -1, (__nv_bfloat16*)out_bf16,
+                                                                      HcWriteBack{hc_w4, (uint16_t*)hc_state}, rot_post);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
-                              __half* x_sorted, cudaStream_t st) {
+                              __half* x_sorted, cudaStream_t st, bool src_f16) {
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -226,7 +281,8 @@ cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int row
   int blocks = (rows + 7) / 8;
   if (blocks > sms * 8) blocks = sms * 8;
   if (blocks < 1) blocks = 1;
-  k_gather_f16<<<blocks, 256, 0, st>>>((const uint16_t*)x_bf16, tokidx, rows, d, x_sorted);
+  if (src_f16) k_gather_rows16<<<blocks, 256, 0, st>>>((const uint4*)x_bf16, tokidx, rows, d / 8, (uint4*)x_sorted);
+  else k_gather_f16<<<blocks, 256, 0, st>>>((const uint16_t*)x_bf16, tokidx, rows, d, x_sorted);
   return cudaGetLastError();
 }
 

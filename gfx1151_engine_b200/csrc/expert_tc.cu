@@ -800,4 +800,10 @@ cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, co
                        img.n_mtiles * 128, status, st);
 }
 
+cudaError_t launch_raw_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
+                          int max_tiles, __half* z16, int32_t* status, cudaStream_t st) {
+  if (img.fmt != kQ4CP || img.paired) return cudaErrorNotSupported;
+  return launch<false, false, kQ4CP>(plan, plan->x, img, tiles, n_tiles, max_tiles, z16, img.n_mtiles * 128, status, st);
+}
+
 }  // namespace b200moe

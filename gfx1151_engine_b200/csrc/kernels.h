@@ -45,6 +45,7 @@ struct SrcTensor {
   long long rows_per_expert = 0;
   long long row_off = 0;            // first row of this half inside an expert
   long long scale_stride = 0;       // q4cp: bytes per scale record
+  int scale_group = 32;             // columns per fp16 scale: 32 (q4cp) or 128 (hgn v2 i4r)
 };
 
 // ---- repack.cu ----
@@ -166,7 +167,19 @@ cudaError_t launch_combine_f32(const float* pairs, const float* pw, const int32_
 cudaError_t launch_combine_f16(const __half* pairs, const float* pw, const int32_t* pairids, int T,
                                int k, int d, int shared_row0, void* out_bf16, cudaStream_t st,
                                const float* hc_w4 = nullptr, void* hc_state = nullptr);
+// rot_post non-null (fp16 pairs only): out[t] = rot_post * Hn(sum), the output rotation of hgn v2 i4r
+// experts (rotate.cu), applied per 128-column block before the result is stored or written back.
+cudaError_t launch_combine_f16_rot(const __half* pairs, const float* pw, const int32_t* pairids, int T,
+                                   int k, int d, const float* rot_post, void* out_bf16, cudaStream_t st,
+                                   const float* hc_w4 = nullptr, void* hc_state = nullptr);
+// src_f16: the source rows are fp16 already (rotated activations) instead of bf16
 cudaError_t launch_gather_f16(const void* x_bf16, const int32_t* tokidx, int rows, int d,
-                              __half* x_sorted, cudaStream_t st);
+                              __half* x_sorted, cudaStream_t st, bool src_f16 = false);
+
+// ---- rotate.cu (hgn v2 i4r: Hadamard steps around the two GEMMs) ----
+cudaError_t launch_rot_in(const void* x_bf16, const float* pre, int T, int d, __half* xr, cudaStream_t st);
+cudaError_t launch_i4r_mid(const __half* z, const float* svh_gu, const float* suh_dn, int rows, int mid, __half* hr,
+                           cudaStream_t st);
+cudaError_t launch_f16_to_f32(const void* src_f16_dev, float* dst, int n, cudaStream_t st);
 
 }  // namespace b200moe

@@ -1,4 +1,4 @@
-// repack.cu -- one-time conversion of the reference's expert tensor layouts (hgn q4cp,
+// repack.cu -- one-time conversion of the reference's expert tensor layouts (hgn q4cp, hgn v2 i4r,
 // GGUF Q4_K, Q5_K, Q5_1, Q8_0, IQ4_NL, IQ4_XS) into the tiled image described in common.cuh, and the inverse
 // check: dequantising rows of the image bit-identically to the reference's row
 // dequantisers (q4cp_row, src/hgn.h:249-261; dequant_row, src/gguf.h:360-374, 408-441).
@@ -44,8 +44,14 @@ __global__ void k_repack_q4cp(Image img, SrcTensor a, SrcTensor b, int K, int fi
     } else {
       int r = j - 256;
       long long row = src_row(img, a, b, emap ? emap[e + first_expert] : e + first_expert, mt, r, &s);
-      const uint32_t* src = (const uint32_t*)(s->scales + row * s->scale_stride + kb * 4);
-      *(uint32_t*)(dst + kCodeBytes + r * 4) = *src;
+      if (s->scale_group == 128) {
+        // hgn v2 i4r: one fp16 scale per 128 columns serves both 32-groups of two K blocks
+        const uint32_t v = *(const uint16_t*)(s->scales + row * s->scale_stride + (kb >> 1) * 2);
+        *(uint32_t*)(dst + kCodeBytes + r * 4) = v | (v << 16);
+      } else {
+        const uint32_t* src = (const uint32_t*)(s->scales + row * s->scale_stride + kb * 4);
+        *(uint32_t*)(dst + kCodeBytes + r * 4) = *src;
+      }
     }
   }
 }

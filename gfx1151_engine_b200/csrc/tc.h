@@ -24,4 +24,9 @@ cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, cons
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                            int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st);
 
+// plain GEMM over the expert-sorted activations (no activation function): z16[row][n_mtiles*128] =
+// W x_sorted[row], for images whose rows are not gate/up pairs (hgn v2 i4r gate_up).
+cudaError_t launch_raw_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
+                          int max_tiles, __half* z16, int32_t* status, cudaStream_t st);
+
 }  // namespace b200moe

@@ -10,6 +10,7 @@ benchmark configurations:
     codes uniform in [0,15], fp16 scales |N(0, 0.02)| per (row, 32 columns);
   * GGUF Q4_K / Q5_K / Q5_1 / Q8_0 / IQ4_NL / IQ4_XS blocks (layout: src/gguf.h:360-441) with uniform codes and
     block scales normalised so that dequantised magnitudes match the q4cp case;
+  * hgn v2 i4r tensors (4-bit codes, fp16 scale per 128 columns) with their sign-scale planes;
   * bf16 activations ~ N(0,1), router logits ~ N(0,1) with an optional per-expert
     Zipf(1.1) bias under a seeded permutation of the expert ids.
 The generator is Philox (counter based): the same seed gives the same bytes on every
@@ -148,6 +149,36 @@ def make_q80(rng, nrows, k, sigma=0.02):
     blk[:, 0:2] = (a / 127.0).astype("<f2").view(np.uint8).reshape(nb, 2)
     blk[:, 2:] = rng.integers(0, 256, size=(nb, 32), dtype=np.uint8)
     return blk.reshape(-1)
+
+
+def i4r_nbytes(rows, cols):
+    return rows * cols // 2 + rows * (cols // 128) * 2
+
+
+def make_i4r(rng, rows, cols, sigma=0.02):
+    """One hgn v2 i4r tensor blob (dtype 23; src/gpu/parts/30_host_util.inc:885-887 and
+    40_model.inc:1593-1600 of the reference): rows*cols/2 code bytes (low nibble = even column), then
+    one fp16 scale per (row, 128 columns), w = (nib - 8) * scale. Scales are signed, as the
+    reference's encoder writes them; |w| <= ~8 * |N(0, sigma / 8)|."""
+    out = np.zeros(i4r_nbytes(rows, cols), dtype=np.uint8)
+    ncode = rows * cols // 2
+    out[:ncode] = rng.integers(0, 256, size=ncode, dtype=np.uint8)
+    sc = (rng.normal(0.0, sigma / 8.0, size=(rows, cols // 128))).astype("<f2")
+    out[ncode:] = sc.view(np.uint8).reshape(-1)
+    return out
+
+
+def make_i4r_planes(rng, n):
+    """A sign-scale plane (.suh / .svh sidecar): fp16, random sign, magnitude around 1."""
+    return (rng.choice([-1.0, 1.0], size=n) * rng.uniform(0.5, 1.5, size=n)).astype("<f2")
+
+
+def make_i4r_layer(experts, d, mid, seed=0):
+    """All tensors of one hgn v2 i4r MoE layer: the two blobs and the four planes."""
+    return {"gate_up": make_i4r(rng_for(seed, 1), experts * 2 * mid, d),
+            "down": make_i4r(rng_for(seed, 2), experts * d, mid),
+            "gu_suh": make_i4r_planes(rng_for(seed, 11), d), "gu_svh": make_i4r_planes(rng_for(seed, 12), 2 * mid),
+            "dn_suh": make_i4r_planes(rng_for(seed, 13), mid), "dn_svh": make_i4r_planes(rng_for(seed, 14), d)}
 
 
 GGML_Q5_1, GGML_Q8_0, GGML_Q4_K, GGML_Q5_K, GGML_IQ4_NL, GGML_IQ4_XS = 7, 8, 12, 13, 20, 23

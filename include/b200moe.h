@@ -113,6 +113,22 @@ int b200moe_load_gguf(b200moe_handle h, int layer, const void* gate_src, const v
 int b200moe_load_shared_q4cp(b200moe_handle h, int layer, const void* gate_src, const void* up_src,
                              const void* down_src, const void* gate_w_bf16_src);
 
+/* Replaces: moe_b_v2 (src/gpu/parts/40_model.inc:4559-4680), the routed experts of hgn v2
+ * checkpoints: dtype 23 "i4r" tensors ([E*2*mid, d] and [E*d, mid]: rows*cols/2 code bytes, low
+ * nibble = even column, then one fp16 scale per 128 columns, w = (nib - 8) * scale) that live in
+ * a Hadamard-rotated domain, with their four fp16 sign-scale planes (the .suh / .svh sidecars of
+ * src/gpu/parts/30_host_util.inc:818-858, one per tensor, shared by all experts):
+ *   gu_suh [d], gu_svh [2*mid], dn_suh [mid], dn_svh [d].
+ * The layer then computes, per token and chosen expert,
+ *   out = dn_svh * Hn( sum_k w_k G_down . Hn( dn_suh * silu(g) * u ) ),  g|u = gu_svh * Hn( G_gate_up . Hn(gu_suh * x) )
+ * with Hn the block-diagonal 128-point Hadamard transform / sqrt(128) (28_kernels_hgn_v2.inc:1-15,
+ * 98-152). Every pointer may be host or device memory. Needs d % 128 == 0, mid % 128 == 0 and
+ * 2*mid <= d; runs on the tensor-core path for every T; not combined with a shared expert, with
+ * expert parallelism or with B200MOE_GEMM_SIMT (B200MOE_ERR_UNSUPPORTED). */
+int b200moe_load_i4r(b200moe_handle h, int layer, const void* gate_up_src, size_t gate_up_bytes,
+                     const void* down_src, size_t down_bytes, const void* gu_suh_f16, const void* gu_svh_f16,
+                     const void* dn_suh_f16, const void* dn_svh_f16);
+
 /* Replaces: GpuModel::moe_b from the router top-k on (src/gpu/parts/40_model.inc:4018-4157) and
  * GpuModel::moe (:1806-1861); oracle Model::moe, src/ref.cpp:574-637. Asynchronous on
  * `stream`; no allocation, no host synchronisation. out is fully overwritten. */

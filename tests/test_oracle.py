@@ -175,3 +175,25 @@ def test_non_finite_logits_keep_ids_in_range():
     xb = synth.make_x(synth.rng_for(5, 9), 3, spec.d)
     y, _, _ = oracle.moe_forward(spec, layer, synth.bf16_bits_to_f32(xb), logits=logits)
     assert np.isnan(y[:2]).all() and np.isfinite(y[2]).all()
+
+
+def test_i4r_oracle_matches_reference_converter_golden(golden_dir):
+    """hgn v2 i4r: rows of the rotated-domain matrices equal the reference converter's decode bit
+    for bit, and the rotated dataflow of oracle/i4r.py reproduces (1e-5 of the output's scale) the
+    float64 output of an ordinary SwiGLU MoE over the reference's UN-rotated weights
+    (tests/golden/make_golden.py::i4r_layer; tools/v2repro/v2enc.py of the reference)."""
+    from oracle import i4r
+    c = dict(experts=4, topk=2, d=256, mid=128, tokens=6, seed=13)   # I4R_SHAPE of tests/golden/make_golden.py
+    g = np.load(os.path.join(golden_dir, "i4r_layer.npz"))
+    E, k, d, mid, T = c["experts"], c["topk"], c["d"], c["mid"], c["tokens"]
+    L = synth.make_i4r_layer(E, d, mid, seed=c["seed"])
+    xb = synth.make_x(synth.rng_for(c["seed"], 9), T, d)
+    logits = synth.make_logits(synth.rng_for(c["seed"], 10), T, E)
+    assert layer_crc(L) == g["crc_layer"] and crc(xb) == g["crc_x"] and crc(logits) == g["crc_logits"], "generator drifted"
+    r = i4r.dequant_rot(L["gate_up"], E * 2 * mid, d, 1 * 2 * mid + 126, 4)
+    assert np.array_equal(r.view(np.uint32), g["gu_rows"].view(np.uint32))
+    r = i4r.dequant_rot(L["down"], E * d, mid, 2 * d, 3)
+    assert np.array_equal(r.view(np.uint32), g["dn_rows"].view(np.uint32))
+    ids, w = oracle.router_topk(logits, k)
+    y = i4r.moe_forward(E, d, mid, L, synth.bf16_bits_to_f32(xb), ids, w, k)
+    assert np.abs(y - g["y"]).max() <= 1e-5 * np.abs(g["y"]).max()
