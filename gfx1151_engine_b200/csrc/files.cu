@@ -281,6 +281,36 @@ extern "C" int b200moe_load_hgn_file(b200moe_handle h, int layer, const char* pa
   if (hgn_find(m, layer_name("layers.%d.mlp.experts.gate_up_proj.weight", model_layer), &gu) ||
       hgn_find(m, layer_name("layers.%d.mlp.experts.down_proj.weight", model_layer), &dn))
     return B200MOE_ERR_BAD_ARG;
+  if (gu.dtype == 23 && dn.dtype == 23) {
+    // hgn v2 i4r experts: [E, O, K] (or flat [E*O, K]) with fp16 sign-scale planes as separate
+    // tensors <base>.suh [K] (gate_up: else the shared input plane experts.su) and <base>.svh [O]
+    // (src/gpu/parts/30_host_util.inc:840-858 of the reference)
+    auto shape_ok = [&](const View& v, uint64_t O, uint64_t K) {
+      if (v.ndims == 3) return v.dims[0] == E && v.dims[1] == O && v.dims[2] == K;
+      return v.ndims == 2 && v.dims[0] == E * O && v.dims[1] == K;
+    };
+    if (!shape_ok(gu, 2 * mid, d) || !shape_ok(dn, d, mid)) return B200MOE_ERR_UNSUPPORTED;
+    auto plane = [&](const std::string& name, uint64_t n, View* out) {
+      const int r = hgn_find(m, name, out);
+      if (r != 0) return r;
+      return out->dtype == 2 && out->size == n * 2 ? 0 : 2;
+    };
+    const std::string ex = layer_name("layers.%d.mlp.experts", model_layer);
+    View p[4];
+    int r = plane(ex + ".gate_up_proj.suh", d, &p[0]);
+    if (r == 1) r = plane(ex + ".su", d, &p[0]);
+    if (r || plane(ex + ".gate_up_proj.svh", 2 * mid, &p[1]) || plane(ex + ".down_proj.suh", mid, &p[2]) ||
+        plane(ex + ".down_proj.svh", d, &p[3]))
+      return B200MOE_ERR_BAD_ARG;
+    if (int s = b200moe_load_i4r(h, layer, gu.data, gu.size, dn.data, dn.size, p[0].data, p[1].data, p[2].data, p[3].data))
+      return s;
+    View rw;
+    const int rr = hgn_find(m, layer_name("layers.%d.mlp.gate.weight", model_layer), &rw);
+    if (rr == 2) return B200MOE_ERR_BAD_ARG;
+    if (rr == 0 && rw.dtype == 0 && rw.size >= E * d * 2 && E <= 512 && d % 64 == 0)
+      if (int s = b200moe_load_router(h, layer, rw.data)) return s;
+    return B200MOE_OK;
+  }
   if (gu.dtype != 5 || dn.dtype != 5 || gu.ndims != 2 || dn.ndims != 2 || gu.dims[0] != E * 2 * mid || gu.dims[1] != d ||
       dn.dims[0] != E * d || dn.dims[1] != mid)
     return B200MOE_ERR_UNSUPPORTED;

@@ -193,6 +193,66 @@ def test_hgn_file_with_shared_expert_and_router(cuda, tmp_path):
         op.load_hgn_file(0, str(tmp_path / "missing.hgn"))
 
 
+def i4r_hgn_tensors(L, E, d, mid, layer_no, shared_su):
+    """An hgn v2 layer: dtype 23 expert tensors [E, O, K] and their fp16 planes; the input plane of
+    gate_up under its own name or as experts.su (src/gpu/parts/30_host_util.inc:852-856)."""
+    ex = "layers.%d.mlp.experts" % layer_no
+    return [
+        (ex + ".gate_up_proj.weight", 23, (E, 2 * mid, d), L["gate_up"].tobytes()),
+        (ex + ".down_proj.weight", 23, (E, d, mid), L["down"].tobytes()),
+        (ex + (".su" if shared_su else ".gate_up_proj.suh"), 2, (d,), L["gu_suh"].tobytes()),
+        (ex + ".gate_up_proj.svh", 2, (2 * mid,), L["gu_svh"].tobytes()),
+        (ex + ".down_proj.suh", 2, (mid,), L["dn_suh"].tobytes()),
+        (ex + ".down_proj.svh", 2, (d,), L["dn_svh"].tobytes()),
+    ]
+
+
+@needs_ref
+def test_reference_reader_accepts_the_synthetic_i4r_file(tmp_path):
+    import zlib
+
+    import oracle
+    E, d, mid = 4, 256, 128
+    L = synth.make_i4r_layer(E, d, mid, seed=29)
+    path = str(tmp_path / "v2.hgn")
+    tensors = i4r_hgn_tensors(L, E, d, mid, 2, True)
+    write_hgn(path, tensors)
+    for name, dtype, dims, raw in tensors:
+        t = oracle.ref_file_tensor("hgn", path, name)
+        assert t is not None and t["dtype"] == dtype and t["dims"][:len(dims)] == list(dims)
+        assert t["size"] == len(raw) and t["crc32"] == zlib.crc32(raw)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shared_su", [False, True])
+def test_hgn_v2_file_with_i4r_experts(cuda, tmp_path, shared_su):
+    """dtype 23 experts and their planes from a file give the bytes of the in-memory load."""
+    torch = cuda
+    E, k, d, mid, T = 4, 2, 256, 128, 40
+    L = synth.make_i4r_layer(E, d, mid, seed=29)
+    path = str(tmp_path / "v2.hgn")
+    write_hgn(path, i4r_hgn_tensors(L, E, d, mid, 2, shared_su))
+    xb = synth.make_x(synth.rng_for(29, 9), T, d)
+    logits = synth.make_logits(synth.rng_for(29, 1), T, E)
+    spec = synth.LayerSpec(experts=E, topk=k, d=d, mid=mid)
+    op_mem = pkg.MoeOperator(E, k, d, mid, T)
+    op_mem.load_i4r(0, L["gate_up"], L["down"], L["gu_suh"], L["gu_svh"], L["dn_suh"], L["dn_svh"])
+    y_mem = run_layer(torch, op_mem, spec, xb, logits)
+    op = pkg.MoeOperator(E, k, d, mid, T)
+    op.load_hgn_file(0, path, model_layer=2)
+    assert np.isfinite(y_mem).all() and np.array_equal(bits(run_layer(torch, op, spec, xb, logits)), bits(y_mem))
+    with open(path, "r+b") as f:     # a plane of the wrong length is refused
+        raw = f.read()
+    bad = str(tmp_path / "bad.hgn")
+    tensors = i4r_hgn_tensors(L, E, d, mid, 2, shared_su)
+    tensors[3] = (tensors[3][0], 2, (2 * mid - 1,), tensors[3][3][:-2])
+    write_hgn(bad, tensors)
+    with pytest.raises(pkg.B200MoeError):
+        op.load_hgn_file(0, bad, model_layer=2)
+    op.close()
+    op_mem.close()
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("sharded,gu,dn", [(False, 12, 7), (True, 12, 7), (False, 20, 23), (True, 23, 20), (False, 13, 7), (True, 8, 8)])
 def test_gguf_file(cuda, tmp_path, sharded, gu, dn):
