@@ -272,7 +272,7 @@ def main():
                     help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
     ap.add_argument("--ep-split", type=int, default=1,
                     help="N>1, p2p transport: 1 (default) = the rows a rank keeps are multiplied in place (no copy), apart from the other ranks' rows; 0 = one GEMM pass per chunk over copied rows")
-    ap.add_argument("--own-order", default="first", choices=["first", "ends"],
+    ap.add_argument("--own-order", default="ends", choices=["first", "ends"],
                     help="N>1, --ep-split 1: the in-place own-rows passes all up front, or the last chunk's at the very end")
     ap.add_argument("--check", type=int, default=1,
                     help="N>1: 1 (default) = compare rank 0's output with the single-GPU operator on the same tokens; 0 = skip")

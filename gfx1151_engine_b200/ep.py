@@ -103,7 +103,7 @@ class ExpertParallelMoe:
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
                  cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False,
-                 has_shared=False, own_order="first"):
+                 has_shared=False, own_order="ends"):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
