@@ -23,10 +23,24 @@ constexpr int kTileK = 64;
 constexpr int kCodeBytes = kTileM * kTileK / 2;  // 4096
 
 enum Format : int {
-  kQ4CP = 0,  // meta: [r][2] fp16 scale                                   -> 512 B
-  kQ4K = 1,   // meta: [r]{fp16 d, fp16 dmin, u8 sc0, u8 m0, u8 sc1, u8 m1} -> 1024 B
-  kQ51 = 2    // meta: [r][2]{fp16 d, fp16 m, u32 high bits}                -> 2048 B
+  kQ4CP = 0,  // meta: [r]{fp16 scale of half 0, of half 1}                          -> 512 B
+  kQ4K = 1,   // meta: [r]{fp16 d, fp16 dmin, u8 sc0, u8 m0, u8 sc1, u8 m1}           -> 1024 B
+  kQ51 = 2    // meta: [r]{fp16 d0, fp16 m0, u32 fifth bits 0, fp16 d1, fp16 m1, u32 fifth bits 1} -> 2048 B
 };
+// kQ51, the fifth-bit word of a 32-group: bit i (i < 16) belongs to the LOW-nibble code of code
+// byte i (element 2i of the group), bit 16 + i to its high-nibble code (element 2i + 1). With the
+// two bits of a code byte 16 apart, one shift and one mask move them to bits 14 and 30 -- the
+// fp16 pair (2.0 or 0, 2.0 or 0) -- and a single half2 multiply-add by 8 adds the 16s to the two
+// looked-up codes.
+__host__ __device__ inline uint32_t fifth_bits_split(uint32_t by_element) {  // bit j = element j  ->  the layout above
+  uint32_t r = 0;
+  for (int i = 0; i < 16; i++)
+    r |= (((by_element >> (2 * i)) & 1u) << i) | (((by_element >> (2 * i + 1)) & 1u) << (16 + i));
+  return r;
+}
+__host__ __device__ inline uint32_t fifth_bit_of(uint32_t split, int j) {  // fifth bit of element j of the group
+  return (split >> ((j & 1) ? 16 + (j >> 1) : (j >> 1))) & 1u;
+}
 // GGUF Q8_0 (int8 codes q, fp16 d per 32: w = d * q) has no tile layout of its own. With the
 // biased code u = q + 128 = 16 * hi + lo the weight is d * (16 * hi - 128) + d * lo: two 4-bit
 // tensors over the SAME activations. The image is kQ51 with twice the K blocks -- for every 64

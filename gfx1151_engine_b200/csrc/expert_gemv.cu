@@ -89,8 +89,9 @@ __device__ __forceinline__ float chunk_dot(const uint4 c, uint32_t lut, uint32_t
   return s0 + s1;
 }
 
-// Q5_1: the same with the fifth bits (bits 2i, 2i+1 of qh belong to code byte i) added to
-// the looked-up pair as 16.0 before the multiply-add: q + 16*bit <= 31 is exact in fp16.
+// Q5_1: the same with the fifth bits (bits i, 16 + i of qh belong to code byte i; shifted to bits
+// 14 and 30 they are the fp16 pair 2.0 / 0) added to the looked-up pair as 8 * 2.0 by one half2
+// multiply-add before the products: q + 16*bit <= 31 is exact in fp16.
 __device__ __forceinline__ float chunk_dot5(const uint4 c, uint32_t qh, uint32_t lut, uint32_t xs) {
   const uint32_t w4[4] = {c.x, c.y, c.z, c.w};
   float s0 = 0.f, s1 = 0.f;
@@ -100,10 +101,10 @@ __device__ __forceinline__ float chunk_dot5(const uint4 c, uint32_t qh, uint32_t
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xs + q * 16));
 #pragma unroll
     for (int b = 0; b < 4; b++) {
-      const uint32_t t = (qh >> (2 * (q * 4 + b))) & 3u;
-      const uint32_t hi = (t & 1u) * 0x4C00u + (t >> 1) * 0x4C000000u;  // 16.0 in fp16 where the bit is set
+      const int i = q * 4 + b;
+      const uint32_t u = (i <= 14 ? (qh << (14 - i)) : (qh >> 1)) & 0x40004000u;
       const uint32_t pair = lds_b32(__byte_perm(w4[q], lut, 0x7604 | (b << 4)));
-      const __half2 w2 = __hadd2(*(const __half2*)&pair, *(const __half2*)&hi);
+      const __half2 w2 = __hfma2(*(const __half2*)&u, __float2half2_rn(8.f), *(const __half2*)&pair);
       fma_pair((b & 1) ? s1 : s0, *(const uint32_t*)&w2, x[b]);
     }
   }

@@ -57,7 +57,7 @@ struct RowMeta<kQ51> {
     qh = *(const uint32_t*)(p + 4);
   }
   __device__ __forceinline__ float value(int nib, int j) const {
-    int x = nib | (int)(((qh >> j) & 1u) << 4);
+    int x = nib | (int)(fifth_bit_of(qh, j) << 4);
     return __fadd_rn(__fmul_rn((float)x, d), m);
   }
 };

@@ -298,11 +298,12 @@ struct GroupDecode<kQ51> {  // w = d*(q + 16*fifth bit) + m, src/gguf.h:360-374
     d2 = __half2half2(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
     m2 = __half2half2(__ushort_as_half((unsigned short)(dm >> 16)));
   }
-  // byte i of the group holds elements 2i, 2i+1; their fifth bits are bits 2i, 2i+1 of qh
+  // byte i of the group holds elements 2i, 2i+1; their fifth bits are bits i, 16 + i of qh:
+  // shifted to bits 14 and 30 they read as the fp16 pair (2.0 or 0, 2.0 or 0)
   __device__ __forceinline__ __half2 weight(uint32_t pair, int i) const {
-    const uint32_t t = (qh >> (2 * i)) & 3u;
-    const uint32_t hi = (t & 1u) * 0x4C00u + (t >> 1) * 0x4C000000u;  // 16.0 in fp16 where the bit is set
-    return __hfma2(__hadd2(*(__half2*)&pair, *(const __half2*)&hi), d2, m2);
+    const uint32_t u = (i <= 14 ? (qh << (14 - i)) : (qh >> 1)) & 0x40004000u;
+    const __half2 q5 = __hfma2(*(const __half2*)&u, __float2half2_rn(8.f), *(const __half2*)&pair);
+    return __hfma2(q5, d2, m2);
   }
 };
 

@@ -111,7 +111,8 @@ __global__ void k_repack_q4k(Image img, SrcTensor a, SrcTensor b, int K, int fir
 }
 
 // Q5_1: one thread per (tile, row, half). Element j of a block is the low nibble of qs[j],
-// element j+16 the high nibble (src/gguf.h:360-374); the fifth bits stay in their word.
+// element j+16 the high nibble (src/gguf.h:360-374); the fifth bits follow their codes into the
+// image's order and then take the split layout of common.cuh.
 __global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int first_expert,
                              const int32_t* __restrict__ emap) {
   const long long total = (long long)img.n_experts * img.n_mtiles * img.n_kblocks * 256;
@@ -139,7 +140,11 @@ __global__ void k_repack_q51(Image img, SrcTensor a, SrcTensor b, int K, int fir
     *(uint4*)(dst + h * 2048 + r * 16) = *(uint4*)out;
     uint8_t* meta = dst + kCodeBytes + r * 16 + h * 8;
 #pragma unroll
-    for (int q = 0; q < 8; q++) meta[q] = blk[q];
+    for (int q = 0; q < 4; q++) meta[q] = blk[q];
+    // the image keeps the block's element order (code byte i = elements 2i, 2i+1), and bit j of the
+    // source word belongs to element j
+    const uint32_t qh = (uint32_t)blk[4] | ((uint32_t)blk[5] << 8) | ((uint32_t)blk[6] << 16) | ((uint32_t)blk[7] << 24);
+    *(uint32_t*)(meta + 4) = fifth_bits_split(qh);
   }
 }
 
@@ -184,7 +189,7 @@ __global__ void k_repack_q5k(Image img, SrcTensor a, SrcTensor b, int K, int fir
     uint8_t* meta = dst + kCodeBytes + r * 16 + h * 8;
     *(__half*)meta = __float2half_rn(__fmul_rn(d, (float)sc));
     *(__half*)(meta + 2) = __float2half_rn(-__fmul_rn(dmin, (float)mn));
-    *(uint32_t*)(meta + 4) = fifth;
+    *(uint32_t*)(meta + 4) = fifth_bits_split(fifth);
   }
 }
 
@@ -332,7 +337,7 @@ __global__ void k_dequant_rows(Image img, int expert, int row0, int nrows, int m
       float d = half_bits_to_f32(*(const uint16_t*)m);
       float mn = half_bits_to_f32(*(const uint16_t*)(m + 2));
       uint32_t qh = *(const uint32_t*)(m + 4);
-      int x = nib | (int)(((qh >> j) & 1u) << 4);
+      int x = nib | (int)(fifth_bit_of(qh, j) << 4);
       v = __fadd_rn(__fmul_rn((float)x, d), mn);
     }
     out[i] = v;
