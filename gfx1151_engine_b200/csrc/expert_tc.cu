@@ -253,11 +253,19 @@ struct KParams {
   int l2_ahead;      // weight tiles are asked into L2 this many own pairs ahead of their register fetch (0: off)
 };
 constexpr int kTraceSlots = 512;
+// Timeline stamps of CTA 0 (a debugging aid: build with -DB200MOE_TRACE and set
+// B200MOE_TC_TRACE=<file>). Compiled out otherwise: with the stamps merely present but switched
+// off the benchmark call took 7 % longer -- the loops below are that sensitive to extra
+// instructions.
+#ifndef B200MOE_TRACE
+#define TR(role, slot, ev) do {} while (0)
+#else
 #define TR(role, slot, ev)                                                            \
   do {                                                                                \
     if (p.trace && blockIdx.x == 0 && (slot) < (uint32_t)kTraceSlots)                 \
       p.trace[((role) * kTraceSlots + (slot)) * 4 + (ev)] = clock64();                \
   } while (0)
+#endif
 
 // Per (row, K block) metadata of the source format, as loaded by a dequantising thread.
 struct RowMetaTc {
@@ -380,7 +388,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
   if (warp == 0) {
     // ================= producer of activation tiles (one tensor copy per K block) =========
     if (lane == 0) {
-      uint32_t pi = 0;
+      uint32_t pi = 0, slot = 0, sph = 0;
       bool ok = true;
       Tile t_ahead = (int)blockIdx.x < n_items ? p.tiles[blockIdx.x / img.n_mtiles] : Tile{0, 0, 0};
       for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
@@ -391,7 +399,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         const CUtensorMap* map = n_pad <= 16 ? &map16 : n_pad <= 64 ? &map64 : n_pad <= 128 ? &map128 : &map192;
         const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : kTcTileN) * 128;
         for (int pp = 0; pp < NP && ok; pp++, pi++) {
-          const uint32_t slot = pi % kNBS, sph = (pi / kNBS) & 1;
+          // slot = pi % kNBS, sph = (pi / kNBS) & 1, kept as counters (no division in the loop)
           const int nk = min(2, KB - 2 * pp);
           ok = mbar_wait(bars + 8 * (kBarDone + slot), sph ^ 1, abort_flag, p.status, 2, 64);
           if (!ok) break;
@@ -400,6 +408,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           mbar_expect_tx(bar, nk * bytes);
           for (int j = 0; j < nk; j++)
             tma_load_2d(sbase + M::slot(slot) + j * kBStage, map, ((2 * pp + j) >> img.act_shift) * kTileK, t.first, bar);
+          if (++slot == (uint32_t)kNBS) {
+            slot = 0;
+            sph ^= 1;
+          }
         }
       }
     }
@@ -409,6 +421,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // (Measured: checking a barrier costs this warp 150-250 cycles under load even when its
     // phase is long complete, and the MMA queue holds about four instructions.)
     uint32_t pi = 0, li = 0;
+    uint32_t aslot = 0, aph = 0, bslot = 0;  // pi % kNS, (pi / kNS) & 1, pi % kNBS as counters
     bool ok = true;
     Tile t_ahead = (int)blockIdx.x < n_items ? p.tiles[blockIdx.x / img.n_mtiles] : Tile{0, 0, 0};
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, li++) {
@@ -422,7 +435,6 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       tc_fence_after();
       const uint32_t d_tmem = tmem + acc * kAccCols;
       for (int pp = 0; pp < NP && ok; pp++, pi++) {
-        const uint32_t aslot = pi % kNS, aph = (pi / kNS) & 1, bslot = pi % kNBS;
         const int nk = min(2, KB - 2 * pp);
         // one wait covers both operands: the relay thread arrives only after the
         // activation tiles of this pair have landed
@@ -449,6 +461,11 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         }
         __syncwarp();
         if (lane == 0) TR(1, pi, 2);
+        if (++aslot == (uint32_t)kNS) {
+          aslot = 0;
+          aph ^= 1;
+        }
+        if (++bslot == (uint32_t)kNBS) bslot = 0;
       }
     }
   } else if (warp >= 4 && warp < 20) {
@@ -472,6 +489,9 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // counters, and the first tile of the NEXT item is looked up when an item is entered,
     // so that no fetch waits for the dependent read of the tile list.
     const size_t tile_b = img.tile_stride();
+    // byte offsets of this thread's reads inside a tile: its 16 code bytes of half 0 and its metadata
+    constexpr int kMetaRow = FMT == kQ4CP ? 4 : FMT == kQ4K ? 8 : 16;
+    const uint32_t off_c = (uint32_t)r * 16u, off_m = (uint32_t)kCodeBytes + (uint32_t)r * kMetaRow;
     auto item_base = [&](int io) -> const uint8_t* {
       const int item = blockIdx.x + io * (int)gridDim.x;
       if (io >= my_items) return nullptr;
@@ -481,6 +501,9 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     int f_io = set / NP, f_pp = set % NP;
     const uint8_t* f_base = item_base(f_io);
     const uint8_t* f_next = item_base(f_io + io_step);
+    // f_tile walks with the stream: the tile of K block 2 * f_pp + kblk of the current item
+    const uint8_t* f_tile = f_base ? f_base + (size_t)(2 * f_pp + kblk) * tile_b : nullptr;
+    const size_t step_b = 4 * tile_b;  // the set's next pair is two pairs = four K blocks further
     auto fetch = [&](uint4& a, uint4& b, RowMetaTc& s2x) {
       // The register fetch below is one own pair ahead of its use, i.e. ~18 KB in flight per SM.
       // One lane per (set, K block) also asks for the whole tile of a later pair -- of this item
@@ -501,38 +524,42 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b2 + (size_t)(2 * q + kblk) * tile_b), "r"((uint32_t)tile_b)
                        : "memory");
       }
-      const int kb = 2 * f_pp + kblk;
-      if (f_base != nullptr && kb < KB) {
-        const uint8_t* tp = f_base + (size_t)kb * tile_b;
-        a = __ldg((const uint4*)(tp + r * 16));
-        b = __ldg((const uint4*)(tp + 2048 + r * 16));
+      if (f_tile != nullptr && 2 * f_pp + kblk < KB) {
+        a = __ldg((const uint4*)(f_tile + off_c));
+        b = __ldg((const uint4*)(f_tile + off_c + 2048));
         if (FMT == kQ4CP) {
-          s2x.a = __ldg((const uint32_t*)(tp + kCodeBytes + r * 4));
+          s2x.a = __ldg((const uint32_t*)(f_tile + off_m));
         } else if (FMT == kQ4K) {
-          const uint2 u = __ldg((const uint2*)(tp + kCodeBytes + r * 8));
+          const uint2 u = __ldg((const uint2*)(f_tile + off_m));
           s2x.a = u.x;
           s2x.b = u.y;
         } else {
-          const uint4 u = __ldg((const uint4*)(tp + kCodeBytes + r * 16));
+          const uint4 u = __ldg((const uint4*)(f_tile + off_m));
           s2x = RowMetaTc{u.x, u.y, u.z, u.w};
         }
       }
       f_pp += 2;
-      if (f_pp >= NP) {
+      if (f_pp < NP) {
+        if (f_tile != nullptr) f_tile += step_b;
+      } else {
         f_pp -= NP * io_step;  // NP == 1: two items further, same pair
         f_io += io_step;
         f_base = f_next;
         f_next = item_base(f_io + io_step);
+        f_tile = f_base ? f_base + (size_t)(2 * f_pp + kblk) * tile_b : nullptr;
       }
     };
     fetch(ca, cb, sc);
     int c_pp = set % NP;  // pair-in-item of the decode stream
     bool ok = true;
+    static_assert(kNS == 2, "a set always fills the tensor-memory slot of its own index");
+    const uint32_t aslot = (uint32_t)set;
+    uint32_t qslot = (uint32_t)set % kNBS, qph = 0;  // (pi - kNS) % kNBS and ((pi - kNS) / kNBS) & 1, from pi == set + kNS on
     for (uint32_t pi = set; pi < total && ok; pi += 2) {
       const bool mine = 2 * c_pp + kblk < KB;  // false only for the second K block of an odd tail
-      const uint32_t aslot = pi % kNS;
       c_pp += 2;
       if (c_pp >= NP) c_pp -= NP * io_step;
+      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 2);
       fetch(na, nb, nsc);
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 0);
       uint32_t v[32];
@@ -558,11 +585,15 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       }
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 1);
       if (pi >= (uint32_t)kNS) {
-        // the slot is free once the MMAs of the pair that used it before have completed
-        const uint32_t q = pi - kNS;
-        ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 7);
+        // the slot is free once the MMAs of the pair that used it before (pi - kNS) have completed
+        ok = mbar_wait(bars + 8 * (kBarDone + qslot), qph, abort_flag, p.status, 7);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        qslot += 2;  // the set's next pair is two further
+        if (qslot >= (uint32_t)kNBS) {
+          qslot -= kNBS;
+          qph ^= 1;
+        }
       }
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 2);
       if (mine) {
@@ -574,27 +605,41 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + aslot));
+      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 0);
       ca = na;
       cb = nb;
       sc = nsc;
+      asm volatile("" ::"r"(ca.x), "r"(ca.w), "r"(cb.x), "r"(cb.w), "r"(sc.a));
+      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 1);
     }
   } else if (warp == 3) {
     // ================= relay: "activations landed" folded into the A-slot barrier ==========
     if (lane == 0) {
       uint32_t pi = 0;
+      uint32_t bslot = 0, bph = 0;  // pi % kNBS, (pi / kNBS) & 1
+      uint32_t qslot = 0, qph = 0;  // the same for q = pi - kNS (valid from pi == kNS on)
+      uint32_t aslot = 0;           // pi % kNS
       bool ok = true;
       for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
         for (int pp = 0; pp < NP && ok; pp++, pi++) {
-          ok = mbar_wait(bars + 8 * (kBarBFull + pi % kNBS), (pi / kNBS) & 1, abort_flag, p.status, 9);
+          ok = mbar_wait(bars + 8 * (kBarBFull + bslot), bph, abort_flag, p.status, 9);
           if (!ok) break;
           // an arrival must fall into the barrier's current phase: the slot's previous use is
           // over once the MMAs of pair pi - kNS have completed
           if (pi >= (uint32_t)kNS) {
-            const uint32_t q = pi - kNS;
-            ok = mbar_wait(bars + 8 * (kBarDone + q % kNBS), (q / kNBS) & 1, abort_flag, p.status, 10);
+            ok = mbar_wait(bars + 8 * (kBarDone + qslot), qph, abort_flag, p.status, 10);
             if (!ok) break;
+            if (++qslot == (uint32_t)kNBS) {
+              qslot = 0;
+              qph ^= 1;
+            }
           }
-          mbar_arrive(bars + 8 * (kBarAFull + pi % kNS));
+          mbar_arrive(bars + 8 * (kBarAFull + aslot));
+          if (++bslot == (uint32_t)kNBS) {
+            bslot = 0;
+            bph ^= 1;
+          }
+          if (++aslot == (uint32_t)kNS) aslot = 0;
         }
       }
     }
