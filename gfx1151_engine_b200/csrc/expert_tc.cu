@@ -488,7 +488,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // The fetch stream runs one own pair ahead of the decode. It walks (item, pair) with
     // counters, and the first tile of the NEXT item is looked up when an item is entered,
     // so that no fetch waits for the dependent read of the tile list.
-    const size_t tile_b = img.tile_stride();
+    constexpr size_t tile_b = tile_bytes(FMT);  // the launcher picks FMT from img.fmt
     // byte offsets of this thread's reads inside a tile: its 16 code bytes of half 0 and its metadata
     constexpr int kMetaRow = FMT == kQ4CP ? 4 : FMT == kQ4K ? 8 : 16;
     const uint32_t off_c = (uint32_t)r * 16u, off_m = (uint32_t)kCodeBytes + (uint32_t)r * kMetaRow;
