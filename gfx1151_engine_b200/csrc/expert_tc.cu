@@ -398,7 +398,30 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         // smallest box that covers the tile's rows: 16, 64, 128 or 192 rows of 64 halfs
         const CUtensorMap* map = n_pad <= 16 ? &map16 : n_pad <= 64 ? &map64 : n_pad <= 128 ? &map128 : &map192;
         const uint32_t bytes = (n_pad <= 16 ? 16 : n_pad <= 64 ? 64 : n_pad <= 128 ? 128 : kTcTileN) * 128;
+        // The dequantising warps fetch their packed weights into registers only one own pair ahead
+        // of their use (~18 KB in flight per SM). This thread, which has time to spare, also asks for
+        // both tiles of a later pair -- of this item or of the next one -- to be brought into L2
+        // with one bulk prefetch, so that the fetch finds them there. Measured: 6 % on a launch
+        // whose tiles all have ~10 rows (short MMAs: the fetch latency shows), nothing on the
+        // benchmark's mix; with every weight read served from L2 (a diagnostic run on one expert's
+        // tiles) such a launch gains 23 %.
+        constexpr size_t w_tile_b = tile_bytes(FMT);
+        const uint8_t* w_this = img.tile(t.expert, it % img.n_mtiles, 0);
+        const uint8_t* w_next =
+            it + (int)gridDim.x < n_items ? img.tile(t_ahead.expert, (it + (int)gridDim.x) % img.n_mtiles, 0) : nullptr;
         for (int pp = 0; pp < NP && ok; pp++, pi++) {
+          if (p.l2_ahead > 0) {
+            int q = pp + 2 * p.l2_ahead;
+            const uint8_t* b2 = w_this;
+            if (q >= NP) {
+              q -= NP;
+              b2 = w_next;
+            }
+            if (b2 != nullptr && q < NP)
+              asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b2 + (size_t)(2 * q) * w_tile_b),
+                           "r"((uint32_t)(min(2, KB - 2 * q) * (int)w_tile_b))
+                           : "memory");
+          }
           // slot = pi % kNBS, sph = (pi / kNBS) & 1, kept as counters (no division in the loop)
           const int nk = min(2, KB - 2 * pp);
           ok = mbar_wait(bars + 8 * (kBarDone + slot), sph ^ 1, abort_flag, p.status, 2, 64);
@@ -504,27 +527,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     // f_tile walks with the stream: the tile of K block 2 * f_pp + kblk of the current item
     const uint8_t* f_tile = f_base ? f_base + (size_t)(2 * f_pp + kblk) * tile_b : nullptr;
     const size_t step_b = 4 * tile_b;  // the set's next pair is two pairs = four K blocks further
+    bool f_valid = false;              // the last fetch had a K block to read (false only beyond an odd tail or the last item)
     auto fetch = [&](uint4& a, uint4& b, RowMetaTc& s2x) {
-      // The register fetch below is one own pair ahead of its use, i.e. ~18 KB in flight per SM.
-      // One lane per (set, K block) also asks for the whole tile of a later pair -- of this item
-      // or of the next one -- to be brought into L2 with a single bulk prefetch, so that the
-      // fetch finds it there. Measured: 6 % on a launch whose tiles all have ~10 rows (short
-      // MMAs: the fetch latency shows), nothing on the benchmark's mix; with every weight read
-      // served from L2 (a diagnostic run on one expert's tiles) such a launch gains 23 %, the
-      // rest of a small tile's ~830 cycles per K-block pair is the store -> MMA -> completion
-      // handshake between the dequantising warps and the MMA warp.
-      if (NP > 1 && p.l2_ahead > 0 && quarter == 0 && lane == 0) {
-        int q = f_pp + 2 * p.l2_ahead;
-        const uint8_t* b2 = f_base;
-        if (q >= NP) {
-          q -= NP;
-          b2 = f_next;
-        }
-        if (b2 != nullptr && q < NP && 2 * q + kblk < KB)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b2 + (size_t)(2 * q + kblk) * tile_b), "r"((uint32_t)tile_b)
-                       : "memory");
-      }
-      if (f_tile != nullptr && 2 * f_pp + kblk < KB) {
+      f_valid = f_tile != nullptr && 2 * f_pp + kblk < KB;
+      if (f_valid) {
         a = __ldg((const uint4*)(f_tile + off_c));
         b = __ldg((const uint4*)(f_tile + off_c + 2048));
         if (FMT == kQ4CP) {
@@ -550,15 +556,12 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       }
     };
     fetch(ca, cb, sc);
-    int c_pp = set % NP;  // pair-in-item of the decode stream
+    bool mine = f_valid;  // the codes in (ca, cb, sc) are a K block of this thread's
     bool ok = true;
     static_assert(kNS == 2, "a set always fills the tensor-memory slot of its own index");
     const uint32_t aslot = (uint32_t)set;
     uint32_t qslot = (uint32_t)set % kNBS, qph = 0;  // (pi - kNS) % kNBS and ((pi - kNS) / kNBS) & 1, from pi == set + kNS on
     for (uint32_t pi = set; pi < total && ok; pi += 2) {
-      const bool mine = 2 * c_pp + kblk < KB;  // false only for the second K block of an odd tail
-      c_pp += 2;
-      if (c_pp >= NP) c_pp -= NP * io_step;
       if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 2);
       fetch(na, nb, nsc);
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 0);
@@ -609,7 +612,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       ca = na;
       cb = nb;
       sc = nsc;
-      asm volatile("" ::"r"(ca.x), "r"(ca.w), "r"(cb.x), "r"(cb.w), "r"(sc.a));
+      mine = f_valid;
       if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 1);
     }
   } else if (warp == 3) {
