@@ -506,8 +506,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     const uint32_t lut = (uint32_t)M::kOffLut | (uint32_t)(DUAL && r >= 64 ? 128 : 0) | (uint32_t)(lane * 4);
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t total = (uint32_t)my_items * (uint32_t)NP;
-    uint4 ca = make_uint4(0, 0, 0, 0), cb = ca, na = ca, nb = ca;
-    RowMetaTc sc = RowMetaTc{0, 0, 0, 0}, nsc = sc;
+    uint4 ca = make_uint4(0, 0, 0, 0), cb = ca;
+    RowMetaTc sc = RowMetaTc{0, 0, 0, 0};
     // The fetch stream runs one own pair ahead of the decode. It walks (item, pair) with
     // counters, and the first tile of the NEXT item is looked up when an item is entered,
     // so that no fetch waits for the dependent read of the tile list.
@@ -562,11 +562,10 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     const uint32_t aslot = (uint32_t)set;
     uint32_t qslot = (uint32_t)set % kNBS, qph = 0;  // (pi - kNS) % kNBS and ((pi - kNS) / kNBS) & 1, from pi == set + kNS on
     for (uint32_t pi = set; pi < total && ok; pi += 2) {
-      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 2);
-      fetch(na, nb, nsc);
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 0);
       uint32_t v[32];
-      if (mine) {
+      const bool mine_now = mine;
+      if (mine_now) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           GroupDecode<FMT> gd;
@@ -586,6 +585,11 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
           }
         }
       }
+      // The codes are used up: the next own pair's go into the same registers (no second set, no
+      // copies). They have the rest of this iteration and the wait of the next one to arrive, and
+      // the producer thread's L2 prefetch has put them close.
+      fetch(ca, cb, sc);
+      mine = f_valid;
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 1);
       if (pi >= (uint32_t)kNS) {
         // the slot is free once the MMAs of the pair that used it before (pi - kNS) have completed
@@ -599,7 +603,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
         }
       }
       if (lane == 0 && quarter == 0) TR(2 + kblk, pi, 2);
-      if (mine) {
+      if (mine_now) {
         tc_fence_after();
         tc_st32(tmem + ((uint32_t)(quarter * 32) << 16) + kTmemA + aslot * 64 + kblk * 32, v);
         tc_wait_st();
@@ -608,12 +612,6 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * (kBarAFull + aslot));
-      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 0);
-      ca = na;
-      cb = nb;
-      sc = nsc;
-      mine = f_valid;
-      if (lane == 0 && quarter == 0 && kblk == 0) TR(5, pi, 1);
     }
   } else if (warp == 3) {
     // ================= relay: "activations landed" folded into the A-slot barrier ==========
