@@ -240,7 +240,12 @@ __device__ __forceinline__ uint32_t instr_desc(int n) {
 }
 
 // finite values saturate to the fp16 range (as on the GEMV path), NaN stays NaN
-__device__ __forceinline__ float sat_f16(float v) { return v != v ? v : fminf(fmaxf(v, -65504.f), 65504.f); }
+// fp32 -> fp16, finite values saturating to the fp16 range, NaN staying NaN: one conversion
+__device__ __forceinline__ __half f16_sat(float v) {
+  unsigned short h;
+  asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
+  return __ushort_as_half(h);
+}
 
 struct KParams {
   Image img;
@@ -696,13 +701,13 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
 #pragma unroll
             for (int j = 0; j < 16; j++) {
               const float g = __uint_as_float(v[j]), u = xu[(pq * 16 + j) * 32 + lane];
-              outs[j * 64 + pq * 32 + lane] = __float2half_rn(sat_f16(__fdividef(g, 1.f + __expf(-g)) * u));
+              outs[j * 64 + pq * 32 + lane] = f16_sat(__fdividef(g, 1.f + __expf(-g)) * u);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
               const float u = __uint_as_float(v[16 + j]), g = xg[(pq * 16 + j) * 32 + lane];
-              outs[(16 + j) * 64 + pq * 32 + lane] = __float2half_rn(sat_f16(__fdividef(g, 1.f + __expf(-g)) * u));
+              outs[(16 + j) * 64 + pq * 32 + lane] = f16_sat(__fdividef(g, 1.f + __expf(-g)) * u);
             }
           }
           asm volatile("bar.sync 3, 128;" ::: "memory");
