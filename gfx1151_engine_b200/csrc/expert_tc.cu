@@ -285,7 +285,7 @@ template <>
 struct GroupDecode<kQ4CP> {  // w = f16(book) * f16(scale)
   __half2 s2;
   __device__ __forceinline__ void init(const RowMetaTc& m, int h) {
-    const uint32_t s16 = h ? (m.a >> 16) : (m.a & 0xFFFFu), v = s16 | (s16 << 16);
+    const uint32_t v = __byte_perm(m.a, 0u, h ? 0x3232u : 0x1010u);  // the half's fp16 scale in both lanes
     s2 = *(const __half2*)&v;
   }
   __device__ __forceinline__ __half2 weight(uint32_t pair, int) const { return __hmul2(*(__half2*)&pair, s2); }
@@ -536,16 +536,17 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
     auto fetch = [&](uint4& a, uint4& b, RowMetaTc& s2x) {
       f_valid = f_tile != nullptr && 2 * f_pp + kblk < KB;
       if (f_valid) {
-        a = __ldg((const uint4*)(f_tile + off_c));
-        b = __ldg((const uint4*)(f_tile + off_c + 2048));
+        const uint8_t* pc = f_tile + off_c;  // the metadata sits off_m - off_c bytes further
+        a = __ldg((const uint4*)pc);
+        b = __ldg((const uint4*)(pc + 2048));
         if (FMT == kQ4CP) {
-          s2x.a = __ldg((const uint32_t*)(f_tile + off_m));
+          s2x.a = __ldg((const uint32_t*)(pc + (off_m - off_c)));
         } else if (FMT == kQ4K) {
-          const uint2 u = __ldg((const uint2*)(f_tile + off_m));
+          const uint2 u = __ldg((const uint2*)(pc + (off_m - off_c)));
           s2x.a = u.x;
           s2x.b = u.y;
         } else {
-          const uint4 u = __ldg((const uint4*)(f_tile + off_m));
+          const uint4 u = __ldg((const uint4*)(pc + (off_m - off_c)));
           s2x = RowMetaTc{u.x, u.y, u.z, u.w};
         }
       }
