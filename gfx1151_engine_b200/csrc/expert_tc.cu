@@ -11,15 +11,17 @@
 // One CTA per SM, 24 warps with fixed roles. K blocks (64 wide) are handled in pairs:
 //   warp 0      producer of activation tiles: TMA tensor copies (128-byte swizzle, box of
 //               16/64/128/192 rows), one per K block, into a ring of 3 pair-slots in shared
-//               memory
+//               memory; the same thread asks for the packed weight tiles of a later pair to be
+//               brought into L2 (one bulk prefetch per pair)
 //   warp 1      issues tcgen05.mma (A from tensor memory, B from shared memory): eight per
 //               pair behind ONE barrier wait and ONE commit; owns the tensor-memory allocation
 //   warp 3      relay: folds "activations of the pair have landed" into the barrier the MMA
 //               warp waits on, so that warp polls a single barrier
 //   warps 4-19  dequantise: two sets of eight warps alternate pairs (set s owns tensor-memory
 //               slot s); thread = one weight row of one K block. Packed codes come straight
-//               from global memory (a warp's 32 rows are 512 contiguous bytes), one own pair
-//               ahead, addressed by running counters (the tile list is read one item
+//               from global memory (a warp's 32 rows are 512 contiguous bytes) into ONE set of
+//               registers, refilled for the next own pair as soon as the decode has used them
+//               up, through a pointer that walks with the stream (the tile list is read one item
 //               ahead, never on the critical path); each code byte indexes a 256-entry half2
 //               pair table replicated per lane in shared memory (bank-conflict free, the
 //               address is one byte permute); one half2 multiply by the group scale; the
@@ -31,7 +33,10 @@
 // Measured limits that shaped this: a single thread starts a TMA copy only every ~170
 // cycles; a barrier check costs 150-250 cycles under load; an M=128 MMA from tensor memory
 // takes N/2 + 9.5 cycles and the MMA queue holds about four of them; the table lookups are
-// bound by shared-memory wavefronts at ~25 code bytes per cycle per SM.
+// bound by shared-memory wavefronts at ~25 code bytes per cycle per SM; and every instruction
+// in the per-pair loops of the dequantising and MMA warps costs measurable time (a warp there
+// issues only every 5-6 cycles), so these loops carry counters instead of divisions and no
+// debugging code unless it is compiled in.
 // Every wait on an mbarrier is bounded; when one gives up the CTA records a status
 // word, stops issuing work, and leaves after releasing its tensor memory.
 #include "tc.h"
