@@ -265,6 +265,7 @@ def main():
                     help="expert tensors: hgn q4cp (the benchmark workload) or GGUF Q4_K gate/up + Q5_1 down "
                          "(the GGUF variant; with --tokens 8192 --no-decode --no-cpu, single GPU)")
     ap.add_argument("--chunks", type=int, default=2, help="N>1: token chunks whose exchanges overlap the GEMMs")
+    ap.add_argument("--chunk-weights", default="", help="N>1: relative chunk sizes, e.g. 1,3,3,1 (overrides --chunks)")
     ap.add_argument("--sm-margin", type=int, default=32, help="N>1: SMs left free for the NCCL kernels")
     ap.add_argument("--transport", default="p2p", choices=["nccl", "p2p"],
                     help="N>1: exchanges by NCCL all-to-all or by peer copies (copy engines) through CUDA IPC")
@@ -325,6 +326,7 @@ def main():
         placement = ep.greedy_placement(load, world)
         epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement,
                                    chunks=args.chunks, sm_margin=args.sm_margin, transport=args.transport,
+                                   chunk_weights=[float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else None,
                                    split_local=args.ep_split == 1, own_order=args.own_order)
         epm.load_q4cp(0, gu, dn)
         op = epm.op
@@ -468,7 +470,7 @@ def main():
                    "recv_rows_max_over_mean": float(mx.item() / (rows.item() / world)),
                    "exchange": ("peer copies by the copy engines into symmetric-memory receive buffers, arrival flags + bounded device-side wait"
                                 if args.transport == "p2p" else "NCCL all_to_all_single (dispatch, combine)") + "; NCCL all_gather of expert offsets",
-                   "chunks": args.chunks, "transport": args.transport,
+                   "chunks": args.chunks, "chunk_weights": args.chunk_weights or None, "transport": args.transport,
                    "check_vs_single_gpu": check}
 
     if rank != 0:

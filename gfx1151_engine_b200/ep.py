@@ -93,6 +93,34 @@ def next_seq(seq):
     return seq - (1 << 32) if seq >= (1 << 31) else seq
 
 
+def chunk_sizes(max_tokens, chunks, weights=None):
+    """Tokens per chunk: equal parts (rounded up), or proportional to `weights` with every chunk at
+    least one token and the sizes adding up to max_tokens."""
+    if weights is None:
+        return [(max_tokens + chunks - 1) // chunks] * chunks
+    w = [float(v) for v in weights]
+    if len(w) != chunks or min(w) <= 0:
+        raise ValueError("chunk_weights: one positive weight per chunk")
+    total = sum(w)
+    sizes = [max(1, int(max_tokens * v / total)) for v in w]
+    sizes[w.index(max(w))] += max_tokens - sum(sizes)   # the rounding remainder goes to the largest chunk
+    if min(sizes) <= 0:
+        raise ValueError("chunk_weights: too many chunks for %d tokens" % max_tokens)
+    return sizes
+
+
+def chunk_spans(T, sizes):
+    """[(first, end)] token ranges of a forward of T tokens over chunks of at most `sizes` tokens,
+    in order; chunks that get no token are left out."""
+    span, a = [], 0
+    for n in sizes:
+        if a >= T:
+            break
+        span.append((a, min(T, a + n)))
+        a += n
+    return span
+
+
 class ExpertParallelMoe:
     """The MoE layer sharded by expert over the ranks of a torch.distributed group.
 
@@ -103,7 +131,7 @@ class ExpertParallelMoe:
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
                  cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False,
-                 has_shared=False, own_order="ends"):
+                 has_shared=False, own_order="ends", chunk_weights=None):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
@@ -120,12 +148,18 @@ class ExpertParallelMoe:
         self.own_order = own_order
         self.has_shared = has_shared
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
+        # chunk sizes: equal, or in the proportions of chunk_weights (e.g. (1, 3, 3, 1): what no GEMM
+        # hides is the dispatch of the FIRST chunk and the return of the LAST one, so those two are
+        # best short)
+        if chunk_weights is not None:
+            chunks = len(chunk_weights)
         self.chunks = chunks
-        self.tc = (max_tokens + chunks - 1) // chunks            # tokens per chunk
+        self.chunk_tokens = chunk_sizes(max_tokens, chunks, chunk_weights)
         dev = torch.device("cuda", device)
         self.ops, self.buf = [], []
         for c in range(chunks):
-            op = pkg.MoeOperator(experts, topk, d_model, d_mid, self.tc, device=device, has_shared=has_shared,
+            tc = self.chunk_tokens[c]
+            op = pkg.MoeOperator(experts, topk, d_model, d_mid, tc, device=device, has_shared=has_shared,
                                  ep_rank=rank, ep_size=world,
                                  ep_sm_margin=sm_margin if (chunks > 1 and transport == "nccl") else 0)
             if c == 0:
@@ -133,9 +167,9 @@ class ExpertParallelMoe:
                     op.ep_set_placement(np.ascontiguousarray(placement, dtype=np.int32))
             else:
                 op.share_weights(self.ops[0])
-            pairs = self.tc * topk
+            pairs = tc * topk
             cap = int(cap_factor * pairs)
-            own_rows = pairs + (self.tc if has_shared else 0)   # the shared expert's rows sit behind the routed ones
+            own_rows = pairs + (tc if has_shared else 0)   # the shared expert's rows sit behind the routed ones
             if transport == "p2p":
                 # written by the peers' copy engines: symmetric memory (mapped into every rank)
                 import torch.distributed._symmetric_memory as symm_mem
@@ -194,8 +228,8 @@ class ExpertParallelMoe:
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
         main = torch.cuda.current_stream()
-        C = min(self.chunks, (T + self.tc - 1) // self.tc)
-        span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
+        span = chunk_spans(T, self.chunk_tokens)
+        C = len(span)
         self.seq = next_seq(self.seq)
         seq = self.seq
         seq_t = self.seq_ring[seq & 3]
@@ -296,8 +330,8 @@ class ExpertParallelMoe:
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
         main = torch.cuda.current_stream()
-        C = min(self.chunks, (T + self.tc - 1) // self.tc)
-        span = [(c * self.tc, min(T, (c + 1) * self.tc)) for c in range(C)]
+        span = chunk_spans(T, self.chunk_tokens)
+        C = len(span)
         # 1. routing + gather of every chunk, expert offsets of all ranks
         for c, (a, b) in enumerate(span):
             B = self.buf[c]

@@ -140,3 +140,19 @@ def test_every_rank_sees_every_receive_count():
     assert need.sum() == world * T * k
     for r in range(world):
         assert need[r] == ep.p2p_plan(eo, r, world)[2] == sum(ep.exchange_splits(eo, r, world)[1])
+
+
+def test_chunk_sizes_and_spans():
+    """Unequal chunks: sizes follow the weights, add up to the capacity, and a shorter forward fills
+    the chunks in order."""
+    assert ep.chunk_sizes(16384, 2) == [8192, 8192]
+    assert ep.chunk_sizes(10, 3) == [4, 4, 4]
+    s = ep.chunk_sizes(16384, 4, (1, 3, 3, 1))
+    assert s == [2048, 6144, 6144, 2048] and sum(s) == 16384
+    s = ep.chunk_sizes(1000, 3, (1, 2, 1))
+    assert sum(s) == 1000 and s[1] == max(s) and min(s) >= 1
+    assert ep.chunk_spans(16384, [2048, 6144, 6144, 2048]) == [(0, 2048), (2048, 8192), (8192, 14336), (14336, 16384)]
+    assert ep.chunk_spans(3000, [2048, 6144, 6144, 2048]) == [(0, 2048), (2048, 3000)]
+    assert ep.chunk_spans(5, [4, 4, 4]) == [(0, 4), (4, 5)]
+    with pytest.raises(ValueError):
+        ep.chunk_sizes(100, 2, (1, 0))
