@@ -275,6 +275,9 @@ def main():
                     help="scale of the per-expert Zipf(1.1) log-bias (1.0 = benchmark workload; 0.5 / 0 = sensitivity runs)")
     ap.add_argument("--ep-split", type=int, default=1,
                     help="N>1, p2p transport: 1 (default) = the rows a rank keeps are multiplied in place (no copy), apart from the other ranks' rows; 0 = one GEMM pass per chunk over copied rows")
+    ap.add_argument("--ep-merge", type=int, default=-1,
+                    help="N>1: 1 = the other ranks' rows are merged by expert before their GEMMs (one run per expert instead of "
+                         "one per source rank and expert), 0 = not, -1 (default) = from 4 GPUs on")
     ap.add_argument("--own-order", default="ends", choices=["first", "ends"],
                     help="N>1, --ep-split 1: the in-place own-rows passes all up front, or the last chunk's at the very end")
     ap.add_argument("--check", type=int, default=1,
@@ -331,7 +334,8 @@ def main():
         epm = ep.ExpertParallelMoe(E, K_TOP, D, MID, T, rank, world, local, cap_factor=2.0, placement=placement,
                                    chunks=args.chunks, sm_margin=args.sm_margin, transport=args.transport,
                                    chunk_weights=[float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else None,
-                                   split_local=args.ep_split == 1, own_order=args.own_order)
+                                   split_local=args.ep_split == 1, own_order=args.own_order,
+                                   merge_sources=None if args.ep_merge < 0 else bool(args.ep_merge))
         epm.load_q4cp(0, gu, dn)
         op = epm.op
     else:

@@ -73,6 +73,12 @@ struct b200moe_ctx {
   int ep_max_tiles = 0;
   TcPlan* tc_ep = nullptr;
   TcPlan* tc_own = nullptr;        // own-rows pass in place: activations from x_send, results into pairs_back
+  // part 4 (the other ranks' rows merged by expert): expert-major copy of the received rows, the
+  // place of every merged row in the receive buffer, the segment table; allocated by the first such call's attach
+  __half* ep_x_merged = nullptr;
+  int32_t *ep_rowmap = nullptr, *ep_segs = nullptr;
+  TcPlan* tc_merge = nullptr;
+  int sms = 148;
   int64_t launches = 0;
   // stage timer: ring of event sets, one set (7 events) per forward call
   bool prof = false;
@@ -344,6 +350,10 @@ int b200moe_destroy(b200moe_handle h) {
   if (h->ep_counts) cudaFree(h->ep_counts);
   if (h->tc_ep) tc_destroy(h->tc_ep);
   if (h->tc_own) tc_destroy(h->tc_own);
+  if (h->tc_merge) tc_destroy(h->tc_merge);
+  if (h->ep_x_merged) cudaFree(h->ep_x_merged);
+  if (h->ep_rowmap) cudaFree(h->ep_rowmap);
+  if (h->ep_segs) cudaFree(h->ep_segs);
   for (auto& e : h->prof_ev) cudaEventDestroy(e);
   if (h->s_in) cudaStreamDestroy(h->s_in);
   if (h->s_out) cudaStreamDestroy(h->s_out);
@@ -1137,6 +1147,10 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   if (h->ep_tiles) cudaFree(h->ep_tiles), h->ep_tiles = nullptr;
   if (h->tc_ep) tc_destroy(h->tc_ep), h->tc_ep = nullptr;
   if (h->tc_own) tc_destroy(h->tc_own), h->tc_own = nullptr;
+  if (h->tc_merge) tc_destroy(h->tc_merge), h->tc_merge = nullptr;
+  if (h->ep_x_merged) cudaFree(h->ep_x_merged), h->ep_x_merged = nullptr;
+  if (h->ep_rowmap) cudaFree(h->ep_rowmap), h->ep_rowmap = nullptr;
+  if (h->ep_segs) cudaFree(h->ep_segs), h->ep_segs = nullptr;
   // the hidden rows of the received rows (indexed like x_recv) and of the own-rows pass in place
   // (indexed like x_send, the shared expert's rows behind the routed ones)
   const long long hid_rows = std::max<long long>(cap_rows, h->max_rows);
@@ -1147,6 +1161,17 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   CU_TRY(h, tc_create(&h->tc_own, h->ep_x_send, h->ep_hid, h->max_rows, h->cfg.d_model, h->cfg.d_mid));
   tc_set_sm_margin(h->tc_ep, h->cfg.ep_sm_margin);
   tc_set_sm_margin(h->tc_own, h->cfg.ep_sm_margin);
+  // part 4: expert-major copy of the received rows (same capacity), row map, segment table
+  CU_TRY(h, cudaMalloc((void**)&h->ep_x_merged, (size_t)cap_rows * h->cfg.d_model * 2 + 256));
+  CU_TRY(h, cudaMalloc((void**)&h->ep_rowmap, (size_t)cap_rows * sizeof(int32_t) + 256));
+  CU_TRY(h, cudaMalloc((void**)&h->ep_segs, (size_t)kMaxExperts * 3 * sizeof(int32_t)));
+  CU_TRY(h, tc_create(&h->tc_merge, h->ep_x_merged, h->ep_hid, cap_rows, h->cfg.d_model, h->cfg.d_mid));
+  tc_set_sm_margin(h->tc_merge, h->cfg.ep_sm_margin);
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&h->sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || h->sms < 1) h->sms = 148;
+  }
   return B200MOE_OK;
 }
 
@@ -1191,7 +1216,7 @@ int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev,
 
 int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream) {
   if (int s = check_layer(h, layer)) return s;
-  if (!eoff_all_dev || !h->tc_ep || part < 0 || part > 3)
+  if (!eoff_all_dev || !h->tc_ep || part < 0 || part > 4)
     return fail(h, B200MOE_ERR_BAD_ARG, "ep_experts: bad argument or buffers not attached");
   LayerWeights& L = h->layers[layer];
   const b200moe_config& c = h->cfg;
@@ -1200,7 +1225,20 @@ int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all
   cudaStream_t st = (cudaStream_t)stream;
   const int El = local_experts(c);
   CU_TRY(h, launch_ep_tiles(eoff_all_dev, c.ep_size, c.experts, first_expert(c), El, h->tile_cap, h->ep_tiles,
-                            h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part));
+                            h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part, h->ep_segs));
+  if (part == 4) {
+    // the other ranks' rows, merged by expert: an expert-major copy of the received rows (one
+    // memory pass), tiles over that copy -- one run per expert instead of one per (source rank,
+    // expert), i.e. far fewer ragged tiles -- and the down GEMM writes every result row back to
+    // its place in the source-major result buffer, so that the return needs no second pass
+    CU_TRY(h, launch_ep_merge_rows(h->ep_x_recv, h->ep_segs, c.ep_size * El, h->ep_counts + 1, c.d_model, h->ep_x_merged,
+                                   h->ep_rowmap, h->sms, st));
+    CU_TRY(h, launch_up_tc(h->tc_merge, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
+    CU_TRY(h, launch_down_tc(h->tc_merge, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv, h->status_dev, st,
+                             h->ep_rowmap));
+    h->launches += 4;
+    return B200MOE_OK;
+  }
   if (part == 3) {
     // own rows in place: activations straight from the send buffer, results straight into the
     // result buffer (same row order) -- no copy in either direction; the shared expert, which
@@ -1216,7 +1254,7 @@ int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all
     return B200MOE_OK;
   }
   if (shared && part != 2)
-    return fail(h, B200MOE_ERR_UNSUPPORTED, "ep_experts: with a shared expert the own rows must run in place (part 3 + part 2)");
+    return fail(h, B200MOE_ERR_UNSUPPORTED, "ep_experts: with a shared expert the own rows must run in place (part 3 + part 2 or 4)");
   CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
   CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv,
                            h->status_dev, st));

@@ -372,9 +372,16 @@ __global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, 
 // s's expert offset table (E+1 entries). One thread per (source, local expert) segment:
 // its position in the buffer, then tiles of at most tile_cap rows (full tiles first, ragged
 // ones by descending size), exactly as the single-GPU tile list is built.
+//
+// part 4 (the other ranks' rows MERGED by expert): the receive buffer is source-major, so an expert
+// that got rows from seven ranks has seven segments there and up to seven ragged tiles. The
+// segments are listed in segs[] with their place in an expert-major copy of the rows -- {first row
+// in the receive buffer, first row in the merged copy, rows} for every (source, expert), zero rows
+// for this rank's own -- and the tile list is built over the merged copy: one run per expert.
 __global__ void __launch_bounds__(kMaxExperts)
 k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, int tile_cap, int own, int part,
-           Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ total_rows) {
+           Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ total_rows,
+           int32_t* __restrict__ segs) {
   __shared__ int s_a[kMaxExperts], s_c[kMaxExperts];
   const int tid = threadIdx.x;
   const int src = tid / El, e = tid % El;
@@ -388,10 +395,37 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
       const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
       first += e2[e0 + El] - e2[e0];
     }
-    // part 1: only the rows this rank sent to itself; part 2: only the other ranks' rows;
+    // part 1: only the rows this rank sent to itself; part 2 and 4: only the other ranks' rows;
     // part 3: this rank's own rows where they lie in its SEND buffer (row = its own expert offset)
-    if ((part == 1 && src != own) || (part == 2 && src == own) || (part == 3 && src != own)) cnt = 0;
+    if ((part == 1 && src != own) || ((part == 2 || part == 4) && src == own) || (part == 3 && src != own)) cnt = 0;
     if (part == 3) first = eo[e0 + e];
+  }
+  if (part == 4) {
+    // rows of expert e before this source's, rows of expert e in all, rows of the experts before e
+    s_c[tid] = cnt;
+    __syncthreads();
+    int before = 0, tot = 0;
+    if (live)
+      for (int s2 = 0; s2 < G; s2++) {
+        const int c2 = s_c[s2 * El + e];
+        tot += c2;
+        before += s2 < src ? c2 : 0;
+      }
+    __syncthreads();
+    if (tid < El) s_a[tid] = tot;
+    __syncthreads();
+    int base = 0;
+    if (live)
+      for (int e2 = 0; e2 < e; e2++) base += s_a[e2];
+    if (live) {
+      segs[3 * tid] = first;
+      segs[3 * tid + 1] = base + before;
+      segs[3 * tid + 2] = cnt;
+    }
+    __syncthreads();
+    // from here on the thread of source 0 stands for the expert's merged run
+    cnt = live && src == 0 ? tot : 0;
+    first = base;
   }
   const int nfull = cnt / tile_cap, rag = cnt % tile_cap;
   s_c[tid] = nfull;
@@ -431,8 +465,51 @@ cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E
 }
 
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
-                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st, int own, int part) {
-  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, own, part, tiles, n_tiles, total_rows);
+                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st, int own, int part,
+                            int32_t* segs) {
+  if (part == 4 && !segs) return cudaErrorInvalidValue;
+  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, own, part, tiles, n_tiles, total_rows, segs);
+  return cudaGetLastError();
+}
+
+// Expert-major copy of the received rows (part 4 of the expert-parallel GEMM pass): one warp per
+// row of the source-major receive buffer; the row's segment is found by bisection in segs[] (sorted
+// by their first row), rows of this rank's own source -- a hole in the receive buffer -- and rows
+// behind the last segment are skipped. rowmap[merged row] = row in the receive buffer: the down
+// GEMM writes its results there, so that they leave in the senders' order without another pass.
+__global__ void __launch_bounds__(256)
+k_ep_merge_rows(const uint4* __restrict__ x_recv, const int32_t* __restrict__ segs, int n_seg,
+                const int32_t* __restrict__ total_rows, int per_row, uint4* __restrict__ x_merged,
+                int32_t* __restrict__ rowmap) {
+  __shared__ int s_first[kMaxExperts], s_dst[kMaxExperts], s_cnt[kMaxExperts];
+  for (int i = threadIdx.x; i < n_seg; i += blockDim.x) {
+    s_first[i] = segs[3 * i];
+    s_dst[i] = segs[3 * i + 1];
+    s_cnt[i] = segs[3 * i + 2];
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int rows = *total_rows;
+  const int n_warps = gridDim.x * (blockDim.x >> 5);
+  for (int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); j < rows; j += n_warps) {
+    int lo = 0, hi = n_seg - 1;
+    while (lo < hi) {   // last segment whose first row is <= j (empty segments share a first row: the last of them holds the rows)
+      const int m = (lo + hi + 1) >> 1;
+      if (s_first[m] <= j) lo = m; else hi = m - 1;
+    }
+    const int off = j - s_first[lo];
+    if (off >= s_cnt[lo]) continue;
+    const int dst = s_dst[lo] + off;
+    const uint4* src = x_recv + (size_t)j * per_row;
+    uint4* out = x_merged + (size_t)dst * per_row;
+    for (int v = lane; v < per_row; v += 32) out[v] = src[v];
+    if (lane == 0) rowmap[dst] = j;
+  }
+}
+
+cudaError_t launch_ep_merge_rows(const __half* x_recv, const int32_t* segs, int n_seg, const int32_t* total_rows, int d,
+                                 __half* x_merged, int32_t* rowmap, int sms, cudaStream_t st) {
+  k_ep_merge_rows<<<sms * 8, 256, 0, st>>>((const uint4*)x_recv, segs, n_seg, total_rows, d / 8, (uint4*)x_merged, rowmap);
   return cudaGetLastError();
 }
 

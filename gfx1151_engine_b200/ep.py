@@ -131,7 +131,7 @@ class ExpertParallelMoe:
 
     def __init__(self, experts, topk, d_model, d_mid, max_tokens, rank, world, device,
                  cap_factor=2.0, placement=None, group=None, chunks=1, sm_margin=16, transport="nccl", split_local=False,
-                 has_shared=False, own_order="ends", chunk_weights=None):
+                 has_shared=False, own_order="ends", chunk_weights=None, merge_sources=None):
         import torch
         import gfx1151_engine_b200 as pkg
         self.torch, self.group = torch, group
@@ -146,6 +146,9 @@ class ExpertParallelMoe:
         # the first rows travel; "ends" = first chunk's up front, last chunk's at the very end, while
         # the last results travel back
         self.own_order = own_order
+        # the other ranks' rows merged by expert before their GEMMs (b200moe_ep_experts_part part 4): one
+        # extra memory pass per chunk against far fewer ragged tiles; pays from about four ranks on
+        self.merge_sources = (world >= 4) if merge_sources is None else bool(merge_sources)
         self.has_shared = has_shared
         self.E, self.k, self.d, self.rank, self.world = experts, topk, d_model, rank, world
         # chunk sizes: equal, or in the proportions of chunk_weights (e.g. (1, 3, 3, 1): what no GEMM
@@ -298,7 +301,8 @@ class ExpertParallelMoe:
         for c in range(C):
             B = self.buf[c]
             self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
-            self.ops[c].ep_experts(layer, B["eoff_all"], stream=main, part=2 if in_place else 0)
+            self.ops[c].ep_experts(layer, B["eoff_all"], stream=main,
+                                   part=(4 if self.merge_sources else 2) if in_place else 0)
             send_back(c)
         if in_place and self.own_order != "first" and C > 1:
             self.ops[C - 1].ep_experts(layer, self.buf[C - 1]["eoff_all"], stream=main, part=3)

@@ -19,7 +19,7 @@ def bits(a):
     return np.ascontiguousarray(a, np.float32).view(np.uint32)
 
 
-def run_ranks(torch, spec, layer, xs, lgs, world, split, placement=None):
+def run_ranks(torch, spec, layer, xs, lgs, world, split, placement=None, merged=False):
     T = xs[0].shape[0]
     pairs = T * spec.topk
     own_rows = pairs + (T if spec.shared else 0)
@@ -55,7 +55,7 @@ def run_ranks(torch, spec, layer, xs, lgs, world, split, placement=None):
     for r in range(world):                      # experts
         if split:
             ops[r].ep_experts(0, eoff_all, part=3)
-            ops[r].ep_experts(0, eoff_all, part=2)
+            ops[r].ep_experts(0, eoff_all, part=4 if merged else 2)
         else:
             ops[r].ep_experts(0, eoff_all)
     torch.cuda.synchronize()
@@ -111,6 +111,10 @@ def test_ep_phases_match_single_gpu(cuda, world, placed):
     halves, _ = run_ranks(torch, spec, layer, xs, lgs, world, split=True, placement=placement)
     for r in range(world):
         assert np.array_equal(bits(halves[r]), bits(plain[r]))
+    # the other ranks' rows merged by expert before their GEMMs (part 4): other tiles, same rows, same bytes
+    merged, _ = run_ranks(torch, spec, layer, xs, lgs, world, split=True, placement=placement, merged=True)
+    for r in range(world):
+        assert np.array_equal(bits(merged[r]), bits(plain[r]))
 
 
 @pytest.mark.parametrize("world", [2, 4])
@@ -128,6 +132,9 @@ def test_ep_with_shared_expert(cuda, world):
         assert np.isfinite(got[r]).all()
         max_abs, mean_rel = output_errors(got[r], want[r])
         assert max_abs <= 4e-3 and mean_rel <= 1e-5, (r, max_abs, mean_rel)
+    merged, _ = run_ranks(torch, spec, layer, xs, lgs, world, split=True, placement=placement, merged=True)
+    for r in range(world):
+        assert np.array_equal(bits(merged[r]), bits(got[r]))
     # without the in-place pass the library refuses the combination instead of dropping the expert
     op = pkg.MoeOperator(spec.experts, spec.topk, spec.d, spec.mid, T, has_shared=True, ep_rank=0, ep_size=world)
     op.load_q4cp(0, dev_bytes(torch, layer["gate_up"]), dev_bytes(torch, layer["down"]))
