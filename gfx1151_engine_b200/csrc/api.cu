@@ -73,11 +73,9 @@ struct b200moe_ctx {
   int ep_max_tiles = 0;
   TcPlan* tc_ep = nullptr;
   TcPlan* tc_own = nullptr;        // own-rows pass in place: activations from x_send, results into pairs_back
-  // part 4 (the other ranks' rows merged by expert): expert-major copy of the received rows, the
-  // place of every merged row in the receive buffer, the segment table; allocated by the first such call's attach
-  __half* ep_x_merged = nullptr;
+  // part 4 (the other ranks' rows with the tails of their segments merged by expert): the place of
+  // every merged row in the source-major layout, the table of the tails
   int32_t *ep_rowmap = nullptr, *ep_segs = nullptr;
-  TcPlan* tc_merge = nullptr;
   int sms = 148;
   int64_t launches = 0;
   // stage timer: ring of event sets, one set (7 events) per forward call
@@ -350,8 +348,6 @@ int b200moe_destroy(b200moe_handle h) {
   if (h->ep_counts) cudaFree(h->ep_counts);
   if (h->tc_ep) tc_destroy(h->tc_ep);
   if (h->tc_own) tc_destroy(h->tc_own);
-  if (h->tc_merge) tc_destroy(h->tc_merge);
-  if (h->ep_x_merged) cudaFree(h->ep_x_merged);
   if (h->ep_rowmap) cudaFree(h->ep_rowmap);
   if (h->ep_segs) cudaFree(h->ep_segs);
   for (auto& e : h->prof_ev) cudaEventDestroy(e);
@@ -1147,8 +1143,6 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   if (h->ep_tiles) cudaFree(h->ep_tiles), h->ep_tiles = nullptr;
   if (h->tc_ep) tc_destroy(h->tc_ep), h->tc_ep = nullptr;
   if (h->tc_own) tc_destroy(h->tc_own), h->tc_own = nullptr;
-  if (h->tc_merge) tc_destroy(h->tc_merge), h->tc_merge = nullptr;
-  if (h->ep_x_merged) cudaFree(h->ep_x_merged), h->ep_x_merged = nullptr;
   if (h->ep_rowmap) cudaFree(h->ep_rowmap), h->ep_rowmap = nullptr;
   if (h->ep_segs) cudaFree(h->ep_segs), h->ep_segs = nullptr;
   // the hidden rows of the received rows (indexed like x_recv) and of the own-rows pass in place
@@ -1161,12 +1155,10 @@ int b200moe_ep_attach(b200moe_handle h, void* x_send, void* x_recv, void* pairs_
   CU_TRY(h, tc_create(&h->tc_own, h->ep_x_send, h->ep_hid, h->max_rows, h->cfg.d_model, h->cfg.d_mid));
   tc_set_sm_margin(h->tc_ep, h->cfg.ep_sm_margin);
   tc_set_sm_margin(h->tc_own, h->cfg.ep_sm_margin);
-  // part 4: expert-major copy of the received rows (same capacity), row map, segment table
-  CU_TRY(h, cudaMalloc((void**)&h->ep_x_merged, (size_t)cap_rows * h->cfg.d_model * 2 + 256));
-  CU_TRY(h, cudaMalloc((void**)&h->ep_rowmap, (size_t)cap_rows * sizeof(int32_t) + 256));
+  // part 4: row map of the merged area (at most one tail per source and expert), table of the tails
+  CU_TRY(h, cudaMalloc((void**)&h->ep_rowmap, (size_t)kMaxExperts * h->tile_cap * sizeof(int32_t) + 256));
   CU_TRY(h, cudaMalloc((void**)&h->ep_segs, (size_t)kMaxExperts * 3 * sizeof(int32_t)));
-  CU_TRY(h, tc_create(&h->tc_merge, h->ep_x_merged, h->ep_hid, cap_rows, h->cfg.d_model, h->cfg.d_mid));
-  tc_set_sm_margin(h->tc_merge, h->cfg.ep_sm_margin);
+  CU_TRY(h, cudaMemset(h->ep_segs, 0, (size_t)kMaxExperts * 3 * sizeof(int32_t)));
   {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1225,17 +1217,19 @@ int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all
   cudaStream_t st = (cudaStream_t)stream;
   const int El = local_experts(c);
   CU_TRY(h, launch_ep_tiles(eoff_all_dev, c.ep_size, c.experts, first_expert(c), El, h->tile_cap, h->ep_tiles,
-                            h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part, h->ep_segs));
+                            h->ep_counts, h->ep_counts + 1, st, c.ep_rank, part, h->ep_segs, (int)h->ep_cap_rows));
   if (part == 4) {
-    // the other ranks' rows, merged by expert: an expert-major copy of the received rows (one
-    // memory pass), tiles over that copy -- one run per expert instead of one per (source rank,
-    // expert), i.e. far fewer ragged tiles -- and the down GEMM writes every result row back to
-    // its place in the source-major result buffer, so that the return needs no second pass
-    CU_TRY(h, launch_ep_merge_rows(h->ep_x_recv, h->ep_segs, c.ep_size * El, h->ep_counts + 1, c.d_model, h->ep_x_merged,
-                                   h->ep_rowmap, h->sms, st));
-    CU_TRY(h, launch_up_tc(h->tc_merge, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
-    CU_TRY(h, launch_down_tc(h->tc_merge, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv, h->status_dev, st,
-                             h->ep_rowmap));
+    // the other ranks' rows with the tails of their (source, expert) segments merged by expert:
+    // full tiles are multiplied where they were received; the rows behind a segment's last full
+    // tile are copied behind the received rows, expert after expert (a small memory pass: at most
+    // one tile's worth of rows per segment), and tiled there -- one ragged tile per expert instead
+    // of one per source and expert --; the down GEMM writes their results back to their places in
+    // the source-major result buffer, so that the return needs no pass of its own
+    CU_TRY(h, launch_ep_merge_tails(h->ep_x_recv, h->ep_segs, c.ep_size * El, h->ep_counts + 1, c.d_model, h->ep_rowmap,
+                                    h->sms, st));
+    CU_TRY(h, launch_up_tc(h->tc_ep, L.gu, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_hid, h->status_dev, st));
+    CU_TRY(h, launch_down_tc(h->tc_ep, L.dn, h->ep_tiles, h->ep_counts, h->ep_max_tiles, h->ep_pairs_recv, h->status_dev, st,
+                             h->ep_rowmap, h->ep_counts + 1));
     h->launches += 4;
     return B200MOE_OK;
   }

@@ -261,7 +261,8 @@ struct KParams {
   int32_t* status;
   long long* trace;  // null, or [8 roles][kTraceSlots][4] clock samples written by CTA 0
   int l2_ahead;      // weight tiles are asked into L2 this many own pairs ahead of their register fetch (0: off)
-  const int32_t* rowmap;  // down kernel, may be null: output row of tile-list row r (else r itself)
+  const int32_t* rowmap;    // down kernel, may be null: tile-list row r >= map_base[0] is written to output row
+  const int32_t* map_base;  // rowmap[r - map_base[0]] (rows below map_base[0], and all rows without a map: to row r)
 };
 constexpr int kTraceSlots = 512;
 // Timeline stamps of CTA 0 (a debugging aid: build with -DB200MOE_TRACE and set
@@ -684,6 +685,8 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
       // Results leave through a shared-memory tile [column = row of the expert][weight row]
       // so that every global store is a full 16-byte piece of one output row.
       const int e128 = quarter * 32 + lane;
+      // (down kernel) rows from map_base on are written where the row map says
+      const int map_base = !UP && p.rowmap != nullptr ? p.map_base[0] : 0x7fffffff;
       for (int c0 = 0; c0 < t.count; c0 += 32) {
         uint32_t v[32];
         tc_ld32(src + c0, v);
@@ -744,7 +747,7 @@ k_expert_tc(const __grid_constant__ CUtensorMap map16, const __grid_constant__ C
             const int piece = e128 + 128 * k, col = piece >> 4, seg = piece & 15;
             if (c0 + col < t.count) {
               const int row = t.first + c0 + col;
-              const size_t orow = p.rowmap ? (size_t)p.rowmap[row] : (size_t)row;
+              const size_t orow = row >= map_base ? (size_t)p.rowmap[row - map_base] : (size_t)row;
               *(uint4*)(p.out + orow * p.out_ld + mt * 128 + seg * 8) = *(const uint4*)(outs + col * 128 + seg * 8);
             }
           }
@@ -788,7 +791,7 @@ cudaError_t encode_2d(PFN_cuTensorMapEncodeTiled_v12000 enc, CUtensorMap* map, c
 template <bool UP, bool DUAL, int FMT>
 cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
                    const Tile* tiles, const int32_t* n_tiles, int max_tiles, __half* out, int out_ld,
-                   int32_t* status, cudaStream_t st, const int32_t* rowmap = nullptr) {
+                   int32_t* status, cudaStream_t st, const int32_t* rowmap = nullptr, const int32_t* map_base = nullptr) {
   constexpr int kSmemBytes = Map::kSmemBytes;
   static bool attr_set = false;  // one flag per template instance
   if (!attr_set) {
@@ -799,7 +802,7 @@ cudaError_t launch(TcPlan* plan, const CUtensorMap* m, const Image& img,
   }
   static const int l2_ahead = getenv("B200MOE_TC_L2_AHEAD") ? atoi(getenv("B200MOE_TC_L2_AHEAD")) : 3;
   KParams p{img, tiles, n_tiles, out, out_ld, status, (UP != (getenv("B200MOE_TC_TRACE_DOWN") != nullptr)) ? plan->trace : nullptr,
-            l2_ahead, rowmap};
+            l2_ahead, rowmap, map_base};
   long long max_items = (long long)max_tiles * img.n_mtiles;
   const int usable = plan->sms - plan->margin > 1 ? plan->sms - plan->margin : 1;
   int grid = (int)(max_items < usable ? max_items : usable);
@@ -875,13 +878,15 @@ cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, cons
 }
 
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
-                           int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st, const int32_t* rowmap) {
+                           int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st, const int32_t* rowmap,
+                           const int32_t* map_base) {
+  if ((rowmap == nullptr) != (map_base == nullptr)) return cudaErrorInvalidValue;
   if (img.fmt == kQ51)
     return launch<false, false, kQ51>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16, img.n_mtiles * 128, status, st,
-                                      rowmap);
+                                      rowmap, map_base);
   if (img.fmt != kQ4CP) return cudaErrorNotSupported;
   return launch<false, false, kQ4CP>(plan, plan->h, img, tiles, n_tiles, max_tiles, pairs16,
-                       img.n_mtiles * 128, status, st, rowmap);
+                       img.n_mtiles * 128, status, st, rowmap, map_base);
 }
 
 cudaError_t launch_raw_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,

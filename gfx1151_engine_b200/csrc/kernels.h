@@ -91,12 +91,14 @@ cudaError_t launch_shared_gate(const void* x_bf16, const uint16_t* gate_w_bf16, 
 
 cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E, const int32_t* place,
                                    cudaStream_t st);
-cudaError_t launch_ep_merge_rows(const __half* x_recv, const int32_t* segs, int n_seg, const int32_t* total_rows, int d,
-                                 __half* x_merged, int32_t* rowmap, int sms, cudaStream_t st);
+cudaError_t launch_ep_merge_tails(__half* x_recv, const int32_t* segs, int n_seg, const int32_t* counts, int d,
+                                  int32_t* rowmap, int sms, cudaStream_t st);
+// counts (device): [0] = rows of the source-major layout, [1] = rows of part 4's merged area behind them
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
-                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st,
+                            Tile* tiles, int32_t* n_tiles, int32_t* counts, cudaStream_t st,
                             int own_rank = 0, int part = 0,   // part 1: rows from own_rank only, 2: all others, 3: own rows at their place in the send buffer,
-                            int32_t* segs = nullptr);         // 4: all others merged by expert (segs: [G * El][3] = {row in the receive buffer, row in the merged copy, rows})
+                            int32_t* segs = nullptr,          // 4: all others, the tails of their segments merged by expert (segs: [G * El][3])
+                            int cap_rows = 0);                //    behind the received rows, as far as the buffer (cap_rows) has room
 
 // ---- expert_simt.cu ----
 cudaError_t launch_up_simt(const Image& img, const void* x_bf16, int d, int mid,

@@ -373,15 +373,18 @@ __global__ void k_apply_placement(int32_t* __restrict__ ids, int stride, int T, 
 // its position in the buffer, then tiles of at most tile_cap rows (full tiles first, ragged
 // ones by descending size), exactly as the single-GPU tile list is built.
 //
-// part 4 (the other ranks' rows MERGED by expert): the receive buffer is source-major, so an expert
-// that got rows from seven ranks has seven segments there and up to seven ragged tiles. The
-// segments are listed in segs[] with their place in an expert-major copy of the rows -- {first row
-// in the receive buffer, first row in the merged copy, rows} for every (source, expert), zero rows
-// for this rank's own -- and the tile list is built over the merged copy: one run per expert.
+// part 4 (the other ranks' rows with their TAILS MERGED by expert): the receive buffer is
+// source-major, so an expert that got rows from seven ranks has seven segments there and up to
+// seven ragged tiles. Full tiles of a segment stay where they are; the rows behind a segment's
+// last full tile (its tail) are copied behind the received rows, expert after expert, and tiled
+// there: one ragged tile per expert instead of one per (source, expert). segs[] lists the tails in
+// the order of their destination, {first row in the receive buffer, first row in the merged area,
+// rows}; counts[1] = received rows R (the merged area starts there), counts[2] = merged rows (0
+// when the buffer has no room for them behind R: the list is then part 2's).
 __global__ void __launch_bounds__(kMaxExperts)
 k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, int tile_cap, int own, int part,
-           Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ total_rows,
-           int32_t* __restrict__ segs) {
+           Tile* __restrict__ tiles, int32_t* __restrict__ n_tiles, int32_t* __restrict__ counts,
+           int32_t* __restrict__ segs, int cap_rows) {
   __shared__ int s_a[kMaxExperts], s_c[kMaxExperts];
   const int tid = threadIdx.x;
   const int src = tid / El, e = tid % El;
@@ -400,34 +403,53 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
     if ((part == 1 && src != own) || ((part == 2 || part == 4) && src == own) || (part == 3 && src != own)) cnt = 0;
     if (part == 3) first = eo[e0 + e];
   }
+  int R = 0;  // rows of the source-major layout
+  for (int s2 = 0; s2 < G; s2++) {
+    const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
+    R += e2[e0 + El] - e2[e0];
+  }
+  // tiles of this thread: nf_a full tiles from first, nf_b full tiles from first_b, one ragged tile
+  int nf_a = cnt / tile_cap, nf_b = 0, first_b = 0, rag = cnt % tile_cap, rag_first = first + nf_a * tile_cap;
+  int merged_rows = 0;
   if (part == 4) {
-    // rows of expert e before this source's, rows of expert e in all, rows of the experts before e
-    s_c[tid] = cnt;
+    const int tail = rag;
+    s_c[tid] = tail;
     __syncthreads();
-    int before = 0, tot = 0;
+    int before = 0, ttot = 0;  // tail rows of expert e from the sources before this one, from all
     if (live)
       for (int s2 = 0; s2 < G; s2++) {
         const int c2 = s_c[s2 * El + e];
-        tot += c2;
+        ttot += c2;
         before += s2 < src ? c2 : 0;
       }
     __syncthreads();
-    if (tid < El) s_a[tid] = tot;
+    if (tid < El) s_a[tid] = ttot;
     __syncthreads();
-    int base = 0;
-    if (live)
-      for (int e2 = 0; e2 < e; e2++) base += s_a[e2];
-    if (live) {
-      segs[3 * tid] = first;
-      segs[3 * tid + 1] = base + before;
-      segs[3 * tid + 2] = cnt;
+    int tbase = 0, all_tails = 0;  // tail rows of the experts before e, of all experts
+    for (int e2 = 0; e2 < El; e2++) {
+      all_tails += s_a[e2];
+      tbase += e2 < e ? s_a[e2] : 0;
     }
     __syncthreads();
-    // from here on the thread of source 0 stands for the expert's merged run
-    cnt = live && src == 0 ? tot : 0;
-    first = base;
+    if (R + all_tails <= cap_rows) {
+      merged_rows = all_tails;
+      if (live) {
+        int32_t* sg = segs + 3 * (e * G + src);   // destination order: expert-major
+        sg[0] = rag_first;
+        sg[1] = R + tbase + before;
+        sg[2] = tail;
+      }
+      // the tail leaves this thread; the thread of source 0 tiles the expert's merged tails
+      rag = 0;
+      if (live && src == 0) {
+        nf_b = ttot / tile_cap;
+        first_b = R + tbase;
+        rag = ttot % tile_cap;
+        rag_first = first_b + nf_b * tile_cap;
+      }
+    }
   }
-  const int nfull = cnt / tile_cap, rag = cnt % tile_cap;
+  const int nfull = nf_a + nf_b;
   s_c[tid] = nfull;
   __syncthreads();
   for (int o = 1; o < kMaxExperts; o <<= 1) {
@@ -437,7 +459,8 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
     __syncthreads();
   }
   const int total_full = s_c[kMaxExperts - 1], full0 = s_c[tid] - nfull;
-  for (int j = 0; j < nfull; j++) tiles[full0 + j] = Tile{e, first + j * tile_cap, tile_cap};
+  for (int j = 0; j < nf_a; j++) tiles[full0 + j] = Tile{e, first + j * tile_cap, tile_cap};
+  for (int j = 0; j < nf_b; j++) tiles[full0 + nf_a + j] = Tile{e, first_b + j * tile_cap, tile_cap};
   s_a[tid] = rag;
   __syncthreads();
   int rank = 0, nparts = 0;
@@ -446,15 +469,11 @@ k_ep_tiles(const int32_t* __restrict__ eoff_all, int G, int E, int e0, int El, i
     nparts += pp > 0;
     rank += (pp > rag) || (pp == rag && o < tid);
   }
-  if (rag > 0) tiles[total_full + rank] = Tile{e, first + nfull * tile_cap, rag};
+  if (rag > 0) tiles[total_full + rank] = Tile{e, rag_first, rag};
   if (tid == 0) {
     n_tiles[0] = total_full + nparts;
-    int rows = 0;
-    for (int s2 = 0; s2 < G; s2++) {
-      const int32_t* e2 = eoff_all + (size_t)s2 * (E + 1);
-      rows += e2[e0 + El] - e2[e0];
-    }
-    *total_rows = rows;
+    counts[0] = R;
+    counts[1] = merged_rows;
   }
 }
 
@@ -465,51 +484,48 @@ cudaError_t launch_apply_placement(int32_t* ids, int stride, int T, int k, int E
 }
 
 cudaError_t launch_ep_tiles(const int32_t* eoff_all, int G, int E, int e0, int El, int tile_cap,
-                            Tile* tiles, int32_t* n_tiles, int32_t* total_rows, cudaStream_t st, int own, int part,
-                            int32_t* segs) {
+                            Tile* tiles, int32_t* n_tiles, int32_t* counts, cudaStream_t st, int own, int part,
+                            int32_t* segs, int cap_rows) {
   if (part == 4 && !segs) return cudaErrorInvalidValue;
-  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, own, part, tiles, n_tiles, total_rows, segs);
+  k_ep_tiles<<<1, kMaxExperts, 0, st>>>(eoff_all, G, E, e0, El, tile_cap, own, part, tiles, n_tiles, counts, segs, cap_rows);
   return cudaGetLastError();
 }
 
-// Expert-major copy of the received rows (part 4 of the expert-parallel GEMM pass): one warp per
-// row of the source-major receive buffer; the row's segment is found by bisection in segs[] (sorted
-// by their first row), rows of this rank's own source -- a hole in the receive buffer -- and rows
-// behind the last segment are skipped. rowmap[merged row] = row in the receive buffer: the down
-// GEMM writes its results there, so that they leave in the senders' order without another pass.
+// The tails of part 4 copied into the merged area behind the received rows: one warp per merged
+// row; its segment is found by bisection in segs[] (in destination order; empty segments share
+// their first row with the next one, so the LAST segment starting at or before the row holds it).
+// rowmap[merged row - R] = the row's place in the source-major layout: the down GEMM writes the
+// result there, so that results leave in the senders' order without another pass.
 __global__ void __launch_bounds__(256)
-k_ep_merge_rows(const uint4* __restrict__ x_recv, const int32_t* __restrict__ segs, int n_seg,
-                const int32_t* __restrict__ total_rows, int per_row, uint4* __restrict__ x_merged,
-                int32_t* __restrict__ rowmap) {
-  __shared__ int s_first[kMaxExperts], s_dst[kMaxExperts], s_cnt[kMaxExperts];
+k_ep_merge_tails(uint4* __restrict__ x_recv, const int32_t* __restrict__ segs, int n_seg,
+                 const int32_t* __restrict__ counts, int per_row, int32_t* __restrict__ rowmap) {
+  __shared__ int s_src[kMaxExperts], s_dst[kMaxExperts];
   for (int i = threadIdx.x; i < n_seg; i += blockDim.x) {
-    s_first[i] = segs[3 * i];
+    s_src[i] = segs[3 * i];
     s_dst[i] = segs[3 * i + 1];
-    s_cnt[i] = segs[3 * i + 2];
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int rows = *total_rows;
+  const int R = counts[0], rows = counts[1];
   const int n_warps = gridDim.x * (blockDim.x >> 5);
-  for (int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); j < rows; j += n_warps) {
+  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < rows; i += n_warps) {
+    const int dst = R + i;
     int lo = 0, hi = n_seg - 1;
-    while (lo < hi) {   // last segment whose first row is <= j (empty segments share a first row: the last of them holds the rows)
+    while (lo < hi) {
       const int m = (lo + hi + 1) >> 1;
-      if (s_first[m] <= j) lo = m; else hi = m - 1;
+      if (s_dst[m] <= dst) lo = m; else hi = m - 1;
     }
-    const int off = j - s_first[lo];
-    if (off >= s_cnt[lo]) continue;
-    const int dst = s_dst[lo] + off;
+    const int j = s_src[lo] + (dst - s_dst[lo]);
     const uint4* src = x_recv + (size_t)j * per_row;
-    uint4* out = x_merged + (size_t)dst * per_row;
+    uint4* out = x_recv + (size_t)dst * per_row;
     for (int v = lane; v < per_row; v += 32) out[v] = src[v];
-    if (lane == 0) rowmap[dst] = j;
+    if (lane == 0) rowmap[i] = j;
   }
 }
 
-cudaError_t launch_ep_merge_rows(const __half* x_recv, const int32_t* segs, int n_seg, const int32_t* total_rows, int d,
-                                 __half* x_merged, int32_t* rowmap, int sms, cudaStream_t st) {
-  k_ep_merge_rows<<<sms * 8, 256, 0, st>>>((const uint4*)x_recv, segs, n_seg, total_rows, d / 8, (uint4*)x_merged, rowmap);
+cudaError_t launch_ep_merge_tails(__half* x_recv, const int32_t* segs, int n_seg, const int32_t* counts, int d,
+                                  int32_t* rowmap, int sms, cudaStream_t st) {
+  k_ep_merge_tails<<<sms * 4, 256, 0, st>>>((uint4*)x_recv, segs, n_seg, counts, d / 8, rowmap);
   return cudaGetLastError();
 }
 

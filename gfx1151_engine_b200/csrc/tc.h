@@ -21,11 +21,11 @@ constexpr int kTcTileN = 192;
 cudaError_t launch_up_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                          int max_tiles, __half* hid16, int32_t* status, cudaStream_t st);
 // down GEMM: pairs16[row][d] = W_down hid16[row].
-// rowmap (device, may be null): result row r of the tile list goes to pairs16[rowmap[r]] instead
-// of pairs16[r].
+// rowmap + map_base (device, both or neither): result row r >= map_base[0] of the tile list goes to
+// pairs16[rowmap[r - map_base[0]]] instead of pairs16[r].
 cudaError_t launch_down_tc(TcPlan* plan, const Image& img, const Tile* tiles, const int32_t* n_tiles,
                            int max_tiles, __half* pairs16, int32_t* status, cudaStream_t st,
-                           const int32_t* rowmap = nullptr);
+                           const int32_t* rowmap = nullptr, const int32_t* map_base = nullptr);
 
 // plain GEMM over the expert-sorted activations (no activation function): z16[row][n_mtiles*128] =
 // W x_sorted[row], for images whose rows are not gate/up pairs (hgn v2 i4r gate_up).

@@ -259,12 +259,14 @@ int b200moe_ep_experts(b200moe_handle h, int layer, const int32_t* eoff_all_dev,
  * rows IN PLACE: read from x_send where ep_route left them and written to pairs_back where
  * ep_combine expects them -- neither direction is copied -- together with the shared expert's rows
  * when the layer has one. A forward is then part 3 + part 2; the own segment of x_recv / pairs_recv
- * stays unused. Part 4 = part 2 with the other ranks' rows MERGED BY EXPERT first: x_recv is
+ * stays unused. Part 4 = part 2 with the TAILS of the other ranks' rows merged by expert: x_recv is
  * source-major, so an expert that received rows from seven ranks has seven runs there and up to
- * seven ragged GEMM tiles; part 4 copies the rows into an expert-major buffer of the library's own
- * (one memory pass), multiplies one run per expert, and has the down GEMM write every result row to
- * its source-major place in pairs_recv -- the same bytes as part 2, with far fewer small tiles
- * (at 8 ranks and three chunks: 820 full + 197 ragged tile columns against 755 + 606). */
+ * seven ragged GEMM tiles. Part 4 multiplies the full tiles of every run where they lie, copies
+ * the rows behind each run's last full tile to the free end of x_recv (behind the received rows;
+ * as far as cap_rows leaves room, else it is part 2), expert after expert, tiles them there -- one
+ * ragged tile per expert -- and has the down GEMM write their results to their source-major places
+ * in pairs_recv: the same bytes as part 2 with far fewer small tiles (at 8 ranks and three
+ * chunks: 820 full + 197 ragged tile columns against 755 + 606). */
 int b200moe_ep_experts_part(b200moe_handle h, int layer, const int32_t* eoff_all_dev, int part, void* stream);
 int b200moe_ep_combine(b200moe_handle h, int T, void* out_bf16_dev, void* stream);
 /* For hosts that move the rows with peer copies (copy engines) instead of a collective: every
