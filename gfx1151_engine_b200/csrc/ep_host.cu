@@ -272,8 +272,8 @@ int b200moe_ep_forward(b200moe_handle h, int layer, const void* x_bf16_dev, int 
   const ncclResult_t r_end = g_nccl.GroupEnd();
   if (r != ncclSuccess) return nccl_fail("dispatch", r);
   if (r_end != ncclSuccess) return nccl_fail("ncclGroupEnd", r_end);
-  // 5: the other ranks' rows
-  if (int rc = b200moe_ep_experts_part(h, layer, s->eoff_all, 2, stream)) return rc;
+  // 5: the other ranks' rows (from four ranks on with the tails of their runs merged by expert)
+  if (int rc = b200moe_ep_experts_part(h, layer, s->eoff_all, G >= 4 ? 4 : 2, stream)) return rc;
   // 6: results back to their owners (into the owner's send order)
   if ((r = g_nccl.GroupStart()) != ncclSuccess) return nccl_fail("ncclGroupStart", r);
   for (int p = 0; p < G; p++) {
