@@ -184,7 +184,7 @@ int report_status(b200moe_handle h, cudaStream_t st) {
   if (e == cudaSuccess && code == 5) e = cudaMemsetAsync(h->grid_bar, 0, 16, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return fail(h, B200MOE_ERR_CUDA, std::string("clearing the status word: ") + cudaGetErrorString(e));
-  char buf[160];
+  char buf[256];
   if (code == 4) {
     snprintf(buf, sizeof buf, "expert id %d outside [0, %d) in the caller's top-k ids: the pair was dropped", detail,
              h->cfg.experts);
