@@ -479,6 +479,8 @@ def main():
                    "exchange": ("peer copies by the copy engines into symmetric-memory receive buffers, arrival flags + bounded device-side wait"
                                 if args.transport == "p2p" else "NCCL all_to_all_single (dispatch, combine)") + "; NCCL all_gather of expert offsets",
                    "chunks": args.chunks, "chunk_weights": args.chunk_weights or None, "transport": args.transport,
+                   "own_rows": "in place, own passes at the %s of the chunk pipeline" % ("ends" if args.own_order == "ends" else "front") if args.ep_split == 1 else "copied like the others",
+                   "tails_merged_by_expert": bool(epm.merge_sources),
                    "check_vs_single_gpu": check}
 
     if rank != 0:
