@@ -444,8 +444,30 @@ def main():
     oh = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
+    if epm is not None and args.transport == "p2p":
+        # host copies per chunk on their own streams: chunk c+1 comes in while chunk c is routed and
+        # multiplied, chunk c goes out while chunk c+1 is multiplied
+        from gfx1151_engine_b200 import ep as ep_mod
+        spans = ep_mod.chunk_spans(T, epm.chunk_tokens)
+        ev_in = [torch.cuda.Event() for _ in spans]
+        ev_out = [torch.cuda.Event() for _ in spans]
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
     def e2e_step():
-        if epm is not None:
+        if epm is not None and args.transport == "p2p":
+            s_in.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s_in):
+                for c, (a, b) in enumerate(spans):
+                    logits[a:b].copy_(lh[a:b], non_blocking=True)
+                    x[a:b].copy_(xh[a:b], non_blocking=True)
+                    ev_in[c].record(s_in)
+            epm.forward(0, x, logits, out, in_ready=ev_in, out_done=ev_out)
+            with torch.cuda.stream(s_out):
+                for c, (a, b) in enumerate(spans):
+                    s_out.wait_event(ev_out[c])
+                    oh[a:b].copy_(out[a:b], non_blocking=True)
+            torch.cuda.synchronize()
+        elif epm is not None:
             x.copy_(xh, non_blocking=True)
             logits.copy_(lh, non_blocking=True)
             epm.forward(0, x, logits, out)

@@ -227,7 +227,7 @@ class ExpertParallelMoe:
                     b[dst].append(b[key] if r == self.rank else hdl.get_buffer(r, list(b[key].shape), b[key].dtype))
         dist.barrier(group=self.group)
 
-    def _forward_p2p(self, layer, x, logits, out):
+    def _forward_p2p(self, layer, x, logits, out, in_ready=None, out_done=None):
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
         main = torch.cuda.current_stream()
@@ -241,6 +241,8 @@ class ExpertParallelMoe:
         routed, tables = [], []
         for c, (a, b) in enumerate(span):
             B = self.buf[c]
+            if in_ready is not None:
+                main.wait_event(in_ready[c])     # the chunk's x and logits (a host copy on another stream) are there
             self.ops[c].ep_route(layer, x[a:b], logits[a:b], eoff_out=B["eoff"], stream=main)
             ev = torch.cuda.Event()
             ev.record(main)
@@ -297,20 +299,32 @@ class ExpertParallelMoe:
                         B["peer_back"][s][dst0:dst0 + n].copy_(B["pairs_recv"][src0:src0 + n], non_blocking=True)
                     B["peer_flags"][s][1, self.rank:self.rank + 1].copy_(seq_t, non_blocking=True)
 
-        # 3. experts per chunk once its rows have arrived; results go straight back to their owners
+        def combine(c):
+            a, b = span[c]
+            B = self.buf[c]
+            self.ops[c].ep_wait_flags(B["flags"][1], self.world, seq, stream=main)
+            self.ops[c].ep_combine(out[a:b], b - a, stream=main)
+            if out_done is not None:
+                out_done[c].record(main)
+
+        # 3. experts per chunk once its rows have arrived; results go straight back to their owners.
+        #    With out_done given (a caller that copies each chunk's output away as soon as it is
+        #    there), a chunk is combined right behind the NEXT chunk's GEMMs -- its results came back
+        #    while those ran -- instead of at the very end.
+        early = out_done is not None
         for c in range(C):
             B = self.buf[c]
             self.ops[c].ep_wait_flags(B["flags"][0], self.world, seq, stream=main)
             self.ops[c].ep_experts(layer, B["eoff_all"], stream=main,
                                    part=(4 if self.merge_sources else 2) if in_place else 0)
             send_back(c)
+            if early and c >= 1:
+                combine(c - 1)
         if in_place and self.own_order != "first" and C > 1:
             self.ops[C - 1].ep_experts(layer, self.buf[C - 1]["eoff_all"], stream=main, part=3)
         # 4. combine
-        for c, (a, b) in enumerate(span):
-            B = self.buf[c]
-            self.ops[c].ep_wait_flags(B["flags"][1], self.world, seq, stream=main)
-            self.ops[c].ep_combine(out[a:b], b - a, stream=main)
+        for c in range(C - 1 if early else 0, C):
+            combine(c)
 
     def load_q4cp(self, layer, gate_up, down):
         """Every rank passes the full tensors; the library keeps this rank's experts."""
@@ -328,9 +342,16 @@ class ExpertParallelMoe:
     def launches(self):
         return sum(op.launches for op in self.ops)
 
-    def forward(self, layer, x, logits, out):
+    def forward(self, layer, x, logits, out, in_ready=None, out_done=None):
+        """in_ready / out_done (p2p transport): one CUDA event per chunk (chunk_spans(T, self.chunk_tokens)).
+        The routing of chunk c waits for in_ready[c] -- the caller's copy of that chunk's x and logits
+        into device memory -- and out_done[c] is recorded when the chunk's rows of `out` are final, so
+        that host copies in and out overlap the other chunks' work."""
         if self.transport == "p2p":
-            return self._forward_p2p(layer, x, logits, out)
+            return self._forward_p2p(layer, x, logits, out, in_ready, out_done)
+        if in_ready is not None:
+            for ev in in_ready:
+                self.torch.cuda.current_stream().wait_event(ev)
         torch, dist = self.torch, self.torch.distributed
         T = x.shape[0]
         main = torch.cuda.current_stream()
